@@ -1,0 +1,50 @@
+// Entry points of the C ABI that are not kernels: version, status text, the
+// tuning switches and the read-out of the sticky device status word.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/braid_b200.h"
+#include "ptx.cuh"
+
+namespace bq {
+int quant_set_option(const char* key, long long value);
+int gemm_set_option(const char* key, long long value);
+}  // namespace bq
+
+extern "C" int bq_version(void) { return 100; }
+
+extern "C" const char* bq_status_string(int status) {
+  switch (status) {
+    case BQ_OK: return "ok";
+    case BQ_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or unknown dtype)";
+    case BQ_ERR_UNSUPPORTED: return "unsupported shape, stride or alignment";
+    case BQ_ERR_LAUNCH: return "CUDA refused the kernel launch";
+    case BQ_ERR_WORKSPACE: return "scratch buffer missing, misaligned or too small";
+    case BQ_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+    case BQ_ERR_NO_DRIVER: return "cuTensorMapEncodeTiled is not available from the driver";
+    case BQ_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int bq_set_option(const char* key, int64_t value) {
+  if (key == nullptr) return BQ_ERR_BAD_ARG;
+  if (bq::quant_set_option(key, value) == BQ_OK) return BQ_OK;
+  return bq::gemm_set_option(key, value);
+}
+
+extern "C" int bq_read_device_status(void* ws, void* stream, int* status_out) {
+  if (ws == nullptr || status_out == nullptr) return BQ_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned int word = 0;
+  unsigned int* dev_word = static_cast<unsigned int*>(ws) + 3;
+  if (cudaMemcpyAsync(&word, dev_word, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return BQ_ERR_LAUNCH;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return BQ_ERR_LAUNCH;
+  if (word != 0) {
+    if (cudaMemsetAsync(dev_word, 0, sizeof(word), s) != cudaSuccess) return BQ_ERR_LAUNCH;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return BQ_ERR_LAUNCH;
+  }
+  *status_out = static_cast<int>(word);
+  return BQ_OK;
+}

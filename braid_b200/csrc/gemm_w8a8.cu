@@ -1,0 +1,628 @@
+// Per-tensor FP8 W8A8 GEMM for sm_100a:  Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw.
+//
+// Stands in for the `torch._scaled_mm(xq, w.data.t(), scale_a=sx, scale_b=w.scale)`
+// call of the reference engine (braid/model/quant.py:232-241).  Both operands are
+// K-major, so 128-byte-swizzled TMA tiles feed tcgen05 shared-memory descriptors
+// directly; accumulation is fp32 in tensor memory; the dequant scales and the
+// output cast are applied in the epilogue.
+//
+// Two kernels, chosen by M:
+//
+//  * gemm_stream_kernel (M <= 256, the decode regime; HBM-bound, judged in GB/s).
+//    Operands are swapped: 128 WEIGHT rows sit on the MMA M side and the (padded)
+//    batch on the MMA N side, so a tile streams 128 x K weight bytes whatever the
+//    batch is.  One CTA per (row tile, K slice); the K slices of a tile form a
+//    thread-block cluster and are summed through distributed shared memory in a
+//    fixed order -- no float atomics, so results are run-to-run identical and a
+//    graph replay equals the eager run bit for bit.  Several weights that share
+//    one activation (q/k/v, qkv/z, gate/up) go in one launch, each segment with
+//    its own scale.
+//
+//  * gemm_tile_kernel (M > 256, the prefill regime; tensor-bound, judged in
+//    TFLOP/s).  Persistent, warp-specialised: one TMA producer warp, one MMA
+//    issuer warp, four epilogue warps; 128x256 output tiles; two 256-column
+//    accumulators in tensor memory so a tile's epilogue overlaps the next
+//    tile's main loop.
+//
+// Every mbarrier wait is bounded (ptx.cuh); a wait that runs out sets the sticky
+// status word and the CTA unwinds through the normal teardown.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/braid_b200.h"
+#include "ptx.cuh"
+
+namespace {
+
+using namespace bq;
+
+constexpr int kBK = 128;         // K bytes per pipeline stage: one swizzle span
+constexpr int kUmmaK = 32;       // K elements one f8 MMA consumes
+constexpr int kRowTile = 128;    // MMA M
+constexpr int kATileBytes = kRowTile * kBK;   // 16 KiB
+constexpr int kMaxSmem = 232448;              // 227 KiB opt-in limit per CTA
+constexpr int kBarrierBytes = 1024;           // mbarriers + tmem slot + flags
+
+struct Segment {
+  const float* sw;     // device: weight dequant scale
+  void* y;             // device: output base of this segment
+  long long ldy;       // row stride of y, elements
+  int n;               // weight rows (output columns) of this segment
+  int tile_begin;      // index of the segment's first tile
+};
+
+struct GemmParams {
+  Segment seg[BQ_MAX_SEGMENTS];
+  int n_seg;
+  const float* sx;     // device: activation dequant scale
+  int M;               // activation rows
+  int mma_n;           // stream kernel: padded batch = MMA N (multiple of 16)
+  int k_blocks;        // ceil(K / 128)
+  int split;           // stream kernel: K slices per tile = cluster size
+  int stages;
+  int out_dtype;
+  int m_tiles;         // tile kernel: ceil(M / 128)
+  int total_tiles;     // tile kernel
+  unsigned int* status;
+};
+
+struct alignas(64) WeightMaps {
+  CUtensorMap w[BQ_MAX_SEGMENTS];
+};
+
+__device__ __forceinline__ int find_segment(const GemmParams& p, int tile) {
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < BQ_MAX_SEGMENTS; ++i)
+    if (i < p.n_seg && tile >= p.seg[i].tile_begin) s = i;
+  return s;
+}
+
+__device__ __forceinline__ void store_out4(void* y, long long idx, int out_dtype, float4 v) {
+  if (out_dtype == BQ_DTYPE_BF16) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(y) + idx) = w;
+  } else if (out_dtype == BQ_DTYPE_F16) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y);
+    const __half2 hi = __floats2half2_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<__half*>(y) + idx) = w;
+  } else {
+    *reinterpret_cast<float4*>(static_cast<float*>(y) + idx) = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Weight-streaming kernel (swap-AB, cluster split-K)
+// ---------------------------------------------------------------------------
+// Shared memory, after aligning the dynamic base to 1024 bytes:
+//   [stages x 16 KiB weight tiles][stages x (mma_n*128) activation tiles] ... [barrier block]
+// The tile area is reused after the main loop as the fp32 staging buffer
+// part[m][128] that the cluster reduction reads.
+__global__ void __launch_bounds__(128, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
+                   const __grid_constant__ WeightMaps tm_w, const GemmParams p,
+                   const int smem_tile_bytes) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+  const int b_tile_bytes = p.mma_n * kBK;
+  const uint32_t a_base = base;
+  const uint32_t b_base = base + p.stages * kATileBytes;
+  const uint32_t bar_base = base + smem_tile_bytes;          // 8-byte aligned
+  // barrier block: full[s] at +8s, empty[s] at +8(stages+s), accum at +8*2*stages
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * p.stages);
+  volatile uint32_t* const tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
+  volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int krank = (p.split > 1) ? static_cast<int>(cluster_ctarank()) : 0;
+  const int tile = blockIdx.x / p.split;
+  const int sg = find_segment(p, tile);
+  const Segment seg = p.seg[sg];
+  const int row0 = (tile - seg.tile_begin) * kRowTile;
+
+  // this CTA's K slice, balanced to within one block
+  const int kb_base = p.k_blocks / p.split, kb_rem = p.k_blocks % p.split;
+  const int kb_count = kb_base + (krank < kb_rem ? 1 : 0);
+  const int kb_begin = krank * kb_base + (krank < kb_rem ? krank : kb_rem);
+
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(p.mma_n)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w.w[sg]);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      // weights are read once: evict first; the activation tile is shared by
+      // every row tile: keep it in L2
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % p.stages, use = i / p.stages;
+        if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) {
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(full_bar(s), kATileBytes + b_tile_bytes);
+        const int kx = (kb_begin + i) * kBK;
+        tma_load_2d(a_base + s * kATileBytes, &tm_w.w[sg], full_bar(s), kx, row0, pol_w);
+        tma_load_2d(b_base + s * b_tile_bytes, &tm_x, full_bar(s), kx, 0, pol_x);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = idesc_e4m3(kRowTile, p.mma_n);
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % p.stages, use = i / p.stages;
+        if (!mbar_wait(full_bar(s), use & 1)) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
+        const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
+#pragma unroll
+        for (int j = 0; j < kBK / kUmmaK; ++j) {
+          // +32 bytes along K inside the swizzle span = +2 in descriptor units
+          mma_f8(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
+        }
+        mma_commit(empty_bar(s));   // stage is free once these MMAs retire
+      }
+      mma_commit(accum_bar);        // accumulator complete
+    }
+    __syncwarp();
+  }
+
+  // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
+  bool ok = mbar_wait(accum_bar, 0);
+  tc_fence_after();
+  if (!ok) *abort_flag = 1;
+  __syncthreads();
+  ok = (*abort_flag == 0);
+  float* const part = reinterpret_cast<float*>(base_ptr);   // [mma_n][128]
+  if (ok) {
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const int n_local = warp * 32 + lane;
+    for (int c = 0; c < p.mma_n; c += 16) {
+      uint32_t r[16];
+      tmem_ld16(lane_addr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part[(c + j) * kRowTile + n_local] = __uint_as_float(r[j]);
+    }
+  } else if (threadIdx.x == 0) {
+    atomicExch(p.status, (unsigned int)kErrDeviceWait);
+  }
+  tc_fence_before();
+  if (p.split > 1) cluster_sync_all(); else __syncthreads();
+
+  // ---- reduce the K slices in rank order and write this CTA's share of rows --
+  if (ok) {
+    const float scale = __ldg(p.sx) * __ldg(seg.sw);
+    const int per = (p.M + p.split - 1) / p.split;
+    const int m_begin = krank * per;
+    const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
+    const int n4 = lane * 4;                      // 4 consecutive output columns
+    const bool col_ok = (row0 + n4) < seg.n;      // n is a multiple of 16
+    for (int m = m_begin + warp; m < m_end; m += 4) {
+      const uint32_t off = smem_u32(part + m * kRowTile + n4);
+      float4 acc;
+      if (p.split > 1) {
+        acc = ld_cluster_f4(map_to_cta(off, 0));
+        for (int r = 1; r < p.split; ++r) {
+          const float4 v = ld_cluster_f4(map_to_cta(off, r));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      } else {
+        acc = *reinterpret_cast<const float4*>(part + m * kRowTile + n4);
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      if (col_ok) store_out4(seg.y, (long long)m * seg.ldy + row0 + n4, p.out_dtype, acc);
+    }
+  }
+  // nobody leaves while a peer may still read its staging buffer
+  if (p.split > 1) cluster_sync_all(); else __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// ---------------------------------------------------------------------------
+// Persistent tile kernel (prefill regime)
+// ---------------------------------------------------------------------------
+constexpr int kTileN = 256;                       // MMA N = weight rows per tile
+constexpr int kBTileBytesBig = kTileN * kBK;      // 32 KiB
+constexpr int kStageBytesBig = kATileBytes + kBTileBytesBig;
+constexpr int kStagesBig = 4;
+constexpr int kTileThreads = 192;
+
+__global__ void __launch_bounds__(kTileThreads, 1)
+gemm_tile_kernel(const __grid_constant__ CUtensorMap tm_x,
+                 const __grid_constant__ WeightMaps tm_w, const GemmParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar_base = base + kStagesBig * kStageBytesBig;
+  auto a_tile = [&](int s) { return base + s * kStageBytesBig; };
+  auto b_tile = [&](int s) { return base + s * kStageBytesBig + kATileBytes; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStagesBig + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * kStagesBig + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kStagesBig + 2 + b); };
+  volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + kStagesBig * kStageBytesBig + 8 * (2 * kStagesBig + 4));
+  volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_x);
+    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tm_w.w[i]);
+    for (int s = 0; s < kStagesBig; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);     // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol = policy_evict_last();   // both operands are re-read by other tiles
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const int sg = find_segment(p, t);
+        const int local = t - p.seg[sg].tile_begin;
+        const int m0 = (local % p.m_tiles) * kRowTile;
+        const int n0 = (local / p.m_tiles) * kTileN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStagesBig, use = it / kStagesBig;
+          if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), kStageBytesBig);
+          tma_load_2d(a_tile(s), &tm_x, full_bar(s), kb * kBK, m0, pol);
+          tma_load_2d(b_tile(s), &tm_w.w[sg], full_bar(s), kb * kBK, n0, pol);
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = idesc_e4m3(kRowTile, kTileN);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const int b = tile_iter & 1, use_b = tile_iter >> 1;
+        if (use_b > 0 && !mbar_wait(acc_empty(b), (use_b - 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + b * kTileN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStagesBig, use = it / kStagesBig;
+          if (!mbar_wait(full_bar(s), use & 1)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(a_tile(s));
+          const uint64_t db = smem_desc_sw128(b_tile(s));
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j)
+            mma_f8(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+          mma_commit(empty_bar(s));
+        }
+        if (ok) mma_commit(acc_full(b));
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    // epilogue warps 2..5; a warp may only touch TMEM lanes [32*(warp%4), +32)
+    const int quad = warp & 3;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const int b = tile_iter & 1, use_b = tile_iter >> 1;
+      const int sg = find_segment(p, t);
+      const Segment seg = p.seg[sg];
+      const int local = t - seg.tile_begin;
+      const int m0 = (local % p.m_tiles) * kRowTile;
+      const int n0 = (local / p.m_tiles) * kTileN;
+      if (!mbar_wait(acc_full(b), use_b & 1)) { ok = false; break; }
+      tc_fence_after();
+      const float scale = __ldg(p.sx) * __ldg(seg.sw);
+      const int m = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * kTileN;
+      for (int c = 0; c < kTileN; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c, r);          // warp-collective: no divergence before it
+        tmem_ld_wait();
+        if (m < p.M && (n0 + c) < seg.n) {
+          const long long idx = (long long)m * seg.ldy + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            float4 v = make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
+                                   __uint_as_float(r[j + 2]) * scale,
+                                   __uint_as_float(r[j + 3]) * scale);
+            store_out4(seg.y, idx + j, p.out_dtype, v);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(b));
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, (unsigned int)kErrDeviceWait);
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// [rows, K] uint8 row-major tensor, box = 128 K-bytes x box_rows, 128-byte swizzle,
+// out-of-range rows/columns read as zero.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return kErrNoDriver;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? kOk : kErrUnsupported;
+}
+
+int device_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (sms[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    sms[dev] = v;
+  }
+  return sms[dev];
+}
+
+long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256;
+thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int configure_once() {
+  static int rc = -1;
+  if (rc < 0) {
+    cudaError_t e1 = cudaFuncSetAttribute(gemm_stream_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e2 = cudaFuncSetAttribute(gemm_tile_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    rc = (e1 == cudaSuccess && e2 == cudaSuccess) ? kOk : kErrLaunch;
+    if (rc != kOk) (void)cudaGetLastError();
+  }
+  return rc;
+}
+
+int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, int tiles,
+                  cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return kErrLaunch;
+  p.mma_n = ((p.M + 15) / 16) * 16;
+  const int b_tile = p.mma_n * kBK;
+  const int stage_bytes = kATileBytes + b_tile;
+  // K slices: enough CTAs to cover the SMs, as a cluster of 1/2/4/8
+  int split = 1;
+  while (split < 8 && tiles * split < sms && split * 2 <= p.k_blocks) split *= 2;
+  if (g_opt_split > 0) {
+    split = (int)g_opt_split;
+    if (split > 8) split = 8;
+    while (split > p.k_blocks) --split;
+  }
+  p.split = split;
+  const int kb_max = (p.k_blocks + split - 1) / split;
+  const int staging = p.mma_n * kRowTile * 4;
+  // deep enough to keep ~100 KB in flight, but no deeper than the slice
+  int stages = (kMaxSmem - kBarrierBytes - 1024) / stage_bytes;
+  if (stages > kb_max) stages = kb_max;
+  if (stages > 24) stages = 24;
+  if (g_opt_stages > 0 && g_opt_stages < stages) stages = (int)g_opt_stages;
+  if (stages < 1) return kErrUnsupported;
+  p.stages = stages;
+  int tile_bytes = stages * stage_bytes;
+  if (tile_bytes < staging) tile_bytes = staging;
+  const int smem = tile_bytes + kBarrierBytes + 1024;
+  if (smem > kMaxSmem) return kErrUnsupported;
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  g_last_launch[0] = 0; g_last_launch[1] = tiles * split; g_last_launch[2] = split;
+  g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
+  return kOk;
+}
+
+int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return kErrLaunch;
+  const int smem = kStagesBig * kStageBytesBig + kBarrierBytes + 1024;
+  int grid = p.total_tiles < sms ? p.total_tiles : sms;
+  g_last_launch[0] = 1; g_last_launch[1] = grid; g_last_launch[2] = 1;
+  g_last_launch[3] = kStagesBig; g_last_launch[4] = smem; g_last_launch[5] = kTileN;
+  gemm_tile_kernel<<<grid, kTileThreads, smem, stream>>>(tm_x, maps, p);
+  if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
+  return kOk;
+}
+
+}  // namespace
+
+namespace bq {
+int gemm_set_option(const char* key, long long value);
+}
+int bq::gemm_set_option(const char* key, long long value) {
+  if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
+  if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
+  if (strcmp(key, "stream_max_m") == 0) {
+    if (value < 1 || value > 256) return kErrBadArg;
+    g_opt_stream_max_m = value;
+    return kOk;
+  }
+  return kErrBadArg;
+}
+
+extern "C" size_t bq_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 16; }
+
+extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
+                                    const void* const* wq, const float* const* sw, void* const* y,
+                                    const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
+                                    size_t ws_bytes, void* stream_v) {
+  if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
+  if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
+  if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
+    return kErrBadArg;
+  if (ws == nullptr || ws_bytes < 16 || !aligned_to(ws, 16)) return kErrWorkspace;
+  if (K % 16 || !aligned_to(xq, 16)) return kErrUnsupported;
+  if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
+  if (int rc = configure_once()) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  WeightMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  p.n_seg = n_seg;
+  p.sx = sx;
+  p.M = (int)M;
+  p.k_blocks = (int)((K + kBK - 1) / kBK);
+  p.out_dtype = out_dtype;
+  // the sticky status word is the 4th word of the scratch, as in the quantizer
+  p.status = static_cast<unsigned int*>(ws) + 3;
+
+  const bool stream_path = M <= g_opt_stream_max_m;
+  const int w_box_rows = stream_path ? kRowTile : kTileN;
+  const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
+  p.m_tiles = (int)((M + kRowTile - 1) / kRowTile);
+  int tiles = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    if (!wq[i] || !sw[i] || !y[i] || N[i] <= 0) return kErrBadArg;
+    if (N[i] % 16 || ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(wq[i], 16) ||
+        !aligned_to(y[i], out_align))
+      return kErrUnsupported;
+    if (N[i] > 0x7fffff00LL) return kErrTooLarge;
+    p.seg[i].sw = sw[i];
+    p.seg[i].y = y[i];
+    p.seg[i].ldy = ldy[i];
+    p.seg[i].n = (int)N[i];
+    p.seg[i].tile_begin = tiles;
+    const long long nt = (N[i] + w_box_rows - 1) / w_box_rows;
+    const long long add = stream_path ? nt : nt * p.m_tiles;
+    if (tiles + add > 0x3fffffffLL) return kErrTooLarge;
+    tiles += (int)add;
+    if (int rc = make_map(&maps.w[i], wq[i], N[i], K, w_box_rows)) return rc;
+  }
+  p.total_tiles = tiles;
+  CUtensorMap tm_x;
+  if (stream_path) {
+    const int mma_n = (int)(((M + 15) / 16) * 16);
+    if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
+    return launch_stream(tm_x, maps, p, tiles, stream);
+  }
+  if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
+  return launch_tile(tm_x, maps, p, stream);
+}
+
+extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* sw,
+                            void* y, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                            void* ws, size_t ws_bytes, void* stream) {
+  const void* wqs[1] = {wq};
+  const float* sws[1] = {sw};
+  void* ys[1] = {y};
+  const int64_t Ns[1] = {N};
+  const int64_t ldys[1] = {ldy};
+  return bq_gemm_w8a8_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes,
+                              stream);
+}
+
+extern "C" int bq_last_gemm_launch(int64_t out[6]) {
+  if (!out) return kErrBadArg;
+  for (int i = 0; i < 6; ++i) out[i] = g_last_launch[i];
+  return kOk;
+}

@@ -1,0 +1,445 @@
+// Dynamic per-tensor FP8 (e4m3fn) activation quantization for sm_100a, one launch.
+//
+//   scale = max(amax(|x|) * (1/448), 1e-12)        q = e4m3(clamp(x / scale, +-448))
+//
+// The arithmetic follows, operation for operation, what the reference engine's
+// torch spelling evaluates on a CUDA device (braid/model/quant.py:108-115 and
+// :228-229; the two-launch kernel braid/kernels/csrc/quant_act.cu:90-131 states
+// the same contract): the scale is a reciprocal MULTIPLY, `x / scale` is a true
+// IEEE division, clamps are comparisons so NaN survives, and the amax is a
+// NaN-propagating max.  max() is exact and order-free, so any grid produces the
+// same scale bits.
+//
+// Shape of the kernel (HBM-bound, 3 bytes moved per bf16 element):
+//   * every thread pulls up to kMaxHeld groups of 8 elements with 128-bit loads
+//     and KEEPS them in registers;
+//   * |x| max: per thread -> warp shuffles -> shared memory -> one atomicMax per
+//     CTA on the bit pattern of the non-negative float (exact; NaN patterns sort
+//     above +inf, which is the propagation torch.amax has);
+//   * a bounded grid barrier (all CTAs co-resident: grid <= #SMs), after which
+//     each thread casts what it holds and writes 8 codes with one 64-bit store.
+//   Inputs too large to hold (prefill sizes) use the streaming variant: same
+//   barrier, second read served mostly by the 126 MB L2.
+// Two prologue variants build the activation in registers first and never write
+// it to memory: SiLU(gate)*up (braid/model/mlp.py:48) and o*sigmoid(gate)
+// (braid/model/attention.py:215), with the double rounding of the two separate
+// torch kernels preserved.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/braid_b200.h"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr float kFp8Max = 448.0f;
+// torch divides a tensor by a host scalar as t * (1/scalar) in fp32.
+constexpr float kInvFp8Max = 1.0f / 448.0f;
+constexpr float kEps = 1e-12f;
+
+constexpr int kMaxHeld = 8;    // groups of 8 elements a thread may keep in registers
+constexpr int kGroup = 8;      // elements per group (one 128-bit load of a 16-bit type)
+
+// Scratch words shared by all quantizer kernels (16 bytes, zero between launches).
+struct QuantWs {
+  unsigned int amax_bits;  // running max of |x| as a float bit pattern
+  unsigned int arrive;     // CTAs that published their max
+  unsigned int depart;     // CTAs that consumed the global max
+  unsigned int status;     // sticky: non-zero once a bounded wait ran out
+};
+
+enum Mode { kPlain = 0, kSiluMul = 1, kSigmoidGate = 2 };
+
+struct QParams {
+  const void* a;        // x | gate | o
+  const void* b;        // - | up   | gate
+  uint8_t* q;
+  float* scale;
+  QuantWs* ws;
+  unsigned int n_groups;      // full groups of 8
+  unsigned int tail;          // plain mode only: leftover elements (< 8)
+  unsigned int groups_per_row;
+  long long ld_a, ld_b;       // row strides in elements (prologue modes)
+  unsigned int chunk;         // sigmoid gate: head width of the strided gate view
+  long long chunk_stride;     // sigmoid gate: distance between heads
+  int held;                   // groups each thread keeps (hold kernel)
+};
+
+template <typename T> struct alignas(16) Pack8 { T v[8]; };
+template <> struct alignas(16) Pack8<float> { float v[8]; };
+
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T narrow(float v);
+template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// NaN-propagating max: once either side is NaN the result is NaN.
+__device__ __forceinline__ float nan_max(float m, float v) { return (v != v || v > m) ? v : m; }
+
+template <typename T>
+__device__ __forceinline__ Pack8<T> load8(const T* p) {
+  Pack8<T> r;
+  if constexpr (sizeof(T) == 4) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    r.v[0] = lo.x; r.v[1] = lo.y; r.v[2] = lo.z; r.v[3] = lo.w;
+    r.v[4] = hi.x; r.v[5] = hi.y; r.v[6] = hi.z; r.v[7] = hi.w;
+  } else {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    *reinterpret_cast<uint4*>(&r) = raw;
+  }
+  return r;
+}
+
+// Builds the 8 activation values of group g for the given prologue.
+template <typename T, int MODE>
+__device__ __forceinline__ Pack8<T> produce(const QParams& p, unsigned int g) {
+  if constexpr (MODE == kPlain) {
+    return load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
+  } else {
+    const unsigned int row = g / p.groups_per_row;
+    const unsigned int col = (g - row * p.groups_per_row) * kGroup;
+    const T* pa = reinterpret_cast<const T*>(p.a) + static_cast<long long>(row) * p.ld_a + col;
+    const T* pb;
+    if constexpr (MODE == kSiluMul) {
+      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b + col;
+    } else {
+      const unsigned int head = col / p.chunk;
+      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
+           static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
+    }
+    const Pack8<T> a = load8(pa);
+    const Pack8<T> b = load8(pb);
+    Pack8<T> h;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (MODE == kSiluMul) {
+        // silu in fp32, rounded to T; product in fp32, rounded to T
+        const float x = widen(a.v[i]);
+        const T s = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
+        h.v[i] = narrow<T>(widen(s) * widen(b.v[i]));
+      } else {
+        const float gt = widen(b.v[i]);
+        const T s = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
+        h.v[i] = narrow<T>(widen(a.v[i]) * widen(s));
+      }
+    }
+    return h;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float absmax8(const Pack8<T>& v, float m) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = nan_max(m, fabsf(widen(v.v[i])));
+  return m;
+}
+
+__device__ __forceinline__ float quant_one(float x, float sc) {
+  float v = __fdiv_rn(x, sc);
+  // comparison clamps: both are false for NaN, which therefore falls through
+  v = (v < -kFp8Max) ? -kFp8Max : ((v > kFp8Max) ? kFp8Max : v);
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void emit8(const Pack8<T>& v, float sc, uint8_t* dst) {
+  uint32_t w[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int i = half * 4 + j * 2;
+      const float2 f = make_float2(quant_one(widen(v.v[i]), sc), quant_one(widen(v.v[i + 1]), sc));
+      const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      word |= (pair & 0xFFFFu) << (16 * j);
+    }
+    w[half] = word;
+  }
+  *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// CTA-wide max, then the grid-wide exchange.  Returns the global amax to every
+// thread.  A single-CTA grid never touches global memory here.
+__device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
+  __shared__ float s_warp[32];
+  __shared__ float s_amax;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_warp[warp] = m;
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float w = (lane < nwarps) ? s_warp[lane] : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) w = nan_max(w, __shfl_xor_sync(0xffffffffu, w, off));
+    if (lane == 0) {
+      if (gridDim.x == 1) {
+        s_amax = w;
+      } else {
+        // |x| >= 0 or NaN with the sign cleared: the unsigned order of the bit
+        // patterns is the order of the values, NaN on top.
+        atomicMax(&ws->amax_bits, __float_as_uint(w));
+        __threadfence();
+        atomicAdd(&ws->arrive, 1u);
+        const long long t0 = clock64();
+        bool ok = true;
+        while (ld_acquire_u32(&ws->arrive) < gridDim.x) {
+          if (clock64() - t0 > bq::kSpinLimitCycles) { ok = false; break; }
+        }
+        if (!ok) atomicExch(&ws->status, (unsigned int)bq::kErrDeviceWait);
+        s_amax = __uint_as_float(ld_acquire_u32(&ws->amax_bits));
+        __threadfence();
+        // the last CTA to have read the result returns the scratch to zero, so
+        // the next launch (and a graph replay) starts clean
+        const unsigned int old = atomicAdd(&ws->depart, 1u);
+        if (old == gridDim.x - 1) {
+          ws->amax_bits = 0u;
+          ws->arrive = 0u;
+          ws->depart = 0u;
+          __threadfence();
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s_amax;
+}
+
+__device__ __forceinline__ float scale_from_amax(float amax) {
+  const float raw = amax * kInvFp8Max;
+  return (raw < kEps) ? kEps : raw;   // NaN compares false and stays NaN
+}
+
+// Hold variant: each thread keeps `p.held` (<= kMaxHeld) groups in registers
+// across the barrier, so the activation is read exactly once.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
+  const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned int nthreads = gridDim.x * blockDim.x;
+  Pack8<T> held[kMaxHeld];
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMaxHeld; ++i) {
+    const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
+    if (i < p.held && g < p.n_groups) {
+      held[i] = produce<T, MODE>(p, g);
+      m = absmax8(held[i], m);
+    }
+  }
+  // plain mode: up to 7 trailing elements, owned by the last thread of the grid
+  float tail_v[kGroup - 1];
+  const bool owns_tail = (MODE == kPlain) && p.tail != 0 && tid == nthreads - 1;
+  if (owns_tail) {
+    const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+    for (unsigned int i = 0; i < p.tail; ++i) {
+      tail_v[i] = widen(src[i]);
+      m = nan_max(m, fabsf(tail_v[i]));
+    }
+  }
+  const float sc = scale_from_amax(grid_amax(m, p.ws));
+  if (tid == 0) p.scale[0] = sc;
+#pragma unroll
+  for (int i = 0; i < kMaxHeld; ++i) {
+    const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
+    if (i < p.held && g < p.n_groups) emit8(held[i], sc, p.q + static_cast<size_t>(g) * kGroup);
+  }
+  if (owns_tail) {
+    uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
+    for (unsigned int i = 0; i < p.tail; ++i)
+      dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+// Streaming variant for activations that do not fit in the register file of
+// one co-resident grid: pass 1 reduces, pass 2 re-reads (L2) and casts.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
+  const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned int nthreads = gridDim.x * blockDim.x;
+  float m = 0.0f;
+  for (unsigned int g = tid; g < p.n_groups; g += nthreads) m = absmax8(produce<T, MODE>(p, g), m);
+  const bool owns_tail = (MODE == kPlain) && p.tail != 0 && tid == nthreads - 1;
+  if (owns_tail) {
+    const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+    for (unsigned int i = 0; i < p.tail; ++i) m = nan_max(m, fabsf(widen(src[i])));
+  }
+  const float sc = scale_from_amax(grid_amax(m, p.ws));
+  if (tid == 0) p.scale[0] = sc;
+  // walk backwards: the groups read last in pass 1 are the likeliest still in L2
+  for (long long g = (long long)p.n_groups - 1 - tid; g >= 0; g -= nthreads)
+    emit8(produce<T, MODE>(p, (unsigned int)g), sc, p.q + static_cast<size_t>(g) * kGroup);
+  if (owns_tail) {
+    const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+    uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
+    for (unsigned int i = 0; i < p.tail; ++i)
+      dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(src[i]), sc), __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+struct DeviceInfo {
+  int sms = 0;
+};
+
+int device_sms() {
+  static DeviceInfo info[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (info[dev].sms == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    info[dev].sms = v;
+  }
+  return info[dev].sms;
+}
+
+long long g_opt_quant_block = 0;   // 0 = heuristic
+long long g_opt_quant_held = 0;    // 0 = heuristic
+
+template <typename T, int MODE>
+int launch_quant(QParams p, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return bq::kErrLaunch;
+  const unsigned long long groups = p.n_groups;
+  // Spread over CTAs first (one group per thread), then deepen each thread up
+  // to kMaxHeld, then switch to the wide block; beyond that, stream.
+  int block = 256;
+  if (groups > (unsigned long long)sms * 256ull * kMaxHeld) block = 512;
+  if (g_opt_quant_block == 256 || g_opt_quant_block == 512) block = (int)g_opt_quant_block;
+  const unsigned long long cap = (unsigned long long)sms * block * kMaxHeld;
+  if (groups <= cap) {
+    int held = 1;
+    while ((unsigned long long)sms * block * held < groups) ++held;
+    if (g_opt_quant_held >= held && g_opt_quant_held <= kMaxHeld) held = (int)g_opt_quant_held;
+    unsigned long long per_cta = (unsigned long long)block * held;
+    int grid = (int)((groups + per_cta - 1) / per_cta);
+    if (grid < 1) grid = 1;
+    p.held = held;
+    quant_hold_kernel<T, MODE><<<grid, block, 0, stream>>>(p);
+  } else {
+    p.held = 0;
+    quant_stream_kernel<T, MODE><<<2 * sms, 512, 0, stream>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? bq::kOk : bq::kErrLaunch;
+}
+
+template <int MODE>
+int dispatch_dtype(int dtype, const QParams& p, cudaStream_t stream) {
+  switch (dtype) {
+    case BQ_DTYPE_F32: return launch_quant<float, MODE>(p, stream);
+    case BQ_DTYPE_BF16: return launch_quant<__nv_bfloat16, MODE>(p, stream);
+    case BQ_DTYPE_F16: return launch_quant<__half, MODE>(p, stream);
+    default: return bq::kErrBadArg;
+  }
+}
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline size_t elem_size(int dtype) { return dtype == BQ_DTYPE_F32 ? 4 : 2; }
+
+int check_ws(void* ws, size_t ws_bytes) {
+  if (ws == nullptr || ws_bytes < sizeof(QuantWs) || !aligned_to(ws, 16)) return bq::kErrWorkspace;
+  return bq::kOk;
+}
+
+}  // namespace
+
+namespace bq {
+int quant_set_option(const char* key, long long value);
+}
+int bq::quant_set_option(const char* key, long long value) {
+  auto eq = [](const char* a, const char* b) {
+    while (*a && *a == *b) { ++a; ++b; }
+    return *a == *b;
+  };
+  if (eq(key, "quant_block")) { g_opt_quant_block = value; return kOk; }
+  if (eq(key, "quant_held")) { g_opt_quant_held = value; return kOk; }
+  return kErrBadArg;
+}
+
+extern "C" size_t bq_quant_workspace_bytes(void) { return sizeof(QuantWs); }
+
+extern "C" int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out, float* scale_out,
+                               void* ws, size_t ws_bytes, void* stream) {
+  if (x == nullptr || q_out == nullptr || scale_out == nullptr || n <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  if (!aligned_to(x, 16) || !aligned_to(q_out, 8)) return bq::kErrUnsupported;
+  if (n / kGroup >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = x;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = scale_out;
+  p.ws = static_cast<QuantWs*>(ws);
+  p.n_groups = static_cast<unsigned int>(n / kGroup);
+  p.tail = static_cast<unsigned int>(n % kGroup);
+  p.groups_per_row = 1;
+  return dispatch_dtype<kPlain>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_silu_mul_quant(const void* gate, const void* up, int dtype, int64_t rows,
+                                 int64_t cols, int64_t ld_gate, int64_t ld_up, void* q_out,
+                                 float* scale_out, void* ws, size_t ws_bytes, void* stream) {
+  if (!gate || !up || !q_out || !scale_out || rows <= 0 || cols <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  const size_t es = elem_size(dtype);
+  if (cols % kGroup || ld_gate < cols || ld_up < cols || (ld_gate * es) % 16 || (ld_up * es) % 16 ||
+      !aligned_to(gate, 16) || !aligned_to(up, 16) || !aligned_to(q_out, 8))
+    return bq::kErrUnsupported;
+  if (rows * (cols / kGroup) >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = gate;
+  p.b = up;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = scale_out;
+  p.ws = static_cast<QuantWs*>(ws);
+  p.groups_per_row = static_cast<unsigned int>(cols / kGroup);
+  p.n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
+  p.ld_a = ld_gate;
+  p.ld_b = ld_up;
+  return dispatch_dtype<kSiluMul>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t rows,
+                                     int64_t cols, int64_t ld_o, int64_t ld_gate, int64_t chunk,
+                                     int64_t chunk_stride, void* q_out, float* scale_out, void* ws,
+                                     size_t ws_bytes, void* stream) {
+  if (!o || !gate || !q_out || !scale_out || rows <= 0 || cols <= 0 || chunk <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  const size_t es = elem_size(dtype);
+  if (cols % kGroup || chunk % kGroup || cols % chunk || ld_o < cols || (ld_o * es) % 16 ||
+      (ld_gate * es) % 16 || (chunk_stride * es) % 16 || !aligned_to(o, 16) ||
+      !aligned_to(gate, 16) || !aligned_to(q_out, 8))
+    return bq::kErrUnsupported;
+  if (rows * (cols / kGroup) >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = o;
+  p.b = gate;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = scale_out;
+  p.ws = static_cast<QuantWs*>(ws);
+  p.groups_per_row = static_cast<unsigned int>(cols / kGroup);
+  p.n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
+  p.ld_a = ld_o;
+  p.ld_b = ld_gate;
+  p.chunk = static_cast<unsigned int>(chunk);
+  p.chunk_stride = chunk_stride;
+  return dispatch_dtype<kSigmoidGate>(dtype, p, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,534 @@
+"""FP8 W8A8 projections on B200 — the host-side mirror of `braid/model/quant.py`.
+
+Same names, signatures and return conventions as the reference module
+(braid/model/quant.py:61-298), so the sublayers that import from it
+(braid/model/mlp.py:16, gdn.py:35, attention.py:27, engine.py:30-37) run
+unchanged; what is underneath is replaced:
+
+  * `quantize_act`  -> one launch of the sm_100a quantizer (`bq_quantize_act`)
+    instead of nine torch kernels / the reference's two-launch kernel;
+  * `fp8_matmul`    -> the hand-written tcgen05 GEMM (`bq_gemm_w8a8`) instead of
+    `torch._scaled_mm`;
+  * `project`       -> one quantization plus ONE grouped GEMM launch for all FP8
+    weights of the call (per-weight scales kept, results identical to separate
+    calls);
+  * new: `silu_mul_quant`, `sigmoid_gate_quant`, `fp8_matmul_grouped`,
+    `mlp_forward`, `gated_output_projection` — the fused prologues the reference
+    leaves as separate bf16 kernels (braid/model/mlp.py:48, attention.py:215).
+
+Weights are quantized with the reference's own torch spelling (load-time work,
+braid/model/quant.py:118-154), on whatever device the weight lives on.
+
+There is no CPU implementation of the kernels: activations must be CUDA
+tensors, and a missing library is an error, not a silent slow path.  The only
+torch arm kept is the one the reference keeps as API behaviour: a
+non-contiguous (or misaligned) activation is quantized by the torch spelling,
+which is exact, and `warm_fused(False)` selects that spelling on purpose for the
+parity gate.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from collections.abc import Iterable, Sequence
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+GROUPS = ("mlp", "attn", "gdn", "head")
+
+
+def parse_groups(spec: str | Iterable[str] | None) -> frozenset[str]:
+    """`"mlp,attn"` / `("mlp", "attn")` / `"all"` / `""` -> a set of group names.
+
+    Unknown names raise `ValueError` (braid/model/quant.py:64-80): a typo must
+    not yield a run that is labelled quantized and is not.
+    """
+    if not spec:
+        return frozenset()
+    names = spec.split(",") if isinstance(spec, str) else list(spec)
+    names = [n.strip() for n in names if n.strip()]
+    if "all" in names:
+        return frozenset(GROUPS)
+    bad = sorted(set(names) - set(GROUPS))
+    if bad:
+        raise ValueError(f"unknown quant group(s) {bad}; known: {list(GROUPS)}")
+    return frozenset(names)
+
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+EPS = 1e-12
+
+_DTYPE_CODE = {torch.float32: _lib.BQ_DTYPE_F32, torch.bfloat16: _lib.BQ_DTYPE_BF16,
+               torch.float16: _lib.BQ_DTYPE_F16}
+
+
+@dataclass
+class FP8Weight:
+    """A `[N, K]` weight held as e4m3 with one dequant scale (braid/model/quant.py:90-105).
+
+    `scale` is a `[1, 1]` fp32 DEVICE tensor: the kernels read it through a
+    pointer, so a captured graph stays valid and nothing is boxed per call.
+    """
+
+    data: torch.Tensor       # [N, K] float8_e4m3fn, row-major (K contiguous)
+    scale: torch.Tensor      # [1, 1] float32
+    shape: tuple[int, int]
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel() + 4
+
+
+def _act_scale(t: torch.Tensor) -> torch.Tensor:
+    """Per-tensor dequant scale, the obvious way (braid/model/quant.py:108-115)."""
+    return (t.detach().float().abs().amax() / FP8_MAX).clamp(min=EPS).reshape(1, 1)
+
+
+def _weight_scale(t: torch.Tensor) -> torch.Tensor:
+    """Same value without an fp32 image of the weight (braid/model/quant.py:118-130)."""
+    t = t.detach()
+    return ((torch.maximum(t.amax().abs(), t.amin().abs()).float() / FP8_MAX)
+            .clamp(min=EPS).reshape(1, 1))
+
+
+# Largest fp32 temporary `quantize_weight` builds at once (braid/model/quant.py:136).
+_CAST_CHUNK_BYTES = 256 * 2 ** 20
+
+
+def quantize_weight(w: torch.Tensor) -> FP8Weight:
+    """`[N, K]` -> e4m3 + one per-tensor scale, once, at load (braid/model/quant.py:139-154)."""
+    if w.dim() != 2:
+        raise ValueError(f"expected a 2-D weight, got {tuple(w.shape)}")
+    N, K = w.shape
+    if K % 16 or N % 16:
+        raise ValueError(
+            f"_scaled_mm needs both weight dims to be multiples of 16; got "
+            f"[{N}, {K}]. Leave this projection in bf16.")
+    scale = _weight_scale(w)
+    data = torch.empty((N, K), dtype=FP8, device=w.device)
+    rows = max(1, min(N, _CAST_CHUNK_BYTES // (K * 4)))
+    for i in range(0, N, rows):
+        band = w[i:i + rows]
+        data[i:i + rows] = (band.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return FP8Weight(data=data, scale=scale, shape=(N, K))
+
+
+# ---------------------------------------------------------------------------
+# library state
+# ---------------------------------------------------------------------------
+_FUSED = None                 # the loaded ctypes library, or None when switched off
+_FUSED_STATE = "not tried"
+_LOCK = threading.Lock()
+
+# Scratch for the kernels: 16-byte slots (amax word, two barrier counters, a
+# sticky status word), zeroed once and returned to zero by the kernels.  Calls
+# take slots round-robin so that launches in flight on different streams do not
+# share barrier words.
+_SLOTS = 256
+_SLOT_BYTES = 64
+_scratch: dict[int, torch.Tensor] = {}
+_next_slot: dict[int, int] = {}
+
+
+def warm_fused(enable: bool = True) -> bool:
+    """Load the kernel library (and its scratch) up front, or switch it off.
+
+    Same contract as braid/model/quant.py:161-201: call it before any CUDA-graph
+    capture; `warm_fused(False)` forces the torch spelling for the parity gate;
+    the return value says whether the kernels are active and `fused_state()`
+    gives the one-line report.  Unlike the reference, a library that cannot be
+    loaded RAISES: there is no slower arm that would make a benchmark look
+    plausible without the kernels.
+    """
+    global _FUSED, _FUSED_STATE
+    if not enable:
+        _FUSED, _FUSED_STATE = None, "disabled by caller"
+        return False
+    if _FUSED is not None:
+        return True
+    try:
+        lib = _lib.load()
+    except Exception as e:
+        _FUSED = None
+        _FUSED_STATE = f"unavailable: {type(e).__name__}: {str(e).split(chr(10), 1)[0][:120]}"
+        raise
+    _FUSED, _FUSED_STATE = lib, "active"
+    if torch.cuda.is_available():
+        _scratch_for(torch.cuda.current_device())
+    return True
+
+
+def fused_state() -> str:
+    """One line on whether the kernels are running (braid/model/quant.py:204-206)."""
+    return _FUSED_STATE
+
+
+def _require_lib():
+    """The loaded library; loading is attempted on first use and failure raises.
+
+    `warm_fused(False)` only selects the torch spelling of the QUANTIZERS (the
+    parity arm); the GEMM has no torch arm here and always needs the library.
+    """
+    if _FUSED is not None:
+        return _FUSED
+    if _FUSED_STATE == "disabled by caller":
+        lib = _lib.load()
+        if torch.cuda.is_available():
+            _scratch_for(torch.cuda.current_device())
+        return lib
+    warm_fused(True)
+    return _FUSED
+
+
+def _quantizers_off() -> bool:
+    return _FUSED is None and _FUSED_STATE == "disabled by caller"
+
+
+def _scratch_for(device_index: int) -> torch.Tensor:
+    buf = _scratch.get(device_index)
+    if buf is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("braid_b200: call warm_fused() before CUDA-graph capture "
+                               "(the kernel scratch cannot be created inside a capture)")
+        with _LOCK:
+            buf = _scratch.get(device_index)
+            if buf is None:
+                buf = torch.zeros(_SLOTS * _SLOT_BYTES, dtype=torch.uint8,
+                                  device=torch.device("cuda", device_index))
+                torch.cuda.synchronize(device_index)
+                _scratch[device_index] = buf
+                _next_slot[device_index] = 0
+    return buf
+
+
+def _take_slot(device: torch.device) -> int:
+    """Device address of the next scratch slot of this device."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _scratch_for(idx)
+    slot = _next_slot[idx]
+    _next_slot[idx] = (slot + 1) % _SLOTS
+    return buf.data_ptr() + slot * _SLOT_BYTES
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_status(device: torch.device | int | None = None) -> int:
+    """Synchronise and return the sticky status of every scratch slot (0 = clean).
+
+    A non-zero value means a bounded device-side wait ran out at some point
+    since the last check.  Never call this during capture.
+    """
+    if device is None:
+        idx = torch.cuda.current_device()
+    elif isinstance(device, int):
+        idx = device
+    else:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _scratch.get(idx)
+    if buf is None:
+        return 0
+    torch.cuda.synchronize(idx)
+    words = buf.view(torch.int32).view(_SLOTS, _SLOT_BYTES // 4)[:, 3]
+    bad = int(words.max().item())
+    if bad:
+        words.zero_()
+    return bad
+
+
+def set_option(key: str, value: int) -> None:
+    """Tuning switch of the library (`decode_split_k`, `decode_stages`, `quant_block`, ...)."""
+    _lib.check(_require_lib().bq_set_option(key.encode(), int(value)), f"set_option({key})")
+
+
+def last_gemm_launch() -> dict:
+    """What the last GEMM call of this thread launched (kernel, grid, split, stages, smem, tile)."""
+    out = (ctypes.c_int64 * 6)()
+    _lib.check(_require_lib().bq_last_gemm_launch(out), "last_gemm_launch")
+    return {"kernel": "stream" if out[0] == 0 else "tile", "grid": out[1], "split": out[2],
+            "stages": out[3], "smem": out[4], "mma_n": out[5]}
+
+
+# ---------------------------------------------------------------------------
+# activation quantization
+# ---------------------------------------------------------------------------
+def _torch_quantize(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The reference spelling, braid/model/quant.py:228-229."""
+    scale = _act_scale(x)
+    return (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8), scale
+
+
+def _check_cuda(x: torch.Tensor, what: str) -> None:
+    if not x.is_cuda:
+        raise RuntimeError(f"{what}: braid_b200 kernels run on CUDA tensors only "
+                           f"(got a {x.device.type} tensor); there is no CPU path")
+
+
+def quantize_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """`[M, K]` (any shape) -> e4m3 codes of the same shape plus a `[1, 1]` fp32 scale.
+
+    Dynamic, per call; bit-identical to the torch spelling on the same device
+    (braid/model/quant.py:209-229).  Contiguous CUDA activations of fp32 / bf16 /
+    fp16 take the one-launch kernel; a non-contiguous or 16-byte-misaligned view
+    takes the torch spelling, as the reference does (`tests/test_quant.py:424-449`).
+    """
+    _check_cuda(x, "quantize_act")
+    if _quantizers_off():
+        return _torch_quantize(x)
+    lib = _require_lib()
+    code = _DTYPE_CODE.get(x.dtype)
+    if code is None:
+        raise ValueError(f"activation must be fp32, bf16 or fp16, got {x.dtype}")
+    if x.numel() == 0:
+        raise ValueError("x must not be empty")
+    if not x.is_contiguous() or x.data_ptr() % 16:
+        return _torch_quantize(x)
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    scale = torch.empty((1, 1), dtype=torch.float32, device=x.device)
+    rc = lib.bq_quantize_act(x.data_ptr(), code, x.numel(), q.data_ptr(), scale.data_ptr(),
+                             _take_slot(x.device), 16, _stream_ptr(x.device))
+    _lib.check(rc, "quantize_act")
+    return q, scale
+
+
+def silu_mul_quant(gate: torch.Tensor, up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """`quantize_act(F.silu(gate) * up)` in one launch, without materialising the product.
+
+    Bit-identical to the two-kernel bf16 spelling followed by the quantizer
+    (braid/model/mlp.py:48-49).  `gate` and `up` are `[..., I]` with a contiguous
+    last axis; they may be two column blocks of one `[M, 2I]` buffer.
+    """
+    _check_cuda(gate, "silu_mul_quant")
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    if _quantizers_off():
+        return _torch_quantize(F.silu(gate) * up)
+    lib = _require_lib()
+    code = _DTYPE_CODE.get(gate.dtype)
+    if code is None:
+        raise ValueError(f"activation must be fp32, bf16 or fp16, got {gate.dtype}")
+    cols = gate.shape[-1]
+    g2, u2 = _as_rows(gate, cols), _as_rows(up, cols)
+    rows = g2.shape[0]
+    q = torch.empty((rows, cols), dtype=FP8, device=gate.device)
+    scale = torch.empty((1, 1), dtype=torch.float32, device=gate.device)
+    rc = lib.bq_silu_mul_quant(g2.data_ptr(), u2.data_ptr(), code, rows, cols,
+                               g2.stride(0), u2.stride(0), q.data_ptr(), scale.data_ptr(),
+                               _take_slot(gate.device), 16, _stream_ptr(gate.device))
+    _lib.check(rc, "silu_mul_quant")
+    return q.reshape(*gate.shape[:-1], cols), scale
+
+
+def sigmoid_gate_quant(o: torch.Tensor, gate: torch.Tensor,
+                       heads: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """`quantize_act(o * torch.sigmoid(gate))` in one launch (braid/model/attention.py:215-216).
+
+    `o` is `[..., H*D]`.  `gate` is either a dense tensor of the same shape or the
+    strided per-head view `[..., H, D]` the attention layer gets from
+    `qg.view(B, T, H, 2*D).chunk(2, dim=-1)` (braid/model/attention.py:177), which
+    is read in place — no `reshape` copy.
+    """
+    _check_cuda(o, "sigmoid_gate_quant")
+    if _quantizers_off():
+        return _torch_quantize(o * torch.sigmoid(gate.reshape(o.shape)))
+    lib = _require_lib()
+    code = _DTYPE_CODE.get(o.dtype)
+    if code is None or gate.dtype != o.dtype:
+        raise ValueError("o and gate must share one of fp32, bf16, fp16")
+    cols = o.shape[-1]
+    o2 = _as_rows(o, cols)
+    rows = o2.shape[0]
+    if gate.dim() == o.dim() + 1 and gate.shape[-1] * gate.shape[-2] == cols:
+        # [..., H, D] view: rows must be uniformly strided, D contiguous
+        D = gate.shape[-1]
+        g3 = gate.reshape(rows, gate.shape[-2], D) if gate.is_contiguous() else \
+            _rows_view_3d(gate, rows)
+        if g3.stride(2) != 1:
+            g3 = g3.contiguous()
+        ld_gate, chunk, chunk_stride, gptr = g3.stride(0), D, g3.stride(1), g3.data_ptr()
+        keep = g3
+    else:
+        if gate.shape != o.shape:
+            raise ValueError(f"gate shape {tuple(gate.shape)} does not match o {tuple(o.shape)}")
+        g2 = _as_rows(gate, cols)
+        ld_gate, chunk, chunk_stride, gptr = g2.stride(0), cols, 0, g2.data_ptr()
+        keep = g2
+    q = torch.empty((rows, cols), dtype=FP8, device=o.device)
+    scale = torch.empty((1, 1), dtype=torch.float32, device=o.device)
+    rc = lib.bq_sigmoid_gate_quant(o2.data_ptr(), gptr, code, rows, cols, o2.stride(0), ld_gate,
+                                   chunk, chunk_stride, q.data_ptr(), scale.data_ptr(),
+                                   _take_slot(o.device), 16, _stream_ptr(o.device))
+    del keep
+    _lib.check(rc, "sigmoid_gate_quant")
+    return q.reshape(*o.shape[:-1], cols), scale
+
+
+def _as_rows(t: torch.Tensor, cols: int) -> torch.Tensor:
+    """A `[rows, cols]` view with a contiguous last axis and one row stride (copy if needed)."""
+    if t.dim() == 2 and t.stride(1) == 1:
+        return t
+    if t.is_contiguous():
+        return t.view(-1, cols)
+    try:
+        v = t.view(-1, cols)
+        if v.stride(1) == 1:
+            return v
+    except RuntimeError:
+        pass
+    return t.reshape(-1, cols).contiguous()
+
+
+def _rows_view_3d(g: torch.Tensor, rows: int) -> torch.Tensor:
+    try:
+        return g.view(rows, g.shape[-2], g.shape[-1])
+    except RuntimeError:
+        return g.reshape(rows, g.shape[-2], g.shape[-1])
+
+
+# ---------------------------------------------------------------------------
+# the GEMM
+# ---------------------------------------------------------------------------
+def _check_gemm_inputs(xq: torch.Tensor, sx: torch.Tensor) -> None:
+    _check_cuda(xq, "fp8_matmul")
+    if xq.dtype is not FP8 or xq.dim() != 2:
+        raise ValueError(f"xq must be a 2-D {FP8} tensor, got {xq.dtype} {tuple(xq.shape)}")
+    if sx.dtype is not torch.float32 or sx.numel() != 1 or not sx.is_cuda:
+        raise ValueError("sx must be a one-element fp32 CUDA tensor")
+
+
+def fp8_matmul(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight,
+               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The GEMM alone on an already-quantized `[M, K]` activation (braid/model/quant.py:232-241).
+
+    `(xq * sx) @ (w.data * w.scale)^T`, fp32 accumulation, `out_dtype` result.
+    """
+    return fp8_matmul_grouped(xq, sx, (w,), out_dtype=out_dtype)[0]
+
+
+def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8Weight],
+                       out_dtype: torch.dtype = torch.bfloat16,
+                       out: Sequence[torch.Tensor] | None = None) -> list[torch.Tensor]:
+    """Several weights against one quantized activation in ONE launch.
+
+    Each weight keeps its own scale, so every result equals the separate
+    `fp8_matmul` call bit for bit.  `out`, if given, holds one `[M, N_i]` tensor
+    per weight (last axis contiguous; column blocks of a wider buffer are fine).
+    More than 8 weights are split over several launches.
+    """
+    _check_gemm_inputs(xq, sx)
+    lib = _require_lib()
+    code = _DTYPE_CODE.get(out_dtype)
+    if code is None:
+        raise ValueError(f"out_dtype must be fp32, bf16 or fp16, got {out_dtype}")
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    M, K = xq.shape
+    outs: list[torch.Tensor] = []
+    for i, w in enumerate(weights):
+        if not isinstance(w, FP8Weight):
+            raise TypeError("fp8_matmul_grouped takes FP8Weight operands")
+        if w.data.shape[1] != K:
+            raise ValueError(f"weight {i} has K={w.data.shape[1]}, activation has K={K}")
+        if not w.data.is_contiguous():
+            raise ValueError("FP8Weight.data must be contiguous [N, K]")
+        if out is not None:
+            y = out[i]
+            if y.shape != (M, w.data.shape[0]) or y.dtype != out_dtype or y.stride(1) != 1:
+                raise ValueError(f"out[{i}] must be [{M}, {w.data.shape[0]}] {out_dtype}")
+        else:
+            y = torch.empty((M, w.data.shape[0]), dtype=out_dtype, device=xq.device)
+        outs.append(y)
+    if M == 0:
+        return outs
+    stream = _stream_ptr(xq.device)
+    for lo in range(0, len(weights), _lib.BQ_MAX_SEGMENTS):
+        ws_, ys = weights[lo:lo + _lib.BQ_MAX_SEGMENTS], outs[lo:lo + _lib.BQ_MAX_SEGMENTS]
+        n = len(ws_)
+        wq = (ctypes.c_void_p * n)(*[w.data.data_ptr() for w in ws_])
+        sw = (ctypes.c_void_p * n)(*[w.scale.data_ptr() for w in ws_])
+        yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+        Ns = (ctypes.c_int64 * n)(*[w.data.shape[0] for w in ws_])
+        ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
+        rc = lib.bq_gemm_w8a8_grouped(xq.data_ptr(), sx.data_ptr(), M, K, n, wq, sw, yp, Ns, ld,
+                                      code, _take_slot(xq.device), 16, stream)
+        _lib.check(rc, "fp8_matmul")
+    return outs
+
+
+def fp8_linear(x: torch.Tensor, w: FP8Weight) -> torch.Tensor:
+    """`F.linear(x, w)` for a single call site; leading dims preserved (braid/model/quant.py:244-252)."""
+    *lead, K = x.shape
+    xq, sx = quantize_act(x.reshape(-1, K))
+    return fp8_matmul(xq, sx, w, out_dtype=x.dtype).reshape(*lead, w.shape[0])
+
+
+def linear(x: torch.Tensor, w: torch.Tensor | FP8Weight) -> torch.Tensor:
+    """Dispatch on the weight's type (braid/model/quant.py:255-257)."""
+    return fp8_linear(x, w) if isinstance(w, FP8Weight) else F.linear(x, w)
+
+
+def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.Tensor]:
+    """`F.linear(x, w)` for several projections that share one activation.
+
+    The activation is quantized once (braid/model/quant.py:260-286) and all FP8
+    weights of the call go through one grouped launch; weights left in bf16 take
+    `F.linear` untouched, so mixed sets (GDN's qkv/z with its bf16 a/b gates) work.
+    """
+    if not any(isinstance(w, FP8Weight) for w in weights):
+        return [F.linear(x, w) for w in weights]
+    *lead, K = x.shape
+    xq, sx = quantize_act(x.reshape(-1, K))
+    fp8 = [w for w in weights if isinstance(w, FP8Weight)]
+    ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
+    out = []
+    for w in weights:
+        if isinstance(w, FP8Weight):
+            out.append(next(ys).reshape(*lead, w.shape[0]))
+        else:
+            out.append(F.linear(x, w))
+    return out
+
+
+def maybe_quantize(w: torch.Tensor, enabled: bool) -> torch.Tensor | FP8Weight:
+    """Quantize if asked and if the shape allows it (braid/model/quant.py:289-298)."""
+    if not enabled or w.dim() != 2:
+        return w
+    N, K = w.shape
+    return w if (K % 16 or N % 16) else quantize_weight(w)
+
+
+# ---------------------------------------------------------------------------
+# fused sublayer tails (what the reference spells as separate bf16 kernels)
+# ---------------------------------------------------------------------------
+def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
+                down_proj: FP8Weight) -> torch.Tensor:
+    """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 4 launches.
+
+    quantize(x) -> one grouped GEMM writing gate|up into one `[M, 2I]` buffer ->
+    SiLU*mul fused into the quantization of h (h never written) -> down GEMM.
+    Result bit-identical to the reference's nine-plus-kernel sequence built from
+    the same primitives.
+    """
+    *lead, K = x.shape
+    xq, sx = quantize_act(x.reshape(-1, K))
+    M = xq.shape[0]
+    I = gate_proj.shape[0]
+    gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
+    fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype,
+                       out=(gu[:, :I], gu[:, I:]))
+    hq, sh = silu_mul_quant(gu[:, :I], gu[:, I:])
+    y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype)
+    return y.reshape(*lead, down_proj.shape[0])
+
+
+def gated_output_projection(o: torch.Tensor, gate: torch.Tensor, o_proj: FP8Weight) -> torch.Tensor:
+    """`linear(o * torch.sigmoid(gate), o_proj)` (braid/model/attention.py:215-216) in 2 launches."""
+    *lead, K = o.shape
+    oq, so = sigmoid_gate_quant(o, gate)
+    return fp8_matmul(oq.reshape(-1, K), so, o_proj, out_dtype=o.dtype).reshape(*lead, o_proj.shape[0])

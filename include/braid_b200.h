@@ -1,0 +1,184 @@
+/*
+ * braid_b200 — C ABI of the B200 (sm_100a) FP8 W8A8 projection path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void* so the header needs no CUDA include) and returns an int
+ * status (BQ_OK == 0).  Nothing here allocates device memory unless it says
+ * so: outputs and scratch are owned by the caller.  All launches go to the
+ * stream given; none of the calls synchronises the device, so they are legal
+ * inside a CUDA stream capture.  Scales are always read and written ON THE
+ * DEVICE through pointers — never passed by value — which is what keeps a
+ * captured graph valid when the activation changes between replays.
+ *
+ * Each declaration cites the interface of the reference engine
+ * (plind-junior/braid) that it stands in for, as path:line inside that project.
+ */
+#ifndef BRAID_B200_H_
+#define BRAID_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define BQ_OK 0
+#define BQ_ERR_BAD_ARG 1        /* null pointer, n <= 0, unknown dtype code           */
+#define BQ_ERR_UNSUPPORTED 2    /* shape/alignment the kernels do not take            */
+#define BQ_ERR_LAUNCH 3         /* the CUDA runtime refused the launch                */
+#define BQ_ERR_WORKSPACE 4      /* scratch pointer null, misaligned or too small      */
+#define BQ_ERR_DEVICE_WAIT 5    /* a bounded device-side wait ran out (see bq_read_device_status) */
+#define BQ_ERR_NO_DRIVER 6      /* cuTensorMapEncodeTiled could not be resolved       */
+#define BQ_ERR_TOO_LARGE 7      /* request exceeds a fixed capacity                   */
+
+/* ---- element type codes for activations / outputs ----------------------- */
+#define BQ_DTYPE_F32 0
+#define BQ_DTYPE_BF16 1
+#define BQ_DTYPE_F16 2
+
+/* Largest number of weights one grouped GEMM launch takes. */
+#define BQ_MAX_SEGMENTS 8
+
+/* Library version (major*100 + minor). */
+int bq_version(void);
+
+/* Human-readable text for a status code; never NULL. */
+const char* bq_status_string(int status);
+
+/*
+ * Bytes of zero-initialised scratch the quantizer entry points need.  The
+ * scratch holds the grid-level amax word, the two barrier counters and a
+ * sticky device status word.  It must be 16-byte aligned and zeroed ONCE by
+ * the caller (cudaMemset); the kernels return it to zero themselves, so one
+ * buffer serves any number of calls that are ordered on a stream.  Calls that
+ * may overlap on the GPU (different streams) need separate buffers.
+ */
+size_t bq_quant_workspace_bytes(void);
+
+/*
+ * Per-tensor dynamic FP8 (e4m3fn) quantization of a contiguous activation:
+ *     scale = max(amax(|x|) * (1/448), 1e-12)   (fp32; NaN propagates)
+ *     q     = e4m3_rne(clamp(x / scale, -448, 448))
+ * bit-identical to the reference's torch spelling run on a CUDA device.
+ * One launch: 128-bit loads, warp-shuffle + grid-level amax, single-pass cast.
+ *
+ * Replaces: braid/model/quant.py:209-229 (`quantize_act`), whose fused arm is
+ * `quantize_act_cuda` in braid/kernels/csrc/quant_act.cu:140-176 bound at
+ * braid/kernels/csrc/bindings.cpp:33.
+ *
+ *   x         device, `n` elements of `dtype` (BQ_DTYPE_*), contiguous
+ *   q_out     device, n bytes (e4m3fn codes)
+ *   scale_out device, one float (the dequant scale, shape [1,1] upstream)
+ *   ws        scratch, see bq_quant_workspace_bytes()
+ */
+int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out, float* scale_out,
+                    void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * SiLU(gate)*up fused into the quantizer: h = bf16(bf16(silu(gate)) * up) is
+ * formed in registers (double rounding exactly as the two torch kernels do),
+ * its amax reduced grid-wide, and only the e4m3 codes of h and the scale are
+ * written — h itself never touches memory.
+ *
+ * Replaces: braid/model/mlp.py:48-49 (`h = F.silu(gate) * up` followed by the
+ * `quantize_act` inside `linear(h, down_proj)`).
+ *
+ *   gate, up   device, [rows, cols] of `dtype` with row strides ld_gate / ld_up
+ *              (elements); cols must be a multiple of 8, rows 16-byte aligned
+ *   q_out      device, rows*cols bytes, contiguous [rows, cols]
+ */
+int bq_silu_mul_quant(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                      int64_t ld_gate, int64_t ld_up, void* q_out, float* scale_out,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * o * sigmoid(gate) fused into the quantizer, h = bf16(o * bf16(sigmoid(gate))).
+ * `gate` may be the strided per-head view the attention layer produces: element
+ * (r, c) lives at gate[r*ld_gate + (c / chunk)*chunk_stride + (c % chunk)], so
+ * the [q | gate] interleave of the q projection is read in place, no copy.
+ *
+ * Replaces: braid/model/attention.py:215-216 (`o = o * torch.sigmoid(gate)`
+ * followed by the `quantize_act` inside `linear(o, o_proj)`); the strided gate
+ * is the `chunk(2, dim=-1)` view of braid/model/attention.py:177-178.
+ *
+ *   o            device, [rows, cols], row stride ld_o (elements)
+ *   chunk        head_dim of the gate view (multiple of 8); pass cols for a dense gate
+ *   chunk_stride distance between consecutive heads of the gate (elements)
+ */
+int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                          int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride,
+                          void* q_out, float* scale_out, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Bytes of scratch the GEMM entry points need for a problem of this size
+ * (split-K partial sums when the cluster path is not used, plus a status word).
+ * May be 0 rows of partials; never less than 16.  Same zero-once contract as
+ * the quantizer scratch.
+ */
+size_t bq_gemm_workspace_bytes(int64_t M, int64_t N_total, int64_t K);
+
+/*
+ * Per-tensor W8A8 GEMM:  Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, fp32
+ * accumulation in tensor memory, scales applied in the epilogue, output cast
+ * to `out_dtype`.  Both operands are K-major, exactly the layout the reference
+ * keeps (`FP8Weight.data` is [N,K] row-major).  M <= 256 takes the
+ * weight-streaming kernel (weight rows on the MMA M side, batch on the N side,
+ * deterministic split-K over a thread-block cluster); larger M takes the
+ * persistent compute-bound kernel.
+ *
+ * Replaces: braid/model/quant.py:232-241 (`fp8_matmul`), i.e. the call
+ * `torch._scaled_mm(xq, w.data.t(), scale_a=sx, scale_b=w.scale, out_dtype=...)`.
+ *
+ *   xq   device, [M,K] e4m3fn codes, contiguous, 16-byte aligned, K % 16 == 0
+ *   wq   device, [N,K] e4m3fn codes, contiguous, 16-byte aligned, N % 16 == 0
+ *   sx   device, one float (activation dequant scale)
+ *   sw   device, one float (weight dequant scale)
+ *   y    device, [M,N] of out_dtype, row stride ldy elements (ldy >= N)
+ */
+int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* sw, void* y,
+                 int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                 void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Several projections of ONE quantized activation in a single launch: segment
+ * i computes Y_i[M,N_i] = (Xq . Wq_i^T) * sx * sw_i with its own weight scale,
+ * so results are bit-identical to n_seg separate bq_gemm_w8a8 calls.  The
+ * pointer arrays are HOST arrays of device pointers.
+ *
+ * Replaces: the per-weight loop of braid/model/quant.py:260-286 (`project`)
+ * and the gate/up pair of braid/model/mlp.py:44-47.
+ */
+int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
+                         const void* const* wq, const float* const* sw, void* const* y,
+                         const int64_t* N, const int64_t* ldy, int out_dtype,
+                         void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Copies the sticky device status word of a scratch buffer to the host
+ * (synchronises `stream`; never call during capture).  0 means every bounded
+ * device wait so far completed; otherwise BQ_ERR_DEVICE_WAIT.  The word is
+ * cleared by the call.
+ */
+int bq_read_device_status(void* ws, void* stream, int* status_out);
+
+/*
+ * Tuning hooks used by the benchmark and tests; not needed for normal use.
+ * bq_set_option("decode_split_k", v)   0 = heuristic, else force a cluster size
+ * bq_set_option("decode_stages", v)    0 = heuristic, else force pipeline depth
+ * Returns BQ_ERR_BAD_ARG for an unknown key.
+ */
+int bq_set_option(const char* key, int64_t value);
+
+/*
+ * Describes the launch the last GEMM call on this thread chose:
+ * out[0]=kernel (0 decode, 1 prefill) out[1]=grid out[2]=cluster/split
+ * out[3]=stages out[4]=dynamic smem bytes out[5]=batch tile (MMA N)
+ */
+int bq_last_gemm_launch(int64_t out[6]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRAID_B200_H_ */
