@@ -452,7 +452,7 @@ int device_sms() {
   return sms[dev];
 }
 
-long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256;
+long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_slice_blocks = 8;
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -477,14 +477,17 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   p.mma_n = ((p.M + 15) / 16) * 16;
   const int b_tile = p.mma_n * kBK;
   const int stage_bytes = kATileBytes + b_tile;
-  // K slices: enough CTAs to cover the SMs, as a cluster of 1/2/4/8
-  int split = 1;
-  while (split < 8 && tiles * split < sms && split * 2 <= p.k_blocks) split *= 2;
-  if (g_opt_split > 0) {
-    split = (int)g_opt_split;
-    if (split > 8) split = 8;
-    while (split > p.k_blocks) --split;
-  }
+  // K slices per tile (= cluster size).  The slicing is a function of K alone,
+  // never of how many weights or rows share the launch: the fp32 summation order
+  // of an output element is then the same whether its weight is multiplied alone
+  // or grouped with others, which keeps `project` bit-identical to per-weight
+  // calls.  Target: slices of about g_opt_slice_blocks x 128 bytes of K.
+  (void)tiles;
+  int split = (int)((p.k_blocks + g_opt_slice_blocks / 2) / g_opt_slice_blocks);
+  if (split < 1) split = 1;
+  if (split > 8) split = 8;
+  if (g_opt_split > 0) split = (int)(g_opt_split > 8 ? 8 : g_opt_split);
+  while (split > p.k_blocks) --split;
   p.split = split;
   const int kb_max = (p.k_blocks + split - 1) / split;
   const int staging = p.mma_n * kRowTile * 4;
@@ -540,6 +543,11 @@ int gemm_set_option(const char* key, long long value);
 int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
+  if (strcmp(key, "decode_slice_blocks") == 0) {
+    if (value < 1) return kErrBadArg;
+    g_opt_slice_blocks = value;
+    return kOk;
+  }
   if (strcmp(key, "stream_max_m") == 0) {
     if (value < 1 || value > 256) return kErrBadArg;
     g_opt_stream_max_m = value;
@@ -561,6 +569,14 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
   if (ws == nullptr || ws_bytes < 16 || !aligned_to(ws, 16)) return kErrWorkspace;
   if (K % 16 || !aligned_to(xq, 16)) return kErrUnsupported;
   if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
+  const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
+  for (int i = 0; i < n_seg; ++i) {   // argument checks first: no CUDA call before they pass
+    if (!wq[i] || !sw[i] || !y[i] || N[i] <= 0) return kErrBadArg;
+    if (N[i] % 16 || ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(wq[i], 16) ||
+        !aligned_to(y[i], out_align))
+      return kErrUnsupported;
+    if (N[i] > 0x7fffff00LL) return kErrTooLarge;
+  }
   if (int rc = configure_once()) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
@@ -578,15 +594,9 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
 
   const bool stream_path = M <= g_opt_stream_max_m;
   const int w_box_rows = stream_path ? kRowTile : kTileN;
-  const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
   p.m_tiles = (int)((M + kRowTile - 1) / kRowTile);
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
-    if (!wq[i] || !sw[i] || !y[i] || N[i] <= 0) return kErrBadArg;
-    if (N[i] % 16 || ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(wq[i], 16) ||
-        !aligned_to(y[i], out_align))
-      return kErrUnsupported;
-    if (N[i] > 0x7fffff00LL) return kErrTooLarge;
     p.seg[i].sw = sw[i];
     p.seg[i].y = y[i];
     p.seg[i].ldy = ldy[i];

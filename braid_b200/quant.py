@@ -133,6 +133,12 @@ _SLOTS = 256
 _SLOT_BYTES = 64
 _scratch: dict[int, torch.Tensor] = {}
 _next_slot: dict[int, int] = {}
+_launches = 0      # kernels of this library launched (or captured) so far
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched or captured by this process."""
+    return _launches
 
 
 def warm_fused(enable: bool = True) -> bool:
@@ -208,6 +214,8 @@ def _scratch_for(device_index: int) -> torch.Tensor:
 
 def _take_slot(device: torch.device) -> int:
     """Device address of the next scratch slot of this device."""
+    global _launches
+    _launches += 1
     idx = device.index if device.index is not None else torch.cuda.current_device()
     buf = _scratch_for(idx)
     slot = _next_slot[idx]

@@ -1,0 +1,182 @@
+"""Per-projection sweeps: decode regime in GB/s (M = 1..128), prefill regime in TFLOP/s
+(M = 2048 / 8192 / a ragged 16-sequence pack), quantizer GB/s — each beside the library GEMM the
+reference calls (`torch._scaled_mm`) on the same GPU.  Run as `python bench.py --sweep`.
+
+Method (the reference's own, braid/bench/noise_floor.py:52-105 and braid/bench/gemm_paths.py:50-74):
+`inner` back-to-back calls captured in one CUDA graph, rotating through a bank of distinct weight
+copies sized past L2 (>= 1 GiB working set) so every call streams from HBM; median of `reps`
+replays timed with CUDA events; never a sync per call.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+from . import quant as Q
+
+PROJECTIONS = {
+    # name: (list of N per weight of one grouped launch, K)
+    "mlp.gate_up": ([12288, 12288], 4096),
+    "mlp.down": ([4096], 12288),
+    "gdn.in_proj_qkv_z": ([8192, 4096], 4096),
+    "gdn.out_proj": ([4096], 4096),
+    "attn.qkv": ([8192, 1024, 1024], 4096),
+    "attn.o_proj": ([4096], 4096),
+    "attn.k_proj": ([1024], 4096),
+}
+
+
+def _bank(ns, k, dev, min_bytes=1 << 30, max_copies=64):
+    per = sum(ns) * k
+    copies = max(2, min(max_copies, -(-min_bytes // per)))
+    g = torch.Generator(device=dev).manual_seed(0)
+    bank = []
+    for _ in range(copies):
+        ws = []
+        for n in ns:
+            data = torch.randint(0, 120, (n, k), generator=g, device=dev, dtype=torch.uint8).view(Q.FP8)
+            ws.append(Q.FP8Weight(data, torch.full((1, 1), 0.01, device=dev), (n, k)))
+        bank.append(ws)
+    return bank
+
+
+def _time_graph(fn_of_index, n_bank, inner, reps):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(min(n_bank, 3)):
+            fn_of_index(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(inner):
+            fn_of_index(i % n_bank)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) / inner)
+    return statistics.median(times)     # ms per call
+
+
+def gemm_row(name, ns, k, m, dev, peaks, inner=None, reps=15, library=True):
+    bank = _bank(ns, k, dev)
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    xq, sx = Q.quantize_act(x)
+    outs = [torch.empty((m, n), dtype=torch.bfloat16, device=dev) for n in ns]
+    flops = 2 * m * sum(ns) * k
+    bytes_ = sum(ns) * k + m * k + 2 * m * sum(ns)
+    if inner is None:
+        inner = max(4, min(64, int(2e9 // max(bytes_, flops // 2000))))
+    ms = _time_graph(lambda i: Q.fp8_matmul_grouped(xq, sx, bank[i], out=outs), len(bank), inner, reps)
+    launch = Q.last_gemm_launch()
+    row = {"proj": name, "M": m, "N": ns, "K": k, "us": ms * 1e3,
+           "gbs": bytes_ / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12,
+           "frac_hbm": bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "launch": launch}
+    if library:
+        def lib(i):
+            for w, o in zip(bank[i], outs):
+                torch._scaled_mm(xq, w.data.t(), scale_a=sx, scale_b=w.scale,
+                                 out_dtype=torch.bfloat16, out=o)
+        try:
+            ms_lib = _time_graph(lib, len(bank), inner, reps)
+            row.update({"lib_us": ms_lib * 1e3, "lib_gbs": bytes_ / (ms_lib * 1e-3) / 1e9,
+                        "lib_tflops": flops / (ms_lib * 1e-3) / 1e12, "speedup_vs_lib": ms_lib / ms})
+        except Exception as e:  # noqa: BLE001
+            row["lib_error"] = f"{type(e).__name__}: {str(e)[:100]}"
+    del bank
+    torch.cuda.empty_cache()
+    return row
+
+
+def quant_row(kind, m, cols, dev, peaks, reps=15):
+    n_bank = max(2, min(64, (256 << 20) // (m * cols * 2)))
+    if kind == "plain":
+        xs = [torch.randn(m, cols, device=dev).to(torch.bfloat16) for _ in range(n_bank)]
+        fn = lambda i: Q.quantize_act(xs[i])  # noqa: E731
+        bytes_ = 3 * m * cols
+    elif kind == "silu_mul":
+        xs = [torch.randn(m, 2 * cols, device=dev).to(torch.bfloat16) for _ in range(n_bank)]
+        fn = lambda i: Q.silu_mul_quant(xs[i][:, :cols], xs[i][:, cols:])  # noqa: E731
+        bytes_ = 5 * m * cols
+    else:
+        raise ValueError(kind)
+    inner = max(8, min(128, int(5e8 // bytes_)))
+    ms = _time_graph(fn, n_bank, inner, reps)
+    return {"quant": kind, "M": m, "cols": cols, "us": ms * 1e3,
+            "gbs": bytes_ / (ms * 1e-3) / 1e9, "frac_hbm": bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+
+def fp8_library_peak(dev, seconds=2.0):
+    """Dense FP8 peak the way the bf16 peak file was taken: `torch._scaled_mm` 8192^3, best of
+    10 (burst) and back to back for `seconds` (sustained)."""
+    n = 8192
+    a = torch.randn(n, n, device=dev).to(Q.FP8)
+    b = torch.randn(n, n, device=dev).to(Q.FP8)
+    one = torch.ones(1, 1, device=dev)
+    f = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
+    for _ in range(3):
+        f()
+    best = 1e9
+    for _ in range(10):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); f(); e.record(); torch.cuda.synchronize()
+        best = min(best, s.elapsed_time(e))
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = max(10, int(seconds * 1e3 / best))
+    s.record()
+    for _ in range(iters):
+        f()
+    e.record(); torch.cuda.synchronize()
+    sustained = s.elapsed_time(e) / iters
+    fl = 2 * n ** 3
+    return {"fp8_tflops_burst": fl / (best * 1e-3) / 1e12,
+            "fp8_tflops_sustained": fl / (sustained * 1e-3) / 1e12}
+
+
+def main(args):
+    import bench   # peaks reader lives with the benchmark
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Q.warm_fused(True)
+    peaks = bench.measured_peaks()
+    out_dir = Path("gpurun_out")
+    out_dir.mkdir(exist_ok=True)
+    rows = []
+    peak8 = fp8_library_peak(dev)
+    print(json.dumps({"fp8_peak": peak8}), flush=True)
+    for name, (ns, k) in PROJECTIONS.items():
+        for m in (1, 8, 16, 32, 64, 128):
+            r = gemm_row(name, ns, k, m, dev, peaks)
+            rows.append(r)
+            print(json.dumps(r), flush=True)
+    g = torch.Generator().manual_seed(4)
+    ragged = int(torch.randint(64, 1025, (16,), generator=g).sum().item())
+    for name in ("mlp.gate_up", "mlp.down", "gdn.in_proj_qkv_z", "gdn.out_proj"):
+        ns, k = PROJECTIONS[name]
+        for m in (2048, 8192, ragged):
+            r = gemm_row(name, ns, k, m, dev, peaks, inner=4, reps=7)
+            r["frac_fp8_burst"] = r["tflops"] / peak8["fp8_tflops_burst"]
+            r["frac_fp8_nominal"] = r["tflops"] / 4500.0
+            rows.append(r)
+            print(json.dumps(r), flush=True)
+    for m, cols in ((1, 4096), (16, 4096), (128, 4096), (128, 12288), (8192, 4096)):
+        r = quant_row("plain", m, cols, dev, peaks)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+    for m in (16, 128, 2048):
+        r = quant_row("silu_mul", m, 12288, dev, peaks)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+    (out_dir / "sweep.json").write_text(json.dumps({"fp8_peak": peak8, "rows": rows}, indent=1))
+    print(json.dumps({"device_status": Q.device_status()}), flush=True)

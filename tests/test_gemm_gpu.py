@@ -1,0 +1,266 @@
+"""The tcgen05 W8A8 GEMM against the CPU oracle (exact dequantize-and-multiply), the library GEMM
+the reference calls (`torch._scaled_mm`), the golden vectors, and its own structural properties:
+determinism, split-K invariance within tolerance, grouped == separate, untouched canaries.
+
+Tolerance (BASELINE): max|y - ref| / max|ref| <= 1e-2 on bf16 outputs against an fp32
+dequant-matmul; fp32 outputs are held to 1e-4."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from oracle import torch_spelling as TS
+from _util import codes_np, config1_inputs, from_bits16, from_bits32, max_rel, randn_cpu
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2
+TOL_F32 = 1e-4
+
+
+def _operands(Q, M, N, K, seed=0):
+    x = randn_cpu((M, K), seed=seed).cuda()
+    w = randn_cpu((N, K), seed=seed + 1, scale=0.02).cuda()
+    fw = Q.quantize_weight(w)
+    xq, sx = Q.quantize_act(x)
+    return x, w, xq, sx, fw
+
+
+def _oracle(xq, sx, fw):
+    return torch.from_numpy(oracle.gemm(codes_np(xq), codes_np(fw.data), sx.item(), fw.scale.item()))
+
+
+@pytest.mark.parametrize("M", [1, 7, 8, 16, 37, 128, 200, 256])
+@pytest.mark.parametrize("N,K", [(16, 16), (128, 128), (512, 256), (1040, 272), (4096, 4096)])
+def test_decode_regime_against_the_oracle(Q, M, N, K):
+    if N * K * M > 4096 * 4096 * 37 and M not in (37, 128):
+        pytest.skip("oracle time")
+    _, _, xq, sx, fw = _operands(Q, M, N, K, seed=M + N)
+    y = Q.fp8_matmul(xq, sx, fw)
+    assert y.shape == (M, N) and y.dtype is torch.bfloat16
+    ref = _oracle(xq, sx, fw)
+    assert max_rel(y.cpu(), ref) <= TOL_BF16
+    y32 = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+    assert max_rel(y32.cpu(), ref) <= TOL_F32
+    assert Q.last_gemm_launch()["kernel"] == "stream"
+
+
+@pytest.mark.parametrize("M,N,K", [(257, 256, 256), (512, 4096, 4096), (1000, 272, 4096),
+                                   (2048, 1024, 128), (2048, 4096, 4096), (4100, 512, 1040)])
+def test_prefill_regime_against_fp32_dequant_matmul(Q, M, N, K):
+    _, _, xq, sx, fw = _operands(Q, M, N, K, seed=M)
+    y = Q.fp8_matmul(xq, sx, fw)
+    assert Q.last_gemm_launch()["kernel"] == "tile"
+    ref = TS.dequant_matmul(xq, sx, fw.data, fw.scale)
+    assert max_rel(y, ref) <= TOL_BF16
+    y32 = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+    assert max_rel(y32, ref) <= TOL_F32
+    if M * N * K <= 512 * 4096 * 4096:
+        sub = slice(0, M, max(1, M // 16))
+        ref_o = torch.from_numpy(oracle.gemm(codes_np(xq[sub]), codes_np(fw.data),
+                                             sx.item(), fw.scale.item()))
+        assert max_rel(y32[sub].cpu(), ref_o) <= TOL_F32
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (128, 4096, 4096), (128, 1024, 4096),
+                                   (64, 4096, 12288), (2048, 4096, 4096)])
+def test_agrees_with_the_library_gemm_the_reference_calls(Q, M, N, K):
+    _, _, xq, sx, fw = _operands(Q, M, N, K, seed=3)
+    y = Q.fp8_matmul(xq, sx, fw)
+    ref = TS.scaled_mm(xq, sx, fw.data, fw.scale)
+    assert max_rel(y, ref) <= TOL_BF16
+    # both round the same fp32 sums to bf16: almost every element is bit-equal
+    assert (y != ref).float().mean().item() < 0.05
+
+
+def test_config_1_against_the_reference_cpu_output(Q, golden):
+    import hashlib
+    x, w = config1_inputs(0)
+    sha = lambda t: np.frombuffer(hashlib.sha256(t.view(torch.uint8).numpy().tobytes()).digest(), np.uint8)
+    if not (np.array_equal(sha(x), golden["c1_xsha"]) and np.array_equal(sha(w), golden["c1_wsha"])):
+        pytest.skip("this torch build draws different random numbers")
+    fw = Q.quantize_weight(w.cuda())
+    xq, sx = Q.quantize_act(x.cuda())
+    y = Q.fp8_matmul(xq, sx, fw)
+    ref = from_bits16(golden["c1_y"]).float()
+    assert max_rel(y.cpu().float(), ref) <= TOL_BF16
+    # end to end through the public call, as the reference's test does
+    y2 = Q.fp8_linear(x.cuda(), fw)
+    assert torch.equal(y, y2)
+
+
+def test_small_golden_gemm(Q, golden):
+    xq = torch.from_numpy(golden["gemm_xq"]).cuda().view(Q.FP8)
+    sx = from_bits32(golden["gemm_sx"]).cuda().reshape(1, 1)
+    for wq_key, sw_key, y_key in (("weight_q", "weight_scale", "gemm_ya"),
+                                  ("gemm_wbq", "gemm_wb_scale", "gemm_yb")):
+        wq = torch.from_numpy(golden[wq_key]).cuda().view(Q.FP8)
+        fw = Q.FP8Weight(data=wq, scale=from_bits32(golden[sw_key]).cuda().reshape(1, 1),
+                         shape=tuple(wq.shape))
+        y = Q.fp8_matmul(xq, sx, fw)
+        assert max_rel(y.cpu().float(), from_bits16(golden[y_key]).float()) <= TOL_BF16
+
+
+def test_run_to_run_determinism_and_split_k(Q):
+    _, _, xq, sx, fw = _operands(Q, 128, 4096, 4096, seed=8)
+    ref = TS.dequant_matmul(xq, sx, fw.data, fw.scale)
+    try:
+        for split in (1, 2, 4, 8):
+            Q.set_option("decode_split_k", split)
+            a = Q.fp8_matmul(xq, sx, fw)
+            assert Q.last_gemm_launch()["split"] == split
+            for _ in range(3):
+                assert torch.equal(a, Q.fp8_matmul(xq, sx, fw)), f"split {split} is not deterministic"
+            assert max_rel(a, ref) <= TOL_BF16
+    finally:
+        Q.set_option("decode_split_k", 0)
+
+
+def test_pipeline_depth_does_not_change_results(Q):
+    _, _, xq, sx, fw = _operands(Q, 16, 512, 4096, seed=9)
+    try:
+        Q.set_option("decode_split_k", 1)
+        base = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+        for stages in (1, 2, 3, 5):
+            Q.set_option("decode_stages", stages)
+            assert torch.equal(base, Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32))
+            assert Q.last_gemm_launch()["stages"] == stages
+    finally:
+        Q.set_option("decode_split_k", 0)
+        Q.set_option("decode_stages", 0)
+
+
+@pytest.mark.parametrize("M", [4, 128, 1024])
+def test_project_matches_linear_per_weight(Q, M):
+    """tests/test_quant.py:211-218 — grouped launch equals the separate calls bit for bit."""
+    x = randn_cpu((M, 256), seed=12).cuda()
+    qa = Q.quantize_weight(randn_cpu((512, 256), seed=13, scale=0.02).cuda())
+    qb = Q.quantize_weight(randn_cpu((128, 256), seed=14, scale=0.03).cuda())
+    qc = Q.quantize_weight(randn_cpu((272, 256), seed=15, scale=0.01).cuda())
+    got = Q.project(x, qa, qb, qc)
+    for g, w in zip(got, (qa, qb, qc)):
+        assert torch.equal(g, Q.fp8_linear(x, w))
+
+
+def test_project_leaves_bf16_weights_on_the_bf16_path(Q):
+    x = randn_cpu((4, 256), seed=16).cuda()
+    a = randn_cpu((512, 256), seed=17, scale=0.02).cuda()
+    b = randn_cpu((32, 256), seed=18, scale=0.02).cuda()
+    got_a, got_b = Q.project(x, Q.quantize_weight(a), b)
+    assert torch.equal(got_b, F.linear(x, b))
+    ga, gb = Q.project(x, a, b)
+    assert torch.equal(ga, F.linear(x, a)) and torch.equal(gb, F.linear(x, b))
+
+
+def test_leading_dims_and_dispatch(Q):
+    x = randn_cpu((2, 3, 256), seed=19).cuda()
+    w = randn_cpu((512, 256), seed=20, scale=0.02).cuda()
+    fw = Q.quantize_weight(w)
+    out = Q.fp8_linear(x, fw)
+    assert out.shape == (2, 3, 512) and out.dtype is torch.bfloat16
+    assert torch.equal(Q.linear(x, w), F.linear(x, w))
+    ref = F.linear(x, w)
+    rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
+    assert rel < 8e-2
+    assert F.cosine_similarity(out.float().flatten(), ref.float().flatten(), dim=0) > 0.99
+    (p,) = Q.project(x, fw)
+    assert p.shape == (2, 3, 512)
+
+
+def test_outputs_stay_inside_their_buffers(Q):
+    """Canary rows/columns around a strided output must survive (M and N off the tile grid)."""
+    for M, N, K in ((37, 272, 256), (300, 272, 256)):
+        _, _, xq, sx, fw = _operands(Q, M, N, K, seed=21)
+        big = torch.full((M + 2, N + 32), 7.0, device="cuda", dtype=torch.bfloat16)
+        out = big[1:M + 1, 16:16 + N]
+        Q.fp8_matmul_grouped(xq, sx, (fw,), out=(out,))
+        assert torch.equal(out, Q.fp8_matmul(xq, sx, fw))
+        mask = torch.ones_like(big, dtype=torch.bool)
+        mask[1:M + 1, 16:16 + N] = False
+        assert (big[mask] == 7.0).all()
+
+
+def test_scaling_the_activation_scale_scales_the_output(Q):
+    """Linearity at full decode size: doubling sx doubles every output exactly (power of two)."""
+    _, _, xq, sx, fw = _operands(Q, 128, 12288, 4096, seed=22)
+    y1 = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+    y2 = Q.fp8_matmul(xq, sx * 2, fw, out_dtype=torch.float32)
+    assert torch.equal(y2, y1 * 2)
+
+
+def test_fused_mlp_equals_the_unfused_sequence(Q):
+    """braid/model/mlp.py:44-49 spelled with separate kernels vs `mlp_forward` (4 launches)."""
+    M, H, I = 128, 4096, 12288
+    x = randn_cpu((M, H), seed=23).cuda()
+    wg = Q.quantize_weight(randn_cpu((I, H), seed=24, scale=0.02).cuda())
+    wu = Q.quantize_weight(randn_cpu((I, H), seed=25, scale=0.02).cuda())
+    wd = Q.quantize_weight(randn_cpu((H, I), seed=26, scale=0.02).cuda())
+    xq, sx = Q.quantize_act(x)
+    gate = Q.fp8_matmul(xq, sx, wg)
+    up = Q.fp8_matmul(xq, sx, wu)
+    h = F.silu(gate) * up
+    want = Q.linear(h, wd)
+    got = Q.mlp_forward(x, wg, wu, wd)
+    assert torch.equal(got, want)
+    # and it tracks the bf16 MLP the way the reference demands (tests/test_quant.py:157-178)
+    wgf, wuf, wdf = (w.data.float() * w.scale for w in (wg, wu, wd))
+    ref = F.linear(F.silu(F.linear(x.float(), wgf)) * F.linear(x.float(), wuf), wdf)
+    assert F.cosine_similarity(got.float().flatten(), ref.flatten(), dim=0) > 0.99
+
+
+def test_gated_output_projection(Q):
+    B, T, H, D = 4, 1, 16, 256
+    qg = randn_cpu((B, T, H * 2 * D), seed=27, scale=2.0).cuda()
+    o = randn_cpu((B, T, H * D), seed=28).cuda()
+    wo = Q.quantize_weight(randn_cpu((4096, H * D), seed=29, scale=0.02).cuda())
+    _, gate = qg.view(B, T, H, 2 * D).chunk(2, dim=-1)
+    want = Q.linear(o * torch.sigmoid(gate.reshape(B, T, H * D)), wo)
+    assert torch.equal(Q.gated_output_projection(o, gate, wo), want)
+
+
+def test_eager_equals_graph_replay(Q):
+    """tests/test_graph_quant.py:48-87 in miniature: capture quantize + grouped GEMM + fused MLP,
+    replay with new contents in the static input, compare with eager bit for bit."""
+    M, H, I = 16, 1024, 2048
+    wq_ = Q.quantize_weight(randn_cpu((2048, H), seed=30, scale=0.02).cuda())
+    wk_ = Q.quantize_weight(randn_cpu((256, H), seed=31, scale=0.02).cuda())
+    wg = Q.quantize_weight(randn_cpu((I, H), seed=32, scale=0.02).cuda())
+    wu = Q.quantize_weight(randn_cpu((I, H), seed=33, scale=0.02).cuda())
+    wd = Q.quantize_weight(randn_cpu((H, I), seed=34, scale=0.02).cuda())
+
+    def step(x):
+        q, k = Q.project(x, wq_, wk_)
+        return q[:, :H] + Q.mlp_forward(x + k.sum(dim=1, keepdim=True) * 0, wg, wu, wd)
+
+    static_x = randn_cpu((M, H), seed=35).cuda()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step(static_x)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_y = step(static_x)
+    for seed in (36, 37):
+        new = randn_cpu((M, H), seed=seed, scale=float(seed - 34)).cuda()
+        eager = step(new).clone()
+        static_x.copy_(new)
+        graph.replay()
+        assert torch.equal(static_y, eager)
+    assert Q.device_status() == 0
+
+
+def test_shape_guards(Q):
+    with pytest.raises(ValueError, match="multiples of 16"):
+        Q.quantize_weight(torch.randn(30, 256, device="cuda", dtype=torch.bfloat16))
+    w = torch.randn(512, 250, device="cuda", dtype=torch.bfloat16)
+    assert Q.maybe_quantize(w, True) is w
+    _, _, xq, sx, fw = _operands(Q, 4, 64, 128, seed=40)
+    bad = Q.FP8Weight(data=fw.data[:, :64].contiguous(), scale=fw.scale, shape=(64, 64))
+    with pytest.raises(ValueError):
+        Q.fp8_matmul(xq, sx, bad)
+    assert Q.device_status() == 0

@@ -1,0 +1,147 @@
+"""Host-side logic and the C-ABI surface, without a GPU: group parsing, shape guards, symbol
+export, argument validation that returns before any CUDA call, and the loud failure modes."""
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_group_names_round_trip():
+    from braid_b200.quant import GROUPS, parse_groups
+    assert parse_groups("") == frozenset()
+    assert parse_groups(None) == frozenset()
+    assert parse_groups("mlp") == {"mlp"}
+    assert parse_groups("mlp, attn") == {"mlp", "attn"}
+    assert parse_groups(["gdn", "head"]) == {"gdn", "head"}
+    assert parse_groups("all") == frozenset(GROUPS)
+
+
+def test_an_unknown_group_raises():
+    from braid_b200.quant import parse_groups
+    with pytest.raises(ValueError, match="unknown quant group"):
+        parse_groups("mpl")
+    with pytest.raises(ValueError, match="unknown quant group"):
+        parse_groups("mlp,attention")
+
+
+def test_public_names_match_the_reference_module():
+    """Everything other reference modules import from braid.model.quant exists here."""
+    from braid_b200 import quant
+    for name in ("GROUPS", "parse_groups", "FP8", "FP8_MAX", "EPS", "FP8Weight", "quantize_weight",
+                 "warm_fused", "fused_state", "quantize_act", "fp8_matmul", "fp8_linear", "linear",
+                 "project", "maybe_quantize", "_act_scale", "_weight_scale", "_CAST_CHUNK_BYTES"):
+        assert hasattr(quant, name), name
+    assert quant.FP8 is torch.float8_e4m3fn and quant.FP8_MAX == 448.0 and quant.EPS == 1e-12
+
+
+def test_weight_quantization_on_cpu_follows_the_reference_spelling(golden):
+    """Load-time work keeps the torch spelling; on a CPU it reproduces the golden weight exactly."""
+    from _util import from_bits16
+    from braid_b200.quant import FP8Weight, maybe_quantize, quantize_weight
+    import numpy as np
+    w = from_bits16(golden["weight_w"])
+    fw = quantize_weight(w)
+    assert isinstance(fw, FP8Weight) and fw.shape == (256, 128) and fw.nbytes == 256 * 128 + 4
+    assert fw.scale.shape == (1, 1) and fw.scale.dtype is torch.float32
+    assert np.array_equal(fw.data.view(torch.uint8).numpy(), golden["weight_q"])
+    assert int(fw.scale.view(torch.int32).item()) & 0xFFFFFFFF == int(golden["weight_scale"].reshape(-1)[0])
+    # banding invariance (tests/test_quant.py:81-96)
+    from braid_b200 import quant as Q
+    old = Q._CAST_CHUNK_BYTES
+    Q._CAST_CHUNK_BYTES = 128 * 4 * 3
+    try:
+        banded = quantize_weight(w)
+    finally:
+        Q._CAST_CHUNK_BYTES = old
+    assert torch.equal(banded.data.view(torch.uint8), fw.data.view(torch.uint8))
+    assert maybe_quantize(w, False) is w
+    z = quantize_weight(torch.zeros(64, 32, dtype=torch.bfloat16))
+    assert torch.isfinite(z.data.float()).all() and (z.scale > 0).all()
+    for a in (w, -w.abs(), w * 100):
+        assert torch.equal(Q._weight_scale(a), Q._act_scale(a))
+
+
+@pytest.mark.parametrize("shape", [(30, 256), (512, 250)])
+def test_shapes_the_gemm_cannot_take_are_refused(shape):
+    from braid_b200.quant import maybe_quantize, quantize_weight
+    w = torch.randn(*shape, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="multiples of 16"):
+        quantize_weight(w)
+    assert maybe_quantize(w, True) is w
+
+
+def test_the_library_exports_every_declared_symbol(lib):
+    """Each `bq_*` function declared in include/braid_b200.h resolves in the built library and has
+    a ctypes signature."""
+    from braid_b200 import _lib
+    header = (ROOT / "include" / "braid_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(bq_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.bq_version() >= 100
+    assert lib.bq_quant_workspace_bytes() == 16
+    assert lib.bq_gemm_workspace_bytes(128, 4096, 4096) >= 16
+
+
+def test_argument_validation_returns_before_any_cuda_call(lib):
+    from braid_b200 import _lib
+    assert lib.bq_quantize_act(None, 1, 8, None, None, None, 0, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_quantize_act(16, 9, 8, 16, 16, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_quantize_act(16, 1, 0, 16, 16, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_quantize_act(16, 1, 8, 16, 16, None, 0, None) == _lib.BQ_ERR_WORKSPACE
+    assert lib.bq_quantize_act(24, 1, 8, 16, 16, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_silu_mul_quant(16, 16, 1, 4, 12, 12, 12, 16, 16, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 1, 8, 64, 24, 64, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 1, 8, 60, 32, 64, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 7, 8, 64, 32, 64, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 1, 8, 64, 32, 64, None, 0, None) == _lib.BQ_ERR_WORKSPACE
+    assert lib.bq_set_option(b"no_such_option", 1) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_set_option(b"decode_split_k", 0) == _lib.BQ_OK
+    for code in range(0, 9):
+        assert _lib.status_string(code)
+    with pytest.raises(ValueError):
+        _lib.check(_lib.BQ_ERR_UNSUPPORTED, "x")
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.BQ_ERR_DEVICE_WAIT, "x")
+
+
+def test_a_missing_library_is_loud(monkeypatch, tmp_path):
+    from braid_b200 import _lib, quant
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libbraid_b200.so")
+    monkeypatch.setattr(quant, "_FUSED", None)
+    monkeypatch.setattr(quant, "_FUSED_STATE", "not tried")
+    with pytest.raises(_lib.LibraryMissing):
+        quant.warm_fused(True)
+    assert quant.fused_state().startswith("unavailable: LibraryMissing")
+
+
+def test_cpu_tensors_are_refused_not_emulated():
+    from braid_b200 import quant
+    x = torch.zeros(4, 16, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        quant.quantize_act(x)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        quant.silu_mul_quant(x, x)
+    fw = quant.quantize_weight(torch.randn(16, 16, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        quant.fp8_matmul(x.to(quant.FP8), torch.ones(1, 1), fw)
+    # weights left in bf16 never touch the kernels
+    w = torch.randn(8, 16, dtype=torch.bfloat16)
+    assert torch.equal(quant.project(x, w)[0], torch.nn.functional.linear(x, w))
+    assert torch.equal(quant.linear(x, w), torch.nn.functional.linear(x, w))
+
+
+def test_the_product_package_never_imports_the_oracle():
+    for path in (ROOT / "braid_b200").rglob("*.py"):
+        text = path.read_text()
+        assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), path

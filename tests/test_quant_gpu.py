@@ -1,0 +1,204 @@
+"""The sm_100a quantizer against the reference's torch spelling on the same device (bit identity),
+against the CPU oracle, and against the committed golden vectors.  Mirrors the reference's own
+gates (tests/test_quant.py:65-70, :146-152, :371-477) and widens them."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import torch_spelling as TS
+from _util import codes_np, f32_bits, from_bits16, randn_cpu, to_np_f32, u8
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.bfloat16, torch.float32, torch.float16]
+DT_IDS = ["bf16", "fp32", "fp16"]
+
+
+def _assert_same(q, s, qr, sr, what=""):
+    assert torch.equal(s, sr), f"{what} scale differs: {s.item():.9e} vs {sr.item():.9e}"
+    diff = int((u8(q) != u8(qr)).sum())
+    assert diff == 0, f"{what}: {diff} of {q.numel()} fp8 bytes differ"
+
+
+@pytest.mark.parametrize("dt", DTYPES, ids=DT_IDS)
+@pytest.mark.parametrize("shape", [(1, 4096), (8, 4096), (37, 12288), (128, 12288)],
+                         ids=["m1", "m8", "m37", "m128"])
+def test_bit_identical_to_the_torch_spelling(Q, dt, shape):
+    """The reference's own gate, same generator and seed (tests/test_quant.py:387-401)."""
+    g = torch.Generator(device="cuda").manual_seed(17)
+    x = (torch.randn(*shape, generator=g, device="cuda", dtype=torch.float32) * 3.5).to(dt)
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    assert q.dtype is Q.FP8 and q.shape == x.shape
+    assert s.shape == (1, 1) and s.dtype is torch.float32 and s.is_cuda
+    _assert_same(q, s, qr, sr, f"{dt} {shape}")
+
+
+@pytest.mark.parametrize("shape", [(1, 8), (1, 1), (3, 100), (5, 7), (16, 4096), (64, 4096),
+                                   (128, 4096), (333, 12288), (2048, 4096), (8192, 4096)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_ragged_small_and_streaming_sizes(Q, shape, dt):
+    """Tails that are not a multiple of 8, single-CTA grids, the register-held regime and the
+    streaming regime (8192x4096 = BASELINE's prefill activation)."""
+    x = randn_cpu(shape, seed=shape[0] * 31 + shape[1], dtype=dt, scale=2.0).cuda()
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    _assert_same(q, s, qr, sr, f"{dt} {shape}")
+
+
+@pytest.mark.parametrize("shape", [(8, 4096), (37, 12288)])
+def test_matches_the_cpu_oracle_with_the_cuda_scale_spelling(Q, shape):
+    x = randn_cpu(shape, seed=5, scale=3.5)
+    q, s = Q.quantize_act(x.cuda())
+    qo, so = oracle.quantize(to_np_f32(x), oracle.SCALE_RCP)
+    assert f32_bits(s) == int(np.float32(so).view(np.uint32))
+    assert np.array_equal(codes_np(q), qo)
+
+
+def test_every_bf16_value_through_the_cast(Q):
+    """All finite bf16 patterns with |x| <= 448: amax is 448, the scale exactly 1.0."""
+    bits = np.arange(65536, dtype=np.uint16)
+    x = from_bits16(bits)
+    keep = torch.isfinite(x.float()) & (x.float().abs() <= 448.0)
+    x = x[keep].contiguous().cuda()
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    _assert_same(q, s, qr, sr, "all bf16")
+    assert np.array_equal(codes_np(q), oracle.cast(to_np_f32(x), np.float32(s.item())))
+
+
+def test_golden_vectors_with_the_device_scale(Q, golden):
+    """Golden inputs from the reference's CPU run: codes must equal the oracle cast at the scale
+    the device computed, and the scale must be the CUDA spelling of the same amax."""
+    for key in ("act_bf16_8x4096", "act_bf16_1x4096"):
+        x = from_bits16(golden[key + "_x"])
+        q, s = Q.quantize_act(x.cuda())
+        want_s = oracle.scale_from_amax(oracle.amax(to_np_f32(x)), oracle.SCALE_RCP)
+        assert f32_bits(s) == int(want_s.view(np.uint32))
+        assert np.array_equal(codes_np(q), oracle.cast(to_np_f32(x), want_s))
+        if int(want_s.view(np.uint32)) == int(golden[key + "_scale"].reshape(-1)[0]):
+            assert np.array_equal(codes_np(q), golden[key + "_q"])
+
+
+def test_degenerate_scales(Q):
+    for label, fill in (("zeros", 0.0), ("huge", 60000.0), ("tiny", 1e-10)):
+        x = torch.full((4, 4096), fill, device="cuda", dtype=torch.bfloat16)
+        q, s = Q.quantize_act(x)
+        qr, sr = TS.quantize_act(x)
+        assert torch.isfinite(s).all(), f"{label}: scale not finite"
+        _assert_same(q, s, qr, sr, label)
+
+
+def test_full_range_is_used(Q):
+    x = torch.randn(16, 256, device="cuda", dtype=torch.bfloat16)
+    xq, sx = Q.quantize_act(x)
+    assert xq.dtype is Q.FP8 and sx.shape == (1, 1)
+    assert xq.float().abs().max().item() > Q.FP8_MAX * 0.5
+
+
+def test_non_contiguous_activation_takes_the_exact_torch_arm(Q):
+    base = randn_cpu((64, 4096), seed=5).cuda()
+    view = base.t()
+    assert not view.is_contiguous()
+    q, s = Q.quantize_act(view)
+    qc, sc = Q.quantize_act(view.contiguous())
+    _assert_same(q, s, qc, sc, "strided")
+
+
+def test_nan_survives(Q):
+    x = randn_cpu((4, 4096), seed=3).cuda()
+    x[2, 100] = float("nan")
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    assert torch.isnan(s).all() and torch.isnan(sr).all()
+    assert torch.equal(u8(q), u8(qr))
+
+
+def test_warm_fused_switch_selects_the_torch_arm(Q):
+    x = randn_cpu((8, 4096), seed=9).cuda()
+    fused = Q.quantize_act(x)
+    assert Q.fused_state() == "active"
+    Q.warm_fused(False)
+    try:
+        assert Q.fused_state() == "disabled by caller"
+        ref = Q.quantize_act(x)
+    finally:
+        Q.warm_fused(True)
+    _assert_same(*fused, *ref, "switch")
+
+
+def test_back_to_back_calls_leave_the_scratch_clean(Q):
+    """The barrier words return to zero: 600 calls (more than the slot pool) stay exact."""
+    x = randn_cpu((128, 4096), seed=1).cuda()
+    qr, sr = TS.quantize_act(x)
+    for _ in range(600):
+        q, s = Q.quantize_act(x)
+    _assert_same(q, s, qr, sr, "repeat")
+    assert Q.device_status() == 0
+
+
+# ---- prologues ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dt", DTYPES, ids=DT_IDS)
+@pytest.mark.parametrize("shape", [(1, 12288), (8, 12288), (37, 256), (128, 12288), (512, 12288)])
+def test_silu_mul_quant_is_bit_identical(Q, dt, shape):
+    gate = randn_cpu(shape, seed=41, dtype=dt, scale=2.0).cuda()
+    up = randn_cpu(shape, seed=42, dtype=dt, scale=1.5).cuda()
+    q, s = Q.silu_mul_quant(gate, up)
+    qr, sr = TS.quantize_act(TS.silu_mul(gate, up))
+    _assert_same(q, s, qr, sr, f"silu {dt} {shape}")
+
+
+def test_silu_mul_quant_reads_column_blocks_in_place(Q):
+    """gate and up as the two halves of one [M, 2I] buffer, the layout the grouped GEMM writes."""
+    M, I = 16, 1024
+    gu = randn_cpu((M, 2 * I), seed=43, scale=2.0).cuda()
+    q, s = Q.silu_mul_quant(gu[:, :I], gu[:, I:])
+    qr, sr = TS.quantize_act(TS.silu_mul(gu[:, :I].contiguous(), gu[:, I:].contiguous()))
+    _assert_same(q, s, qr, sr, "column blocks")
+
+
+@pytest.mark.parametrize("dt", DTYPES, ids=DT_IDS)
+def test_sigmoid_gate_quant_dense_and_per_head_view(Q, dt):
+    B, T, H, D = 2, 5, 16, 256
+    qg = randn_cpu((B, T, H * 2 * D), seed=44, dtype=dt, scale=2.0).cuda()
+    o = randn_cpu((B, T, H * D), seed=45, dtype=dt).cuda()
+    _, gate_v = qg.view(B, T, H, 2 * D).chunk(2, dim=-1)        # strided, as in the attention layer
+    gate_dense = gate_v.reshape(B, T, H * D)
+    qr, sr = TS.quantize_act(TS.sigmoid_gate(o, gate_dense))
+    q1, s1 = Q.sigmoid_gate_quant(o, gate_dense)
+    _assert_same(q1, s1, qr, sr, "dense gate")
+    q2, s2 = Q.sigmoid_gate_quant(o, gate_v)
+    _assert_same(q2, s2, qr, sr, "per-head view")
+    assert q2.shape == o.shape
+
+
+def test_prologues_against_the_golden_vectors(Q, golden):
+    """Inputs and outputs of the reference's CPU run.  The device evaluates expf with its own
+    library, so agreement with the CPU codes is near-total rather than exact; the bit-exact
+    arbiter is the torch-on-device comparison above."""
+    gate, up = from_bits16(golden["mlp_gate"]).cuda(), from_bits16(golden["mlp_up"]).cuda()
+    q, s = Q.silu_mul_quant(gate, up)
+    want = golden["mlp_hq"]
+    assert (codes_np(q) != want).mean() < 0.02
+    H, D = 4, 64
+    qg = from_bits16(golden["sig_qg"]).view(2, 3, H, 2 * D).cuda()
+    o = from_bits16(golden["sig_o"]).view(2, 3, H * D).cuda()
+    q, s = Q.sigmoid_gate_quant(o, qg[..., D:])
+    assert (codes_np(q).reshape(6, H * D) != golden["sig_oq"].reshape(6, H * D)).mean() < 0.02
+
+
+def test_bad_arguments_raise(Q):
+    with pytest.raises(ValueError):
+        Q.quantize_act(torch.zeros(4, 8, device="cuda", dtype=torch.int32))
+    with pytest.raises(ValueError):
+        Q.quantize_act(torch.zeros(0, 8, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        Q.quantize_act(torch.zeros(4, 8, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        Q.silu_mul_quant(torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16),
+                         torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16))
+    assert Q.device_status() == 0
