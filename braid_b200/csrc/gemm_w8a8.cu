@@ -52,7 +52,9 @@ struct Segment {
   void* y;             // device: output base of this segment
   long long ldy;       // row stride of y, elements
   int n;               // weight rows (output columns) of this segment
-  int tile_begin;      // index of the segment's first tile
+  int tile_begin;      // tile kernel: index of the segment's first tile
+  int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
+  int cluster_begin;   // stream kernel: index of the segment's first cluster
 };
 
 struct GemmParams {
@@ -62,7 +64,7 @@ struct GemmParams {
   int M;               // activation rows
   int mma_n;           // stream kernel: padded batch = MMA N (multiple of 16)
   int k_blocks;        // ceil(K / 128)
-  int split;           // stream kernel: K slices per tile = cluster size
+  int cluster;         // stream kernel: CTAs per cluster = largest split of the launch
   int stages;
   int out_dtype;
   int m_tiles;         // tile kernel: ceil(M / 128)
@@ -73,6 +75,22 @@ struct GemmParams {
 struct alignas(64) WeightMaps {
   CUtensorMap w[BQ_MAX_SEGMENTS];
 };
+
+#ifdef BQ_PHASES
+// Development aid (never compiled into the shipped library): nanosecond stamps of
+// the phases of every CTA of the stream kernel.
+__device__ unsigned long long g_phase_ts[8 * 2048];
+__device__ int g_dbg_mode = 0;   // 1: one MMA per k-block, 2: no MMA (timing experiments only)
+__device__ __forceinline__ void phase_stamp(int idx) {
+  if (threadIdx.x == 0 && blockIdx.x < 2048) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_phase_ts[blockIdx.x * 8 + idx] = t;
+  }
+}
+#else
+__device__ __forceinline__ void phase_stamp(int) {}
+#endif
 
 __device__ __forceinline__ int find_segment(const GemmParams& p, int tile) {
   int s = 0;
@@ -128,16 +146,28 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
 
+  phase_stamp(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int krank = (p.split > 1) ? static_cast<int>(cluster_ctarank()) : 0;
-  const int tile = blockIdx.x / p.split;
-  const int sg = find_segment(p, tile);
+  // A cluster of p.cluster CTAs works on p.cluster / split row tiles of one weight
+  // at a time: CTAs [g*split, (g+1)*split) of the cluster hold the K slices of
+  // tile g and reduce among themselves.
+  const int crank = (p.cluster > 1) ? static_cast<int>(cluster_ctarank()) : 0;
+  const int cluster_id = blockIdx.x / p.cluster;
+  int sg = 0;
+#pragma unroll
+  for (int i = 1; i < BQ_MAX_SEGMENTS; ++i)
+    if (i < p.n_seg && cluster_id >= p.seg[i].cluster_begin) sg = i;
   const Segment seg = p.seg[sg];
-  const int row0 = (tile - seg.tile_begin) * kRowTile;
+  const int split = seg.split;
+  const int group = crank / split;              // which tile of the cluster
+  const int krank = crank - group * split;      // which K slice of that tile
+  const int tile_in_seg = (cluster_id - seg.cluster_begin) * (p.cluster / split) + group;
+  const int row0 = tile_in_seg * kRowTile;
+  const bool active = row0 < seg.n;             // padding CTAs only keep the cluster barriers
 
   // this CTA's K slice, balanced to within one block
-  const int kb_base = p.k_blocks / p.split, kb_rem = p.k_blocks % p.split;
-  const int kb_count = kb_base + (krank < kb_rem ? 1 : 0);
+  const int kb_base = p.k_blocks / split, kb_rem = p.k_blocks % split;
+  const int kb_count = active ? kb_base + (krank < kb_rem ? 1 : 0) : 0;
   const int kb_begin = krank * kb_base + (krank < kb_rem ? krank : kb_rem);
 
   uint32_t tmem_cols = 32;
@@ -154,7 +184,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == 1 && active) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
     tmem_relinquish();
   }
@@ -162,6 +192,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  phase_stamp(1);
+
+  if (!active) {
+    // nothing to compute: match the two cluster barriers of the working CTAs
+    if (p.cluster > 1) { cluster_sync_all(); cluster_sync_all(); }
+    return;
+  }
 
   if (warp == 0) {
     if (elect_one()) {
@@ -194,6 +231,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         tc_fence_after();
         const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
         const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
+#ifdef BQ_PHASES
+        if (g_dbg_mode == 2) { mbar_arrive(empty_bar(s)); continue; }
+        if (g_dbg_mode == 1) {
+          mma_f8(tmem_base, da, db, idesc, i != 0 ? 1u : 0u);
+          mma_commit(empty_bar(s));
+          continue;
+        }
+#endif
 #pragma unroll
         for (int j = 0; j < kBK / kUmmaK; ++j) {
           // +32 bytes along K inside the swizzle span = +2 in descriptor units
@@ -209,6 +254,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
+  phase_stamp(2);
   if (!ok) *abort_flag = 1;
   __syncthreads();
   ok = (*abort_flag == 0);
@@ -227,12 +273,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     atomicExch(p.status, (unsigned int)kErrDeviceWait);
   }
   tc_fence_before();
-  if (p.split > 1) cluster_sync_all(); else __syncthreads();
+  phase_stamp(3);
+  if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
+  phase_stamp(4);
 
   // ---- reduce the K slices in rank order and write this CTA's share of rows --
   if (ok) {
     const float scale = __ldg(p.sx) * __ldg(seg.sw);
-    const int per = (p.M + p.split - 1) / p.split;
+    const int per = (p.M + split - 1) / split;
     const int m_begin = krank * per;
     const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
     const int n4 = lane * 4;                      // 4 consecutive output columns
@@ -240,10 +288,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     for (int m = m_begin + warp; m < m_end; m += 4) {
       const uint32_t off = smem_u32(part + m * kRowTile + n4);
       float4 acc;
-      if (p.split > 1) {
-        acc = ld_cluster_f4(map_to_cta(off, 0));
-        for (int r = 1; r < p.split; ++r) {
-          const float4 v = ld_cluster_f4(map_to_cta(off, r));
+      if (split > 1) {
+        const int peer0 = group * split;
+        acc = ld_cluster_f4(map_to_cta(off, peer0));
+        for (int r = 1; r < split; ++r) {
+          const float4 v = ld_cluster_f4(map_to_cta(off, peer0 + r));
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
       } else {
@@ -254,7 +303,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
   }
   // nobody leaves while a peer may still read its staging buffer
-  if (p.split > 1) cluster_sync_all(); else __syncthreads();
+  phase_stamp(5);
+  if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
+  phase_stamp(6);
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
@@ -452,7 +503,7 @@ int device_sms() {
   return sms[dev];
 }
 
-long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_slice_blocks = 8;
+long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -470,33 +521,59 @@ int configure_once() {
   return rc;
 }
 
-int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, int tiles,
+// K slices of one weight.  A function of the weight's own shape only -- never of
+// what else shares the launch or of the batch -- so an output element is summed
+// in the same order whether its weight is multiplied alone or grouped with
+// others (`project` stays bit-identical to per-weight calls).  Small weights
+// are sliced so that their tiles x slices cover most of the SMs.
+int split_for_weight(long long n_rows, int k_blocks) {
+  const long long tiles = (n_rows + kRowTile - 1) / kRowTile;
+  int s = 1;
+  while (s < 8 && tiles * (s * 2) <= g_opt_cta_target && (s * 2) * 2 <= k_blocks) s *= 2;
+  if (g_opt_split > 0) {
+    s = 1;
+    while (s * 2 <= g_opt_split && s < 8) s *= 2;
+    while (s > 1 && s > k_blocks) s /= 2;
+  }
+  return s;
+}
+
+int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p,
                   cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return kErrLaunch;
   p.mma_n = ((p.M + 15) / 16) * 16;
   const int b_tile = p.mma_n * kBK;
   const int stage_bytes = kATileBytes + b_tile;
-  // K slices per tile (= cluster size).  The slicing is a function of K alone,
-  // never of how many weights or rows share the launch: the fp32 summation order
-  // of an output element is then the same whether its weight is multiplied alone
-  // or grouped with others, which keeps `project` bit-identical to per-weight
-  // calls.  Target: slices of about g_opt_slice_blocks x 128 bytes of K.
-  (void)tiles;
-  int split = (int)((p.k_blocks + g_opt_slice_blocks / 2) / g_opt_slice_blocks);
-  if (split < 1) split = 1;
-  if (split > 8) split = 8;
-  if (g_opt_split > 0) split = (int)(g_opt_split > 8 ? 8 : g_opt_split);
-  while (split > p.k_blocks) --split;
-  p.split = split;
-  const int kb_max = (p.k_blocks + split - 1) / split;
+  int cluster = 1, min_split = 8;
+  for (int i = 0; i < p.n_seg; ++i) {
+    p.seg[i].split = split_for_weight(p.seg[i].n, p.k_blocks);
+    if (p.seg[i].split > cluster) cluster = p.seg[i].split;
+    if (p.seg[i].split < min_split) min_split = p.seg[i].split;
+  }
+  p.cluster = cluster;
+  int clusters = 0;
+  for (int i = 0; i < p.n_seg; ++i) {
+    const int tiles = (p.seg[i].n + kRowTile - 1) / kRowTile;
+    const int per_cluster = cluster / p.seg[i].split;
+    p.seg[i].cluster_begin = clusters;
+    clusters += (tiles + per_cluster - 1) / per_cluster;
+  }
+  const long long grid = (long long)clusters * cluster;
+  if (grid > 0x7fffffffLL) return kErrTooLarge;
+  const int kb_max = (p.k_blocks + min_split - 1) / min_split;
   const int staging = p.mma_n * kRowTile * 4;
-  // deep enough to keep ~100 KB in flight, but no deeper than the slice
-  int stages = (kMaxSmem - kBarrierBytes - 1024) / stage_bytes;
+  // Shared memory per CTA: small enough that the whole grid is resident at once
+  // (up to 3 CTAs per SM), so one CTA's epilogue overlaps its neighbours' loads.
+  int per_sm = (int)((grid + sms - 1) / sms);
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 3) per_sm = 3;
+  const int budget = kMaxSmem / per_sm - 1024 - kBarrierBytes - 1024;
+  int stages = budget / stage_bytes;
   if (stages > kb_max) stages = kb_max;
   if (stages > 24) stages = 24;
+  if (stages < 2) stages = kb_max < 2 ? kb_max : 2;
   if (g_opt_stages > 0 && g_opt_stages < stages) stages = (int)g_opt_stages;
-  if (stages < 1) return kErrUnsupported;
   p.stages = stages;
   int tile_bytes = stages * stage_bytes;
   if (tile_bytes < staging) tile_bytes = staging;
@@ -505,18 +582,18 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3(128, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  g_last_launch[0] = 0; g_last_launch[1] = tiles * split; g_last_launch[2] = split;
+  g_last_launch[0] = 0; g_last_launch[1] = grid; g_last_launch[2] = cluster;
   g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
@@ -543,9 +620,9 @@ int gemm_set_option(const char* key, long long value);
 int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
-  if (strcmp(key, "decode_slice_blocks") == 0) {
+  if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
-    g_opt_slice_blocks = value;
+    g_opt_cta_target = value;
     return kOk;
   }
   if (strcmp(key, "stream_max_m") == 0) {
@@ -613,7 +690,7 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    return launch_stream(tm_x, maps, p, tiles, stream);
+    return launch_stream(tm_x, maps, p, stream);
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
   return launch_tile(tm_x, maps, p, stream);
@@ -630,6 +707,16 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
   return bq_gemm_w8a8_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes,
                               stream);
 }
+
+#ifdef BQ_PHASES
+extern "C" int bq_debug_set_mode(int mode) {
+  return cudaMemcpyToSymbol(g_dbg_mode, &mode, sizeof(int)) == cudaSuccess ? 0 : 3;
+}
+extern "C" int bq_debug_read_phases(unsigned long long* out, int n_ctas) {
+  return cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(unsigned long long) * 8 * n_ctas) ==
+                 cudaSuccess ? 0 : 3;
+}
+#endif
 
 extern "C" int bq_last_gemm_launch(int64_t out[6]) {
   if (!out) return kErrBadArg;
