@@ -145,3 +145,27 @@ def test_the_product_package_never_imports_the_oracle():
     for path in (ROOT / "braid_b200").rglob("*.py"):
         text = path.read_text()
         assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), path
+
+
+def test_install_into_rebinds_a_reference_shaped_module():
+    """`install_into` on a stand-in with the reference's attribute names (no reference needed)."""
+    import sys
+    import types
+    from braid_b200 import quant
+    from braid_b200.integrate import adopt_weight, install_into
+    ref = types.ModuleType("fake_ref_quant")
+    for name in ("quantize_act", "fp8_matmul", "fp8_linear", "linear", "project", "warm_fused",
+                 "fused_state", "FP8Weight", "quantize_weight", "maybe_quantize"):
+        setattr(ref, name, object())
+    user = types.ModuleType("fake_ref_mlp")
+    user.fp8_matmul = user.quantize_act = object()
+    sys.modules["fake_ref_mlp"] = user
+    try:
+        done = install_into(ref, extra_modules=("fake_ref_mlp", "not.loaded"))
+    finally:
+        del sys.modules["fake_ref_mlp"]
+    assert ref.fp8_matmul is quant.fp8_matmul and ref.project is quant.project
+    assert user.fp8_matmul is quant.fp8_matmul and user.quantize_act is quant.quantize_act
+    assert "fake_ref_mlp.fp8_matmul" in done and ref._FUSED_STATE == "active"
+    w = quant.quantize_weight(torch.randn(16, 16, dtype=torch.bfloat16))
+    assert adopt_weight(w).data is w.data
