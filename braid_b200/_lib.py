@@ -30,6 +30,7 @@ SIGNATURES = {
     "bq_status_string": (ctypes.c_char_p, [_int]),
     "bq_quant_workspace_bytes": (_sz, []),
     "bq_quantize_act": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "bq_quantize_act_static": (_int, [_vp, _int, _i64, _vp, _vp, _vp]),
     "bq_silu_mul_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_sigmoid_gate_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64,
                                      _vp, _vp, _vp, _sz, _vp]),

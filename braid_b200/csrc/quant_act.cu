@@ -443,3 +443,76 @@ extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype,
   p.chunk_stride = chunk_stride;
   return dispatch_dtype<kSigmoidGate>(dtype, p, static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------
+// Quantizer entry point that needs no scratch buffer from the caller
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot hand it device memory of their own making:
+// a runtime that owns every byte of the GPU through its own arena and forbids
+// cudaMalloc after start-up, a plugin called from inside a region where the
+// host's allocator is locked or a real-time style loop with a no-allocation
+// rule, or a thin FFI shim in a language where creating and zeroing a device
+// buffer is more machinery than the call itself.
+// For them the 16 bytes of barrier words live in the library's own image.
+//
+// The array below is device memory reserved when the library is loaded on a
+// GPU and kept until the process exits (BQ_STATIC_SCRATCH_BYTES per GPU that
+// loads the library).  Inside host code its NAME is only a handle, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, asked
+// once per device with that device current, and cached.
+static __device__ __align__(256) unsigned int g_static_scratch[BQ_STATIC_SCRATCH_BYTES / 4];
+
+namespace {
+
+// Device address of g_static_scratch on the current device (0 on failure).
+QuantWs* static_scratch_for_current_device(int* rc_out) {
+  static QuantWs* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc_out = bq::kErrLaunch;
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      *rc_out = bq::kErrLaunch;
+      return nullptr;
+    }
+    cached[dev] = static_cast<QuantWs*>(ptr);
+  }
+  *rc_out = bq::kOk;
+  return cached[dev];
+}
+
+}  // namespace
+
+extern "C" int bq_quantize_act_static(const void* x, int dtype, int64_t n, void* q_out,
+                                      float* scale_out, void* stream) {
+  if (x == nullptr || q_out == nullptr || scale_out == nullptr || n <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (n > BQ_STATIC_MAX_ELEMENTS) return bq::kErrTooLarge;
+  if (!aligned_to(x, 16) || !aligned_to(q_out, 8)) return bq::kErrUnsupported;
+  int rc = bq::kOk;
+  QuantWs* ws = static_scratch_for_current_device(&rc);
+  if (ws == nullptr) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  The kernels return the
+  // amax word and the two counters to zero themselves, but a call that was cut
+  // short (a wait that ran out) would not have: clear the three words that must
+  // start at zero, in stream order, and leave the sticky status word alone.
+  if (cudaMemsetAsync(ws, 0, 3 * sizeof(unsigned int), s) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return bq::kErrLaunch;
+  }
+  QParams p{};
+  p.a = x;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = scale_out;
+  p.ws = ws;
+  p.n_groups = static_cast<unsigned int>(n / kGroup);
+  p.tail = static_cast<unsigned int>(n % kGroup);
+  p.groups_per_row = 1;
+  return dispatch_dtype<kPlain>(dtype, p, s);
+}

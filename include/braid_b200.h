@@ -77,6 +77,33 @@ int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out, float* sca
                     void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The same quantizer for callers that cannot give the library a scratch buffer.
+ * It has no counterpart in the reference; it exists for hosts that may not
+ * allocate device memory at the point of the call: runtimes that pre-carve the
+ * whole GPU into their own arena and forbid cudaMalloc afterwards, code that
+ * runs while the host's allocator is locked, control loops with a no-allocation
+ * rule, and FFI shims for which creating and zeroing a device buffer is the
+ * hard part.  The barrier words live in a fixed array of
+ * BQ_STATIC_SCRATCH_BYTES inside the library image (held by every GPU that
+ * loads the library, until the process exits).  The call allocates nothing and
+ * calls no allocating routine; inputs and outputs are still the caller's.
+ *
+ *  - Limit: n <= BQ_STATIC_MAX_ELEMENTS, otherwise BQ_ERR_TOO_LARGE and nothing
+ *    is launched.  Alignment rules as for bq_quantize_act.
+ *  - The first call on each device looks up the array's device address (once,
+ *    with that device current).  Make that first call before any stream capture.
+ *  - All calls on a device share the one array: calls that may overlap on the
+ *    GPU (different streams without ordering) race on it and give wrong scales.
+ *    Each call clears the words that must start at zero, in stream order.
+ *  - A bounded wait that runs out is recorded inside the array only; use
+ *    bq_quantize_act with your own scratch if you need to read that status.
+ */
+#define BQ_STATIC_SCRATCH_BYTES 256
+#define BQ_STATIC_MAX_ELEMENTS (INT64_C(1) << 28)
+int bq_quantize_act_static(const void* x, int dtype, int64_t n, void* q_out, float* scale_out,
+                           void* stream);
+
+/*
  * SiLU(gate)*up fused into the quantizer: h = bf16(bf16(silu(gate)) * up) is
  * formed in registers (double rounding exactly as the two torch kernels do),
  * its amax reduced grid-wide, and only the e4m3 codes of h and the scale are
