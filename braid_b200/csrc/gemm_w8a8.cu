@@ -147,6 +147,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   volatile uint32_t* const abort_flag = tmem_slot + 1;
 
   phase_stamp(0);
+  pdl_launch_dependents();   // the next kernel may start its own set-up right away
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A cluster of p.cluster CTAs works on p.cluster / split row tiles of one weight
   // at a time: CTAs [g*split, (g+1)*split) of the cluster hold the K slices of
@@ -206,9 +207,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       // every row tile: keep it in L2
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      for (int i = 0; i < kb_count; ++i) {
+      // Weights do not depend on any earlier kernel: fill the pipeline with them
+      // first, and only then wait for the kernel that produces the activation.
+      const int prefill = kb_count < p.stages ? kb_count : p.stages;
+      for (int i = 0; i < prefill; ++i) {
+        mbar_expect_tx(full_bar(i), kATileBytes + b_tile_bytes);
+        tma_load_2d(a_base + i * kATileBytes, &tm_w.w[sg], full_bar(i), (kb_begin + i) * kBK, row0,
+                    pol_w);
+      }
+      pdl_wait_prior_grids();
+      for (int i = 0; i < prefill; ++i)
+        tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
+      for (int i = prefill; i < kb_count; ++i) {
         const int s = i % p.stages, use = i / p.stages;
-        if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) {
+        if (!mbar_wait(empty_bar(s), (use - 1) & 1)) {
           *abort_flag = 1;
           break;
         }
@@ -252,6 +264,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   }
 
   // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
+  pdl_wait_prior_grids();   // scales are read and outputs written only after this
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
   phase_stamp(2);
@@ -285,21 +298,41 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
     const int n4 = lane * 4;                      // 4 consecutive output columns
     const bool col_ok = (row0 + n4) < seg.n;      // n is a multiple of 16
-    for (int m = m_begin + warp; m < m_end; m += 4) {
-      const uint32_t off = smem_u32(part + m * kRowTile + n4);
-      float4 acc;
+    const int peer0 = group * split;
+    for (int m = m_begin + warp; m < m_end; m += 8) {
+      // two output rows per pass, all partials requested before any is used
+      const bool two = (m + 4) < m_end;
+      float4 part0[8], part1[8];
+      const uint32_t off0 = smem_u32(part + m * kRowTile + n4);
+      const uint32_t off1 = off0 + 4u * kRowTile * 4u;
       if (split > 1) {
-        const int peer0 = group * split;
-        acc = ld_cluster_f4(map_to_cta(off, peer0));
-        for (int r = 1; r < split; ++r) {
-          const float4 v = ld_cluster_f4(map_to_cta(off, peer0 + r));
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < split) {
+            part0[r] = ld_cluster_f4(map_to_cta(off0, peer0 + r));
+            if (two) part1[r] = ld_cluster_f4(map_to_cta(off1, peer0 + r));
+          }
         }
       } else {
-        acc = *reinterpret_cast<const float4*>(part + m * kRowTile + n4);
+        part0[0] = *reinterpret_cast<const float4*>(part + m * kRowTile + n4);
+        if (two) part1[0] = *reinterpret_cast<const float4*>(part + (m + 4) * kRowTile + n4);
       }
-      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-      if (col_ok) store_out4(seg.y, (long long)m * seg.ldy + row0 + n4, p.out_dtype, acc);
+      float4 acc0 = part0[0], acc1 = part1[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) {
+        if (r < split) {     // fixed rank order: the sum does not depend on timing
+          acc0.x += part0[r].x; acc0.y += part0[r].y; acc0.z += part0[r].z; acc0.w += part0[r].w;
+          if (two) {
+            acc1.x += part1[r].x; acc1.y += part1[r].y; acc1.z += part1[r].z; acc1.w += part1[r].w;
+          }
+        }
+      }
+      acc0.x *= scale; acc0.y *= scale; acc0.z *= scale; acc0.w *= scale;
+      if (col_ok) store_out4(seg.y, (long long)m * seg.ldy + row0 + n4, p.out_dtype, acc0);
+      if (two) {
+        acc1.x *= scale; acc1.y *= scale; acc1.z *= scale; acc1.w *= scale;
+        if (col_ok) store_out4(seg.y, (long long)(m + 4) * seg.ldy + row0 + n4, p.out_dtype, acc1);
+      }
     }
   }
   // nobody leaves while a peer may still read its staging buffer
@@ -359,6 +392,8 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tm_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait_prior_grids();   // the activation codes and scales come from the previous kernel
 
   if (warp == 0) {
     if (elect_one()) {
@@ -504,6 +539,7 @@ int device_sms() {
 }
 
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
+long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -586,13 +622,15 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cfg.blockDim = dim3(128, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_opt_pdl ? 2 : 1;
   g_last_launch[0] = 0; g_last_launch[1] = grid; g_last_launch[2] = cluster;
   g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
@@ -607,8 +645,19 @@ int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, 
   int grid = p.total_tiles < sms ? p.total_tiles : sms;
   g_last_launch[0] = 1; g_last_launch[1] = grid; g_last_launch[2] = 1;
   g_last_launch[3] = kStagesBig; g_last_launch[4] = smem; g_last_launch[5] = kTileN;
-  gemm_tile_kernel<<<grid, kTileThreads, smem, stream>>>(tm_x, maps, p);
-  if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kTileThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tile_kernel, tm_x, maps, p);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
 }
 
@@ -620,6 +669,7 @@ int gemm_set_option(const char* key, long long value);
 int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
+  if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;

@@ -181,6 +181,18 @@ __host__ __device__ constexpr uint32_t idesc_e4m3(int mma_m, int mma_n) {
          (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
+// ---- programmatic dependent launch -------------------------------------------------
+// Lets the next kernel in the stream begin (its own set-up, loads that do not depend on
+// this kernel) before this one has finished.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Blocks until every kernel this one depends on has completed and its writes are visible.
+// A no-op when the kernel was launched without the programmatic attribute.
+__device__ __forceinline__ void pdl_wait_prior_grids() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- thread-block clusters ----------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -201,8 +213,7 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr)
-               : "memory");
+               : "r"(addr));
   return v;
 }
 __device__ __forceinline__ float ld_cluster_f1(uint32_t addr) {

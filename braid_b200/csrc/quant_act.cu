@@ -175,7 +175,9 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
 }
 
 // CTA-wide max, then the grid-wide exchange.  Returns the global amax to every
-// thread.  A single-CTA grid never touches global memory here.
+// thread.  A single-CTA grid never touches global memory here.  When it returns
+// true in *must_depart, thread 0 of the CTA owes the scratch a grid_depart()
+// call; that part is kept off the critical path on purpose.
 __device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
   __shared__ float s_warp[32];
   __shared__ float s_amax;
@@ -194,27 +196,25 @@ __device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
         s_amax = w;
       } else {
         // |x| >= 0 or NaN with the sign cleared: the unsigned order of the bit
-        // patterns is the order of the values, NaN on top.
+        // patterns is the order of the values, NaN on top.  The max is published
+        // first; the release on the counter orders it before the arrival.
         atomicMax(&ws->amax_bits, __float_as_uint(w));
-        __threadfence();
-        atomicAdd(&ws->arrive, 1u);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ws->arrive) : "memory");
+        // amax word and arrival counter sit in one aligned 8-byte pair: one
+        // acquire load sees both
+        unsigned int amax_bits = 0, arrived = 0;
         const long long t0 = clock64();
         bool ok = true;
-        while (ld_acquire_u32(&ws->arrive) < gridDim.x) {
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];"
+                       : "=r"(amax_bits), "=r"(arrived)
+                       : "l"(ws)
+                       : "memory");
+          if (arrived >= gridDim.x) break;
           if (clock64() - t0 > bq::kSpinLimitCycles) { ok = false; break; }
         }
         if (!ok) atomicExch(&ws->status, (unsigned int)bq::kErrDeviceWait);
-        s_amax = __uint_as_float(ld_acquire_u32(&ws->amax_bits));
-        __threadfence();
-        // the last CTA to have read the result returns the scratch to zero, so
-        // the next launch (and a graph replay) starts clean
-        const unsigned int old = atomicAdd(&ws->depart, 1u);
-        if (old == gridDim.x - 1) {
-          ws->amax_bits = 0u;
-          ws->arrive = 0u;
-          ws->depart = 0u;
-          __threadfence();
-        }
+        s_amax = __uint_as_float(amax_bits);
       }
     }
   }
@@ -222,24 +222,95 @@ __device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
   return s_amax;
 }
 
+// Called by thread 0 of every CTA of a multi-CTA grid after it has the global
+// amax: the last CTA to check out returns the scratch to zero, so the next
+// launch (and a graph replay) starts clean.
+__device__ __forceinline__ void grid_depart(QuantWs* ws) {
+  if (gridDim.x == 1 || threadIdx.x != 0) return;
+  const unsigned int old = atomicAdd(&ws->depart, 1u);
+  if (old == gridDim.x - 1) {
+    ws->amax_bits = 0u;
+    ws->arrive = 0u;
+    ws->depart = 0u;
+    __threadfence();
+  }
+}
+
 __device__ __forceinline__ float scale_from_amax(float amax) {
   const float raw = amax * kInvFp8Max;
   return (raw < kEps) ? kEps : raw;   // NaN compares false and stays NaN
 }
 
-// Hold variant: each thread keeps `p.held` (<= kMaxHeld) groups in registers
-// across the barrier, so the activation is read exactly once.
+// Raw operands of one group: one 8-pack for the plain mode, two for the prologues.
+template <typename T, int MODE> struct RawGroup {
+  Pack8<T> a;
+  Pack8<T> b;
+};
+
 template <typename T, int MODE>
+__device__ __forceinline__ void load_raw(const QParams& p, unsigned int g, Pack8<T>& a, Pack8<T>& b) {
+  if constexpr (MODE == kPlain) {
+    a = load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
+  } else {
+    const unsigned int row = g / p.groups_per_row;
+    const unsigned int col = (g - row * p.groups_per_row) * kGroup;
+    const T* pa = reinterpret_cast<const T*>(p.a) + static_cast<long long>(row) * p.ld_a + col;
+    const T* pb;
+    if constexpr (MODE == kSiluMul) {
+      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b + col;
+    } else {
+      const unsigned int head = col / p.chunk;
+      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
+           static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
+    }
+    a = load8(pa);
+    b = load8(pb);
+  }
+}
+
+// a <- the activation values (in place); plain mode is the identity.
+template <typename T, int MODE>
+__device__ __forceinline__ void apply_prologue(Pack8<T>& a, const Pack8<T>& b) {
+  if constexpr (MODE != kPlain) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (MODE == kSiluMul) {
+        // silu in fp32, rounded to T; product in fp32, rounded to T
+        const float x = widen(a.v[i]);
+        const T sl = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
+        a.v[i] = narrow<T>(widen(sl) * widen(b.v[i]));
+      } else {
+        const float gt = widen(b.v[i]);
+        const T sg = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
+        a.v[i] = narrow<T>(widen(a.v[i]) * widen(sg));
+      }
+    }
+  }
+}
+
+// Hold variant: each thread keeps `p.held` (<= MAXH) groups in registers across
+// the barrier, so the activation is read exactly once.  All loads of a thread
+// are issued before the first value is used.
+template <typename T, int MODE, int MAXH>
 __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
+  bq::pdl_launch_dependents();
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
-  Pack8<T> held[kMaxHeld];
+  Pack8<T> held[MAXH];
+  Pack8<T> other[MODE == kPlain ? 1 : MAXH];
+  bq::pdl_wait_prior_grids();   // the activation is the previous kernel's output
+#pragma unroll
+  for (int i = 0; i < MAXH; ++i) {
+    const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
+    if (i < p.held && g < p.n_groups)
+      load_raw<T, MODE>(p, g, held[i], other[MODE == kPlain ? 0 : i]);
+  }
   float m = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kMaxHeld; ++i) {
+  for (int i = 0; i < MAXH; ++i) {
     const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
     if (i < p.held && g < p.n_groups) {
-      held[i] = produce<T, MODE>(p, g);
+      apply_prologue<T, MODE>(held[i], other[MODE == kPlain ? 0 : i]);
       m = absmax8(held[i], m);
     }
   }
@@ -256,7 +327,7 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
   const float sc = scale_from_amax(grid_amax(m, p.ws));
   if (tid == 0) p.scale[0] = sc;
 #pragma unroll
-  for (int i = 0; i < kMaxHeld; ++i) {
+  for (int i = 0; i < MAXH; ++i) {
     const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
     if (i < p.held && g < p.n_groups) emit8(held[i], sc, p.q + static_cast<size_t>(g) * kGroup);
   }
@@ -265,14 +336,17 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
   }
+  grid_depart(p.ws);
 }
 
 // Streaming variant for activations that do not fit in the register file of
 // one co-resident grid: pass 1 reduces, pass 2 re-reads (L2) and casts.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
+  bq::pdl_launch_dependents();
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
+  bq::pdl_wait_prior_grids();
   float m = 0.0f;
   for (unsigned int g = tid; g < p.n_groups; g += nthreads) m = absmax8(produce<T, MODE>(p, g), m);
   const bool owns_tail = (MODE == kPlain) && p.tail != 0 && tid == nthreads - 1;
@@ -291,6 +365,7 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(src[i]), sc), __NV_SATFINITE, __NV_E4M3);
   }
+  grid_depart(p.ws);
 }
 
 struct DeviceInfo {
@@ -311,32 +386,51 @@ int device_sms() {
 
 long long g_opt_quant_block = 0;   // 0 = heuristic
 long long g_opt_quant_held = 0;    // 0 = heuristic
+long long g_opt_quant_pdl = 1;     // programmatic dependent launch on by default
+
+template <typename Kernel>
+int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3((unsigned)block, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_quant_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
+  return bq::kOk;
+}
 
 template <typename T, int MODE>
 int launch_quant(QParams p, cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return bq::kErrLaunch;
+  // registers a thread may spend on held values: 8 groups of a 16-bit type in
+  // the plain mode; half of that when two operands are staged or T is fp32
+  constexpr int kMaxH = (MODE == kPlain ? 8 : 4) / (sizeof(T) == 4 ? 2 : 1);
   const unsigned long long groups = p.n_groups;
-  // Spread over CTAs first (one group per thread), then deepen each thread up
-  // to kMaxHeld, then switch to the wide block; beyond that, stream.
-  int block = 256;
-  if (groups > (unsigned long long)sms * 256ull * kMaxHeld) block = 512;
+  // One group per thread while that covers the input with 256-thread CTAs on
+  // every SM; after that 512-thread CTAs, deepening each thread up to kMaxH;
+  // beyond that, stream.
+  int block = (groups > (unsigned long long)sms * 256ull) ? 512 : 256;
   if (g_opt_quant_block == 256 || g_opt_quant_block == 512) block = (int)g_opt_quant_block;
-  const unsigned long long cap = (unsigned long long)sms * block * kMaxHeld;
+  const unsigned long long cap = (unsigned long long)sms * block * kMaxH;
   if (groups <= cap) {
     int held = 1;
     while ((unsigned long long)sms * block * held < groups) ++held;
-    if (g_opt_quant_held >= held && g_opt_quant_held <= kMaxHeld) held = (int)g_opt_quant_held;
+    if (g_opt_quant_held >= held && g_opt_quant_held <= kMaxH) held = (int)g_opt_quant_held;
     unsigned long long per_cta = (unsigned long long)block * held;
     int grid = (int)((groups + per_cta - 1) / per_cta);
     if (grid < 1) grid = 1;
     p.held = held;
-    quant_hold_kernel<T, MODE><<<grid, block, 0, stream>>>(p);
-  } else {
-    p.held = 0;
-    quant_stream_kernel<T, MODE><<<2 * sms, 512, 0, stream>>>(p);
+    return launch_with_pdl(quant_hold_kernel<T, MODE, kMaxH>, grid, block, p, stream);
   }
-  return cudaGetLastError() == cudaSuccess ? bq::kOk : bq::kErrLaunch;
+  p.held = 0;
+  return launch_with_pdl(quant_stream_kernel<T, MODE>, 2 * sms, 512, p, stream);
 }
 
 template <int MODE>
@@ -369,6 +463,7 @@ int bq::quant_set_option(const char* key, long long value) {
   };
   if (eq(key, "quant_block")) { g_opt_quant_block = value; return kOk; }
   if (eq(key, "quant_held")) { g_opt_quant_held = value; return kOk; }
+  if (eq(key, "quant_pdl")) { g_opt_quant_pdl = value ? 1 : 0; return kOk; }
   return kErrBadArg;
 }
 
