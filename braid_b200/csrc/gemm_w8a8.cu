@@ -120,6 +120,61 @@ __device__ __forceinline__ void store_out4(void* y, long long idx, int out_dtype
   }
 }
 
+struct EpilogueArgs {
+  const float* part;       // this CTA's staging buffer [mma_n][128] fp32
+  uint32_t part_addr;      // its shared-memory address
+  int peer0;               // cluster rank of K slice 0 of this tile
+  int m_begin, m_end;      // output rows this CTA reduces and writes
+  int warp, lane;
+  int row0;                // first weight row (output column) of the tile
+  float scale;
+  bool col_ok;
+  void* y;
+  long long ldy;
+  int out_dtype;
+};
+
+// Sums the SPLIT partial tiles of this CTA's rows in rank order (fixed order:
+// the result does not depend on timing) and stores them.  Every thread asks
+// for all the partials of a batch of rows before it uses any of them, so the
+// remote shared-memory latency is paid once per batch, not once per load.
+template <int SPLIT>
+__device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
+  constexpr int kRows = 16 / SPLIT;          // rows in flight per thread
+  constexpr int kWarps = 8;
+  const int n4 = e.lane * 4;                 // 4 consecutive output columns
+  for (int m0 = e.m_begin + e.warp; m0 < e.m_end; m0 += kWarps * kRows) {
+    float4 v[kRows][SPLIT];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int m = m0 + i * kWarps;
+      if (m < e.m_end) {
+        const uint32_t off = e.part_addr + static_cast<uint32_t>(m * kRowTile + n4) * 4u;
+#pragma unroll
+        for (int r = 0; r < SPLIT; ++r) {
+          if constexpr (SPLIT == 1)
+            v[i][0] = *reinterpret_cast<const float4*>(e.part + m * kRowTile + n4);
+          else
+            v[i][r] = ld_cluster_f4(map_to_cta(off, e.peer0 + r));
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int m = m0 + i * kWarps;
+      if (m < e.m_end) {
+        float4 acc = v[i][0];
+#pragma unroll
+        for (int r = 1; r < SPLIT; ++r) {
+          acc.x += v[i][r].x; acc.y += v[i][r].y; acc.z += v[i][r].z; acc.w += v[i][r].w;
+        }
+        acc.x *= e.scale; acc.y *= e.scale; acc.z *= e.scale; acc.w *= e.scale;
+        if (e.col_ok) store_out4(e.y, (long long)m * e.ldy + e.row0 + n4, e.out_dtype, acc);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Weight-streaming kernel (swap-AB, cluster split-K)
 // ---------------------------------------------------------------------------
@@ -127,7 +182,7 @@ __device__ __forceinline__ void store_out4(void* y, long long idx, int out_dtype
 //   [stages x 16 KiB weight tiles][stages x (mma_n*128) activation tiles] ... [barrier block]
 // The tile area is reused after the main loop as the fp32 staging buffer
 // part[m][128] that the cluster reduction reads.
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(256, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ WeightMaps tm_w, const GemmParams p,
                    const int smem_tile_bytes) {
@@ -265,6 +320,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
   pdl_wait_prior_grids();   // scales are read and outputs written only after this
+  // the epilogue warps get here at once and have the scale ready long before
+  // the accumulator is
+  const float scale = __ldg(p.sx) * __ldg(seg.sw);
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
   phase_stamp(2);
@@ -273,9 +331,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   ok = (*abort_flag == 0);
   float* const part = reinterpret_cast<float*>(base_ptr);   // [mma_n][128]
   if (ok) {
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const int n_local = warp * 32 + lane;
-    for (int c = 0; c < p.mma_n; c += 16) {
+    // 8 warps: warp w reads TMEM lanes 32*(w%4).. (the only ones it may touch)
+    // and every other 16-column chunk, starting at chunk w/4
+    const int quad = warp & 3;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int n_local = quad * 32 + lane;
+    for (int c = (warp >> 2) * 16; c < p.mma_n; c += 32) {
       uint32_t r[16];
       tmem_ld16(lane_addr + c, r);
       tmem_ld_wait();
@@ -292,47 +353,23 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   // ---- reduce the K slices in rank order and write this CTA's share of rows --
   if (ok) {
-    const float scale = __ldg(p.sx) * __ldg(seg.sw);
     const int per = (p.M + split - 1) / split;
     const int m_begin = krank * per;
     const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
-    const int n4 = lane * 4;                      // 4 consecutive output columns
-    const bool col_ok = (row0 + n4) < seg.n;      // n is a multiple of 16
+#ifdef BQ_PHASES
+    const bool col_ok = (row0 + lane * 4) < seg.n && g_dbg_mode != 3;
+#else
+    const bool col_ok = (row0 + lane * 4) < seg.n;      // n is a multiple of 16
+#endif
+    const uint32_t part_addr = smem_u32(part);
     const int peer0 = group * split;
-    for (int m = m_begin + warp; m < m_end; m += 8) {
-      // two output rows per pass, all partials requested before any is used
-      const bool two = (m + 4) < m_end;
-      float4 part0[8], part1[8];
-      const uint32_t off0 = smem_u32(part + m * kRowTile + n4);
-      const uint32_t off1 = off0 + 4u * kRowTile * 4u;
-      if (split > 1) {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (r < split) {
-            part0[r] = ld_cluster_f4(map_to_cta(off0, peer0 + r));
-            if (two) part1[r] = ld_cluster_f4(map_to_cta(off1, peer0 + r));
-          }
-        }
-      } else {
-        part0[0] = *reinterpret_cast<const float4*>(part + m * kRowTile + n4);
-        if (two) part1[0] = *reinterpret_cast<const float4*>(part + (m + 4) * kRowTile + n4);
-      }
-      float4 acc0 = part0[0], acc1 = part1[0];
-#pragma unroll
-      for (int r = 1; r < 8; ++r) {
-        if (r < split) {     // fixed rank order: the sum does not depend on timing
-          acc0.x += part0[r].x; acc0.y += part0[r].y; acc0.z += part0[r].z; acc0.w += part0[r].w;
-          if (two) {
-            acc1.x += part1[r].x; acc1.y += part1[r].y; acc1.z += part1[r].z; acc1.w += part1[r].w;
-          }
-        }
-      }
-      acc0.x *= scale; acc0.y *= scale; acc0.z *= scale; acc0.w *= scale;
-      if (col_ok) store_out4(seg.y, (long long)m * seg.ldy + row0 + n4, p.out_dtype, acc0);
-      if (two) {
-        acc1.x *= scale; acc1.y *= scale; acc1.z *= scale; acc1.w *= scale;
-        if (col_ok) store_out4(seg.y, (long long)(m + 4) * seg.ldy + row0 + n4, p.out_dtype, acc1);
-      }
+    const EpilogueArgs ea{part, part_addr, peer0, m_begin, m_end, warp, lane, row0, scale, col_ok,
+                          seg.y, seg.ldy, p.out_dtype};
+    switch (split) {
+      case 1: reduce_store<1>(ea); break;
+      case 2: reduce_store<2>(ea); break;
+      case 4: reduce_store<4>(ea); break;
+      default: reduce_store<8>(ea); break;
     }
   }
   // nobody leaves while a peer may still read its staging buffer
@@ -600,10 +637,11 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   const int kb_max = (p.k_blocks + min_split - 1) / min_split;
   const int staging = p.mma_n * kRowTile * 4;
   // Shared memory per CTA: small enough that the whole grid is resident at once
-  // (up to 3 CTAs per SM), so one CTA's epilogue overlaps its neighbours' loads.
+  // (up to 2 CTAs per SM: 256 threads x ~128 registers each), so one CTA's
+  // epilogue overlaps its neighbour's loads.
   int per_sm = (int)((grid + sms - 1) / sms);
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 3) per_sm = 3;
+  if (per_sm > 2) per_sm = 2;
   const int budget = kMaxSmem / per_sm - 1024 - kBarrierBytes - 1024;
   int stages = budget / stage_bytes;
   if (stages > kb_max) stages = kb_max;
@@ -619,7 +657,7 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(128, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
