@@ -289,6 +289,9 @@ def main():
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
+        # NCCL's version banner goes to stdout and would precede the one JSON line
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         import torch.distributed as dist_mod
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
