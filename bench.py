@@ -299,6 +299,9 @@ def main():
     from braid_b200 import quant as Q
     from braid_b200.projection_set import ProjectionSet, StackShapes
     Q.warm_fused(True)
+    for kv in filter(None, os.environ.get("BQ_OPTIONS", "").split(",")):   # tuning experiments
+        k, v = kv.split("=")
+        Q.set_option(k, int(v))
     dev = torch.device("cuda", local)
     shapes = StackShapes()
     ps = ProjectionSet(shapes, args.rows, dev, seed=rank, layers=args.layers)

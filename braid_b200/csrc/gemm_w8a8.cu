@@ -70,6 +70,7 @@ struct GemmParams {
   int m_tiles;         // tile kernel: ceil(M / 128)
   int total_tiles;     // tile kernel
   unsigned int* status;
+  int seq;             // launch counter (development builds only)
 };
 
 struct alignas(64) WeightMaps {
@@ -80,6 +81,8 @@ struct alignas(64) WeightMaps {
 // Development aid (never compiled into the shipped library): nanosecond stamps of
 // the phases of every CTA of the stream kernel.
 __device__ unsigned long long g_phase_ts[8 * 2048];
+__device__ unsigned long long g_chain_ts[64 * 512 * 4];   // [launch % 64][cta < 512][start, accum, end, smid]
+__device__ unsigned int g_chain_seq = 0;
 __device__ int g_dbg_mode = 0;   // 1: one MMA per k-block, 2: no MMA (timing experiments only)
 __device__ __forceinline__ void phase_stamp(int idx) {
   if (threadIdx.x == 0 && blockIdx.x < 2048) {
@@ -88,8 +91,21 @@ __device__ __forceinline__ void phase_stamp(int idx) {
     g_phase_ts[blockIdx.x * 8 + idx] = t;
   }
 }
+__device__ __forceinline__ void chain_stamp(int seq, int idx) {
+  if (threadIdx.x == 0 && blockIdx.x < 512) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_chain_ts[((seq & 63) * 512 + blockIdx.x) * 4 + idx] = t;
+    if (idx == 0) {
+      unsigned int smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      g_chain_ts[((seq & 63) * 512 + blockIdx.x) * 4 + 3] = smid;
+    }
+  }
+}
 #else
 __device__ __forceinline__ void phase_stamp(int) {}
+__device__ __forceinline__ void chain_stamp(int, int) {}
 #endif
 
 __device__ __forceinline__ int find_segment(const GemmParams& p, int tile) {
@@ -202,6 +218,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   volatile uint32_t* const abort_flag = tmem_slot + 1;
 
   phase_stamp(0);
+  chain_stamp(p.seq, 0);
   pdl_launch_dependents();   // the next kernel may start its own set-up right away
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A cluster of p.cluster CTAs works on p.cluster / split row tiles of one weight
@@ -326,6 +343,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
   phase_stamp(2);
+  chain_stamp(p.seq, 1);
   if (!ok) *abort_flag = 1;
   __syncthreads();
   ok = (*abort_flag == 0);
@@ -376,6 +394,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   phase_stamp(5);
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
   phase_stamp(6);
+  chain_stamp(p.seq, 2);
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
@@ -577,6 +596,7 @@ int device_sms() {
 
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
+long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -642,7 +662,10 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   int per_sm = (int)((grid + sms - 1) / sms);
   if (per_sm < 1) per_sm = 1;
   if (per_sm > 2) per_sm = 2;
-  const int budget = kMaxSmem / per_sm - 1024 - kBarrierBytes - 1024;
+  int budget = kMaxSmem / per_sm - 1024 - kBarrierBytes - 1024;
+  // Leave room for the NEXT kernel's CTAs: with programmatic dependent launch they
+  // become resident while this kernel still runs and pre-load their weights.
+  if (g_opt_smem_cap > 0 && budget > g_opt_smem_cap) budget = (int)g_opt_smem_cap;
   int stages = budget / stage_bytes;
   if (stages > kb_max) stages = kb_max;
   if (stages > 24) stages = 24;
@@ -671,6 +694,10 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cfg.numAttrs = g_opt_pdl ? 2 : 1;
   g_last_launch[0] = 0; g_last_launch[1] = grid; g_last_launch[2] = cluster;
   g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
+#ifdef BQ_PHASES
+  static int launch_seq = 0;
+  p.seq = launch_seq++;
+#endif
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
@@ -708,6 +735,7 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
+  if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;
@@ -799,6 +827,10 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
 #ifdef BQ_PHASES
 extern "C" int bq_debug_set_mode(int mode) {
   return cudaMemcpyToSymbol(g_dbg_mode, &mode, sizeof(int)) == cudaSuccess ? 0 : 3;
+}
+extern "C" int bq_debug_read_chain(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_chain_ts, sizeof(unsigned long long) * 64 * 512 * 4) ==
+                 cudaSuccess ? 0 : 3;
 }
 extern "C" int bq_debug_read_phases(unsigned long long* out, int n_ctas) {
   return cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(unsigned long long) * 8 * n_ctas) ==
