@@ -40,6 +40,11 @@ SIGNATURES = {
                                     ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                     ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
                                     _vp, _sz, _vp]),
+    "bq_linear_w8a8_grouped": (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _i64,
+                                      _vp, _vp, _int,
+                                      ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                                      ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
+                                      _vp, _sz, _vp]),
     "bq_read_device_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "bq_set_option": (_int, [ctypes.c_char_p, _i64]),
     "bq_last_gemm_launch": (_int, [ctypes.POINTER(_i64)]),

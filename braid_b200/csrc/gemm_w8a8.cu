@@ -31,10 +31,13 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/braid_b200.h"
 #include "ptx.cuh"
+#include "quant_device.cuh"
 
 namespace {
 
@@ -57,6 +60,15 @@ struct Segment {
   int cluster_begin;   // stream kernel: index of the segment's first cluster
 };
 
+// The activation quantizer fused into the stream kernel (mode 0 = not fused: the
+// kernel then reads ready-made codes and a ready-made scale).
+struct FuseParams {
+  int mode;               // 0 off, 1 plain, 2 SiLU(a)*b, 3 a*sigmoid(b)
+  int dtype;              // BQ_DTYPE_* of the activation operands
+  bq::qd::QParams q;      // operands, addressing, codes out (q.q) and scale out (q.scale)
+  unsigned int* words;    // [0] amax bits [1] amax arrivals [2] codes arrivals [3] status [4] departures
+};
+
 struct GemmParams {
   Segment seg[BQ_MAX_SEGMENTS];
   int n_seg;
@@ -71,6 +83,7 @@ struct GemmParams {
   int total_tiles;     // tile kernel
   unsigned int* status;
   int seq;             // launch counter (development builds only)
+  FuseParams fuse;
 };
 
 struct alignas(64) WeightMaps {
@@ -191,6 +204,99 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
   }
 }
 
+constexpr int kQuantThreads = 192;   // warps 2..7 of the stream kernel
+
+__device__ __forceinline__ void quant_bar() {   // the six quantizer warps only
+  asm volatile("bar.sync 1, 192;" ::: "memory");
+}
+
+// Fused activation quantizer, run by warps 2..7 of EVERY CTA of the grid while the
+// producer warp is already streaming weights.  Two passes over the activation (the
+// second is served by L2): |x| max -> grid-wide exchange -> scale -> cast -> codes
+// to global memory -> arrival on the "codes are complete" counter the producers
+// poll before they issue the first activation-tile load.  Returns the global amax.
+template <typename T, int MODE>
+__device__ __forceinline__ float fused_quantize_t(const FuseParams& f, int qtid, float* s_red,
+                                                  unsigned int* status) {
+  using namespace bq::qd;
+  const unsigned int nq = gridDim.x * kQuantThreads;
+  const unsigned int q0 = blockIdx.x * kQuantThreads + qtid;
+  float m = 0.0f;
+  for (unsigned int g = q0; g < f.q.n_groups; g += nq) m = absmax8(produce<T, MODE>(f.q, g), m);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((qtid & 31) == 0) s_red[qtid >> 5] = m;
+  quant_bar();
+  if (qtid == 0) {
+    float w = s_red[0];
+#pragma unroll
+    for (int i = 1; i < kQuantThreads / 32; ++i) w = nan_max(w, s_red[i]);
+    if (gridDim.x > 1) {
+      atomicMax(&f.words[0], __float_as_uint(w));
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&f.words[1]) : "memory");
+      unsigned int amax_bits = 0, arrived = 0;
+      const long long t0 = clock64();
+      for (;;) {
+        asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(amax_bits), "=r"(arrived)
+                     : "l"(f.words)
+                     : "memory");
+        if (arrived >= gridDim.x) break;
+        if (clock64() - t0 > kSpinLimitCycles) {
+          atomicExch(status, (unsigned int)kErrDeviceWait);
+          break;
+        }
+      }
+      w = __uint_as_float(amax_bits);
+    }
+    s_red[6] = w;
+  }
+  quant_bar();
+  const float amax = s_red[6];
+  const float sc = scale_from_amax(amax);
+  for (unsigned int g = q0; g < f.q.n_groups; g += nq)
+    emit8(produce<T, MODE>(f.q, g), sc, f.q.q + static_cast<size_t>(g) * kGroup);
+  // codes were written through the generic proxy and will be read by TMA (async
+  // proxy) of other CTAs: device-scope fence, proxy fence, then the arrival
+  __threadfence();
+  asm volatile("fence.proxy.async;" ::: "memory");
+  quant_bar();
+  if (qtid == 0) {
+    if (blockIdx.x == 0) f.q.scale[0] = sc;
+    if (gridDim.x > 1)   // a single CTA hands over through shared memory and leaves the words alone
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&f.words[2]) : "memory");
+  }
+  return amax;
+}
+
+template <typename T>
+__device__ __forceinline__ float fused_quantize_m(const FuseParams& f, int qtid, float* s_red,
+                                                  unsigned int* status) {
+  switch (f.mode) {
+    case 1: return fused_quantize_t<T, bq::qd::kPlain>(f, qtid, s_red, status);
+    case 2: return fused_quantize_t<T, bq::qd::kSiluMul>(f, qtid, s_red, status);
+    default: return fused_quantize_t<T, bq::qd::kSigmoidGate>(f, qtid, s_red, status);
+  }
+}
+
+__device__ __noinline__ float fused_quantize(const FuseParams& f, int qtid, float* s_red,
+                                             unsigned int* status) {
+  switch (f.dtype) {
+    case BQ_DTYPE_F32: return fused_quantize_m<float>(f, qtid, s_red, status);
+    case BQ_DTYPE_F16: return fused_quantize_m<__half>(f, qtid, s_red, status);
+    default: return fused_quantize_m<__nv_bfloat16>(f, qtid, s_red, status);
+  }
+}
+
+// A CTA is done with the fused quantizer's counters: the last one out zeroes them.
+__device__ __forceinline__ void fused_depart(unsigned int* words) {
+  const unsigned int old = atomicAdd(&words[4], 1u);   // words[3] is the sticky status word
+  if (old == gridDim.x - 1) {
+    words[0] = 0u; words[1] = 0u; words[2] = 0u; words[4] = 0u;
+    __threadfence();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Weight-streaming kernel (swap-AB, cluster split-K)
 // ---------------------------------------------------------------------------
@@ -198,9 +304,9 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
 //   [stages x 16 KiB weight tiles][stages x (mma_n*128) activation tiles] ... [barrier block]
 // The tile area is reused after the main loop as the fp32 staging buffer
 // part[m][128] that the cluster reduction reads.
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
-                   const __grid_constant__ WeightMaps tm_w, const GemmParams p,
+                   const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p,
                    const int smem_tile_bytes) {
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -216,6 +322,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   volatile uint32_t* const tmem_slot =
       reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
+  float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // 8 floats
+  const bool fused = p.fuse.mode != 0;
 
   phase_stamp(0);
   chain_stamp(p.seq, 0);
@@ -255,6 +363,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
+    s_quant[7] = 0.0f;
     fence_mbar_init();
   }
   if (warp == 1 && active) {
@@ -268,7 +377,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   phase_stamp(1);
 
   if (!active) {
-    // nothing to compute: match the two cluster barriers of the working CTAs
+    // nothing to multiply; it still takes its share of the fused quantizer and
+    // matches the two cluster barriers of the working CTAs
+    if (fused && warp >= 2) {
+      pdl_wait_prior_grids();
+      fused_quantize(p.fuse, threadIdx.x - 64, s_quant, p.status);
+      if (threadIdx.x == 64 && gridDim.x > 1) fused_depart(p.fuse.words);
+    }
     if (p.cluster > 1) { cluster_sync_all(); cluster_sync_all(); }
     return;
   }
@@ -287,7 +402,29 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         tma_load_2d(a_base + i * kATileBytes, &tm_w.w[sg], full_bar(i), (kb_begin + i) * kBK, row0,
                     pol_w);
       }
-      pdl_wait_prior_grids();
+      if (fused) {
+        // the activation codes are being produced by the quantizer warps of the
+        // whole grid: wait (bounded) until every CTA has reported its share
+        if (gridDim.x > 1) {
+          const long long t0 = clock64();
+          for (;;) {
+            unsigned int done;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(&p.fuse.words[2]) : "memory");
+            if (done >= gridDim.x) break;
+            if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
+          }
+          fused_depart(p.fuse.words);
+        } else {
+          // single CTA: its own quantizer warps signal through shared memory
+          const long long t0 = clock64();
+          while (*reinterpret_cast<volatile float*>(s_quant + 7) == 0.0f) {
+            if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      } else {
+        pdl_wait_prior_grids();
+      }
       for (int i = 0; i < prefill; ++i)
         tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
       for (int i = prefill; i < kb_count; ++i) {
@@ -337,9 +474,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
   pdl_wait_prior_grids();   // scales are read and outputs written only after this
+  if (fused && warp >= 2) {
+    fused_quantize(p.fuse, threadIdx.x - 64, s_quant, p.status);
+    if (threadIdx.x == 64 && gridDim.x == 1) {
+      __threadfence_block();
+      *reinterpret_cast<volatile float*>(s_quant + 7) = 1.0f;   // single-CTA hand-off to the producer
+    }
+  }
   // the epilogue warps get here at once and have the scale ready long before
   // the accumulator is
-  const float scale = __ldg(p.sx) * __ldg(seg.sw);
+  const float sw = __ldg(seg.sw);
+  const float sx_ready = fused ? 0.0f : __ldg(p.sx);
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
   phase_stamp(2);
@@ -347,6 +492,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   if (!ok) *abort_flag = 1;
   __syncthreads();
   ok = (*abort_flag == 0);
+  const float scale = (fused ? bq::qd::scale_from_amax(s_quant[6]) : sx_ready) * sw;
   float* const part = reinterpret_cast<float*>(base_ptr);   // [mma_n][128]
   if (ok) {
     // 8 warps: warp w reads TMEM lanes 32*(w%4).. (the only ones it may touch)
@@ -614,6 +760,55 @@ int configure_once() {
   return rc;
 }
 
+// Largest grid of the stream kernel that is resident at once with this cluster
+// size and shared-memory footprint (the fused quantizer has grid-wide waits).
+int max_resident_ctas(int cluster, int smem) {
+  struct Entry { int cluster, smem, cap; };
+  static Entry cache[64];
+  static int n_cached = 0;
+  for (int i = 0; i < n_cached; ++i)
+    if (cache[i].cluster == cluster && cache[i].smem == smem) return cache[i].cap;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(cluster * 64), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_stream_kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    clusters = 0;
+  }
+  // The occupancy calculator reports one CTA per SM for this kernel even where two
+  // demonstrably run side by side (all 256 CTAs of a 100 KB launch start within 1.3 us of
+  // each other), so the per-SM count is derived from the resources themselves: shared
+  // memory (1 KB reserved per CTA), registers, and the two-CTA cap of the launch bounds.
+  cudaFuncAttributes fa;
+  memset(&fa, 0, sizeof(fa));
+  int regs = 128;
+  if (cudaFuncGetAttributes(&fa, gemm_stream_kernel) == cudaSuccess && fa.numRegs > 0)
+    regs = fa.numRegs;
+  else
+    (void)cudaGetLastError();
+  int per_sm = 233472 / (smem + 1024);
+  const int by_regs = 65536 / (((regs + 7) / 8) * 8 * 256);
+  if (per_sm > by_regs) per_sm = by_regs;
+  if (per_sm > 2) per_sm = 2;
+  if (per_sm < 1) per_sm = 1;
+  int cap = clusters * cluster * per_sm > 0 ? clusters * cluster * per_sm : -1;
+  if (getenv("BQ_DEBUG"))
+    fprintf(stderr, "[bq] residency: cluster %d smem %d regs %d -> %d clusters x %d per SM = %d CTAs\n",
+            cluster, smem, regs, clusters, per_sm, cap);
+  if (n_cached < 64) cache[n_cached++] = Entry{cluster, smem, cap};
+  return cap;
+}
+
 // K slices of one weight.  A function of the weight's own shape only -- never of
 // what else shares the launch or of the batch -- so an output element is summed
 // in the same order whether its weight is multiplied alone or grouped with
@@ -621,8 +816,10 @@ int configure_once() {
 // are sliced so that their tiles x slices cover most of the SMs.
 int split_for_weight(long long n_rows, int k_blocks) {
   const long long tiles = (n_rows + kRowTile - 1) / kRowTile;
+  // at most 4: clusters of 8 leave a fifth of the SMs unusable (15 clusters of 8 fit on the
+  // 148 SMs, against 33 clusters of 4)
   int s = 1;
-  while (s < 8 && tiles * (s * 2) <= g_opt_cta_target && (s * 2) * 2 <= k_blocks) s *= 2;
+  while (s < 4 && tiles * (s * 2) <= g_opt_cta_target && (s * 2) * 2 <= k_blocks) s *= 2;
   if (g_opt_split > 0) {
     s = 1;
     while (s * 2 <= g_opt_split && s < 8) s *= 2;
@@ -676,6 +873,14 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   if (tile_bytes < staging) tile_bytes = staging;
   const int smem = tile_bytes + kBarrierBytes + 1024;
   if (smem > kMaxSmem) return kErrUnsupported;
+  if (p.fuse.mode != 0) {
+    // the fused quantizer waits on the whole grid: every CTA must be resident
+    const int cap = max_resident_ctas(cluster, smem);
+    if (getenv("BQ_DEBUG"))
+      fprintf(stderr, "[bq] fused launch: grid %lld cluster %d smem %d resident cap %d\n", grid,
+              cluster, smem, cap);
+    if (cap <= 0 || grid > cap) return kErrUnsupported;
+  }
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -751,15 +956,17 @@ int bq::gemm_set_option(const char* key, long long value) {
 
 extern "C" size_t bq_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 16; }
 
-extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
-                                    const void* const* wq, const float* const* sw, void* const* y,
-                                    const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
-                                    size_t ws_bytes, void* stream_v) {
+namespace {
+
+int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
+                const void* const* wq, const float* const* sw, void* const* y, const int64_t* N,
+                const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
+                const FuseParams* fuse) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
     return kErrBadArg;
-  if (ws == nullptr || ws_bytes < 16 || !aligned_to(ws, 16)) return kErrWorkspace;
+  if (ws == nullptr || ws_bytes < (fuse ? 32u : 16u) || !aligned_to(ws, 16)) return kErrWorkspace;
   if (K % 16 || !aligned_to(xq, 16)) return kErrUnsupported;
   if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
   const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
@@ -770,6 +977,8 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
       return kErrUnsupported;
     if (N[i] > 0x7fffff00LL) return kErrTooLarge;
   }
+  const bool stream_path = M <= g_opt_stream_max_m;
+  if (fuse && !stream_path) return kErrUnsupported;   // the fused form exists for the decode regime
   if (int rc = configure_once()) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
@@ -784,8 +993,11 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
   p.out_dtype = out_dtype;
   // the sticky status word is the 4th word of the scratch, as in the quantizer
   p.status = static_cast<unsigned int*>(ws) + 3;
+  if (fuse) {
+    p.fuse = *fuse;
+    p.fuse.words = static_cast<unsigned int*>(ws);
+  }
 
-  const bool stream_path = M <= g_opt_stream_max_m;
   const int w_box_rows = stream_path ? kRowTile : kTileN;
   p.m_tiles = (int)((M + kRowTile - 1) / kRowTile);
   int tiles = 0;
@@ -810,6 +1022,57 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
   return launch_tile(tm_x, maps, p, stream);
+}
+
+}  // namespace
+
+extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
+                                    const void* const* wq, const float* const* sw, void* const* y,
+                                    const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
+                                    size_t ws_bytes, void* stream_v) {
+  return run_grouped(xq, sx, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v,
+                     nullptr);
+}
+
+extern "C" int bq_linear_w8a8_grouped(const void* a, const void* b, int mode, int act_dtype,
+                                      int64_t M, int64_t K, int64_t ld_a, int64_t ld_b,
+                                      int64_t chunk, int64_t chunk_stride, void* xq_out,
+                                      float* sx_out, int n_seg, const void* const* wq,
+                                      const float* const* sw, void* const* y, const int64_t* N,
+                                      const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes,
+                                      void* stream_v) {
+  if (!a || !xq_out || !sx_out || M <= 0 || K <= 0) return kErrBadArg;
+  if (mode < 1 || mode > 3 || (mode != 1 && !b)) return kErrBadArg;
+  if (act_dtype != BQ_DTYPE_F32 && act_dtype != BQ_DTYPE_BF16 && act_dtype != BQ_DTYPE_F16)
+    return kErrBadArg;
+  const size_t es = act_dtype == BQ_DTYPE_F32 ? 4 : 2;
+  if (K % 16 || !aligned_to(a, 16) || !aligned_to(xq_out, 16)) return kErrUnsupported;
+  if (mode == 1) {
+    if (ld_a != K) return kErrUnsupported;          // the plain form reads a dense [M, K]
+  } else {
+    if (ld_a < K || (ld_a * es) % 16 || (ld_b * es) % 16 || !aligned_to(b, 16)) return kErrUnsupported;
+    if (mode == 2 && ld_b < K) return kErrUnsupported;
+    if (mode == 3 && (chunk <= 0 || chunk % 8 || K % chunk || (chunk_stride * es) % 16))
+      return kErrUnsupported;
+  }
+  if (M * (K / 8) >= 0x7fffffffLL) return kErrTooLarge;
+  FuseParams f;
+  memset(&f, 0, sizeof(f));
+  f.mode = mode;
+  f.dtype = act_dtype;
+  f.q.a = a;
+  f.q.b = b;
+  f.q.q = static_cast<uint8_t*>(xq_out);
+  f.q.scale = sx_out;
+  f.q.n_groups = (unsigned int)(M * (K / 8));
+  f.q.tail = 0;
+  f.q.groups_per_row = (unsigned int)(K / 8);
+  f.q.ld_a = ld_a;
+  f.q.ld_b = ld_b;
+  f.q.chunk = (unsigned int)(mode == 3 ? chunk : K);
+  f.q.chunk_stride = chunk_stride;
+  return run_grouped(xq_out, sx_out, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes,
+                     stream_v, &f);
 }
 
 extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* sw,

@@ -32,16 +32,11 @@
 
 #include "../../include/braid_b200.h"
 #include "ptx.cuh"
+#include "quant_device.cuh"
 
 namespace {
 
-constexpr float kFp8Max = 448.0f;
-// torch divides a tensor by a host scalar as t * (1/scalar) in fp32.
-constexpr float kInvFp8Max = 1.0f / 448.0f;
-constexpr float kEps = 1e-12f;
-
-constexpr int kMaxHeld = 8;    // groups of 8 elements a thread may keep in registers
-constexpr int kGroup = 8;      // elements per group (one 128-bit load of a 16-bit type)
+using namespace bq::qd;
 
 // Scratch words shared by all quantizer kernels (16 bytes, zero between launches).
 struct QuantWs {
@@ -50,129 +45,6 @@ struct QuantWs {
   unsigned int depart;     // CTAs that consumed the global max
   unsigned int status;     // sticky: non-zero once a bounded wait ran out
 };
-
-enum Mode { kPlain = 0, kSiluMul = 1, kSigmoidGate = 2 };
-
-struct QParams {
-  const void* a;        // x | gate | o
-  const void* b;        // - | up   | gate
-  uint8_t* q;
-  float* scale;
-  QuantWs* ws;
-  unsigned int n_groups;      // full groups of 8
-  unsigned int tail;          // plain mode only: leftover elements (< 8)
-  unsigned int groups_per_row;
-  long long ld_a, ld_b;       // row strides in elements (prologue modes)
-  unsigned int chunk;         // sigmoid gate: head width of the strided gate view
-  long long chunk_stride;     // sigmoid gate: distance between heads
-  int held;                   // groups each thread keeps (hold kernel)
-};
-
-template <typename T> struct alignas(16) Pack8 { T v[8]; };
-template <> struct alignas(16) Pack8<float> { float v[8]; };
-
-__device__ __forceinline__ float widen(float v) { return v; }
-__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
-__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T narrow(float v);
-template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-
-// NaN-propagating max: once either side is NaN the result is NaN.
-__device__ __forceinline__ float nan_max(float m, float v) { return (v != v || v > m) ? v : m; }
-
-template <typename T>
-__device__ __forceinline__ Pack8<T> load8(const T* p) {
-  Pack8<T> r;
-  if constexpr (sizeof(T) == 4) {
-    const float4 lo = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    r.v[0] = lo.x; r.v[1] = lo.y; r.v[2] = lo.z; r.v[3] = lo.w;
-    r.v[4] = hi.x; r.v[5] = hi.y; r.v[6] = hi.z; r.v[7] = hi.w;
-  } else {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
-    *reinterpret_cast<uint4*>(&r) = raw;
-  }
-  return r;
-}
-
-// Builds the 8 activation values of group g for the given prologue.
-template <typename T, int MODE>
-__device__ __forceinline__ Pack8<T> produce(const QParams& p, unsigned int g) {
-  if constexpr (MODE == kPlain) {
-    return load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
-  } else {
-    const unsigned int row = g / p.groups_per_row;
-    const unsigned int col = (g - row * p.groups_per_row) * kGroup;
-    const T* pa = reinterpret_cast<const T*>(p.a) + static_cast<long long>(row) * p.ld_a + col;
-    const T* pb;
-    if constexpr (MODE == kSiluMul) {
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b + col;
-    } else {
-      const unsigned int head = col / p.chunk;
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
-           static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
-    }
-    const Pack8<T> a = load8(pa);
-    const Pack8<T> b = load8(pb);
-    Pack8<T> h;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if constexpr (MODE == kSiluMul) {
-        // silu in fp32, rounded to T; product in fp32, rounded to T
-        const float x = widen(a.v[i]);
-        const T s = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
-        h.v[i] = narrow<T>(widen(s) * widen(b.v[i]));
-      } else {
-        const float gt = widen(b.v[i]);
-        const T s = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
-        h.v[i] = narrow<T>(widen(a.v[i]) * widen(s));
-      }
-    }
-    return h;
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ float absmax8(const Pack8<T>& v, float m) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) m = nan_max(m, fabsf(widen(v.v[i])));
-  return m;
-}
-
-__device__ __forceinline__ float quant_one(float x, float sc) {
-  float v = __fdiv_rn(x, sc);
-  // comparison clamps: both are false for NaN, which therefore falls through
-  v = (v < -kFp8Max) ? -kFp8Max : ((v > kFp8Max) ? kFp8Max : v);
-  return v;
-}
-
-template <typename T>
-__device__ __forceinline__ void emit8(const Pack8<T>& v, float sc, uint8_t* dst) {
-  uint32_t w[2];
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int i = half * 4 + j * 2;
-      const float2 f = make_float2(quant_one(widen(v.v[i]), sc), quant_one(widen(v.v[i + 1]), sc));
-      const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
-      word |= (pair & 0xFFFFu) << (16 * j);
-    }
-    w[half] = word;
-  }
-  *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-}
-
-__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 // CTA-wide max, then the grid-wide exchange.  Returns the global amax to every
 // thread.  A single-CTA grid never touches global memory here.  When it returns
@@ -236,58 +108,6 @@ __device__ __forceinline__ void grid_depart(QuantWs* ws) {
   }
 }
 
-__device__ __forceinline__ float scale_from_amax(float amax) {
-  const float raw = amax * kInvFp8Max;
-  return (raw < kEps) ? kEps : raw;   // NaN compares false and stays NaN
-}
-
-// Raw operands of one group: one 8-pack for the plain mode, two for the prologues.
-template <typename T, int MODE> struct RawGroup {
-  Pack8<T> a;
-  Pack8<T> b;
-};
-
-template <typename T, int MODE>
-__device__ __forceinline__ void load_raw(const QParams& p, unsigned int g, Pack8<T>& a, Pack8<T>& b) {
-  if constexpr (MODE == kPlain) {
-    a = load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
-  } else {
-    const unsigned int row = g / p.groups_per_row;
-    const unsigned int col = (g - row * p.groups_per_row) * kGroup;
-    const T* pa = reinterpret_cast<const T*>(p.a) + static_cast<long long>(row) * p.ld_a + col;
-    const T* pb;
-    if constexpr (MODE == kSiluMul) {
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b + col;
-    } else {
-      const unsigned int head = col / p.chunk;
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
-           static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
-    }
-    a = load8(pa);
-    b = load8(pb);
-  }
-}
-
-// a <- the activation values (in place); plain mode is the identity.
-template <typename T, int MODE>
-__device__ __forceinline__ void apply_prologue(Pack8<T>& a, const Pack8<T>& b) {
-  if constexpr (MODE != kPlain) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if constexpr (MODE == kSiluMul) {
-        // silu in fp32, rounded to T; product in fp32, rounded to T
-        const float x = widen(a.v[i]);
-        const T sl = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
-        a.v[i] = narrow<T>(widen(sl) * widen(b.v[i]));
-      } else {
-        const float gt = widen(b.v[i]);
-        const T sg = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
-        a.v[i] = narrow<T>(widen(a.v[i]) * widen(sg));
-      }
-    }
-  }
-}
-
 // Hold variant: each thread keeps `p.held` (<= MAXH) groups in registers across
 // the barrier, so the activation is read exactly once.  All loads of a thread
 // are issued before the first value is used.
@@ -324,7 +144,7 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
       m = nan_max(m, fabsf(tail_v[i]));
     }
   }
-  const float sc = scale_from_amax(grid_amax(m, p.ws));
+  const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
   if (tid == 0) p.scale[0] = sc;
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) {
@@ -336,7 +156,7 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
   }
-  grid_depart(p.ws);
+  grid_depart(static_cast<QuantWs*>(p.ws));
 }
 
 // Streaming variant for activations that do not fit in the register file of
@@ -354,7 +174,7 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
     for (unsigned int i = 0; i < p.tail; ++i) m = nan_max(m, fabsf(widen(src[i])));
   }
-  const float sc = scale_from_amax(grid_amax(m, p.ws));
+  const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
   if (tid == 0) p.scale[0] = sc;
   // walk backwards: the groups read last in pass 1 are the likeliest still in L2
   for (long long g = (long long)p.n_groups - 1 - tid; g >= 0; g -= nthreads)
@@ -365,7 +185,7 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(src[i]), sc), __NV_SATFINITE, __NV_E4M3);
   }
-  grid_depart(p.ws);
+  grid_depart(static_cast<QuantWs*>(p.ws));
 }
 
 struct DeviceInfo {
@@ -427,6 +247,13 @@ int launch_quant(QParams p, cudaStream_t stream) {
     int grid = (int)((groups + per_cta - 1) / per_cta);
     if (grid < 1) grid = 1;
     p.held = held;
+    // The smallest instantiation that holds `held` groups: fewer registers per
+    // thread, so the next GEMM's CTAs fit on the SM beside a waiting quantizer CTA.
+    if (held <= 1) return launch_with_pdl(quant_hold_kernel<T, MODE, 1>, grid, block, p, stream);
+    if (held <= 2 && kMaxH >= 2)
+      return launch_with_pdl(quant_hold_kernel<T, MODE, (kMaxH >= 2 ? 2 : kMaxH)>, grid, block, p, stream);
+    if (held <= 4 && kMaxH >= 4)
+      return launch_with_pdl(quant_hold_kernel<T, MODE, (kMaxH >= 4 ? 4 : kMaxH)>, grid, block, p, stream);
     return launch_with_pdl(quant_hold_kernel<T, MODE, kMaxH>, grid, block, p, stream);
   }
   p.held = 0;
@@ -480,7 +307,7 @@ extern "C" int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out,
   p.a = x;
   p.q = static_cast<uint8_t*>(q_out);
   p.scale = scale_out;
-  p.ws = static_cast<QuantWs*>(ws);
+  p.ws = ws;
   p.n_groups = static_cast<unsigned int>(n / kGroup);
   p.tail = static_cast<unsigned int>(n % kGroup);
   p.groups_per_row = 1;
@@ -503,7 +330,7 @@ extern "C" int bq_silu_mul_quant(const void* gate, const void* up, int dtype, in
   p.b = up;
   p.q = static_cast<uint8_t*>(q_out);
   p.scale = scale_out;
-  p.ws = static_cast<QuantWs*>(ws);
+  p.ws = ws;
   p.groups_per_row = static_cast<unsigned int>(cols / kGroup);
   p.n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
   p.ld_a = ld_gate;
@@ -529,7 +356,7 @@ extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype,
   p.b = gate;
   p.q = static_cast<uint8_t*>(q_out);
   p.scale = scale_out;
-  p.ws = static_cast<QuantWs*>(ws);
+  p.ws = ws;
   p.groups_per_row = static_cast<unsigned int>(cols / kGroup);
   p.n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
   p.ld_a = ld_o;

@@ -469,10 +469,101 @@ def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8
     return outs
 
 
+_FUSE_LINEAR = False    # quantize-and-multiply in one launch: correct, but measured slower than
+                        # the two-launch form with programmatic dependent launch
+
+
+def set_fused_linear(enable: bool) -> None:
+    """Switch the one-launch quantize-and-multiply form on or off (results are identical)."""
+    global _FUSE_LINEAR
+    _FUSE_LINEAR = bool(enable)
+
+
+def linear_fused(a: torch.Tensor, weights: Sequence[FP8Weight], *, mode: str = "plain",
+                 b: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                 out: Sequence[torch.Tensor] | None = None):
+    """Quantization of the activation and the grouped GEMM in ONE launch (M <= 256).
+
+    mode "plain": activation `a` `[M, K]`; "silu_mul": `quantize(F.silu(a) * b)`;
+    "sigmoid_gate": `quantize(a * sigmoid(b))` with `b` dense or the per-head `[M, H, D]` view.
+    Returns `(outs, codes, scale)`, or `None` when the shape is not eligible (the caller then
+    uses the separate kernels, which give the same bits).
+    """
+    if not _FUSE_LINEAR or _quantizers_off() or not a.is_cuda or a.dim() != 2:
+        return None
+    M, K = a.shape
+    if M == 0 or M > 256 or K % 16:
+        return None
+    code_in = _DTYPE_CODE.get(a.dtype)
+    out_dtype = a.dtype if out_dtype is None else out_dtype
+    code_out = _DTYPE_CODE.get(out_dtype)
+    if code_in is None or code_out is None or not weights:
+        return None
+    if len(weights) > _lib.BQ_MAX_SEGMENTS or any(not isinstance(w, FP8Weight) for w in weights):
+        return None
+    lib = _require_lib()
+    ld_a = ld_b = chunk = chunk_stride = 0
+    bptr, mcode, keep = 0, 1, None
+    if a.stride(1) != 1 or a.data_ptr() % 16:
+        return None
+    if mode == "plain":
+        if not a.is_contiguous():
+            return None
+        ld_a = K
+    elif mode == "silu_mul":
+        if b is None or b.shape != a.shape or b.dtype != a.dtype or b.stride(1) != 1:
+            return None
+        mcode, bptr, ld_a, ld_b = 2, b.data_ptr(), a.stride(0), b.stride(0)
+    elif mode == "sigmoid_gate":
+        if b is None or b.dtype != a.dtype:
+            return None
+        if b.dim() == 3 and b.shape[0] == M and b.shape[1] * b.shape[2] == K and b.stride(2) == 1:
+            chunk, chunk_stride, ld_b = b.shape[2], b.stride(1), b.stride(0)
+        elif b.shape == a.shape and b.stride(1) == 1:
+            chunk, chunk_stride, ld_b = K, 0, b.stride(0)
+        else:
+            return None
+        mcode, bptr, ld_a = 3, b.data_ptr(), a.stride(0)
+    else:
+        raise ValueError(f"unknown mode {mode!r}")
+    es = a.element_size()
+    if (ld_a * es) % 16 or (ld_b * es) % 16 or bptr % 16 or (chunk_stride * es) % 16 or chunk % 8:
+        return None
+    outs = []
+    for i, w in enumerate(weights):
+        if w.data.shape[1] != K or not w.data.is_contiguous():
+            return None
+        y = out[i] if out is not None else torch.empty((M, w.data.shape[0]), dtype=out_dtype,
+                                                       device=a.device)
+        if y.shape != (M, w.data.shape[0]) or y.dtype != out_dtype or y.stride(1) != 1:
+            raise ValueError(f"out[{i}] must be [{M}, {w.data.shape[0]}] {out_dtype}")
+        outs.append(y)
+    xq = torch.empty((M, K), dtype=FP8, device=a.device)
+    sx = torch.empty((1, 1), dtype=torch.float32, device=a.device)
+    n = len(weights)
+    wq = (ctypes.c_void_p * n)(*[w.data.data_ptr() for w in weights])
+    sw = (ctypes.c_void_p * n)(*[w.scale.data_ptr() for w in weights])
+    yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in outs])
+    Ns = (ctypes.c_int64 * n)(*[w.data.shape[0] for w in weights])
+    ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in outs])
+    rc = lib.bq_linear_w8a8_grouped(a.data_ptr(), bptr, mcode, code_in, M, K, ld_a, ld_b, chunk,
+                                    chunk_stride, xq.data_ptr(), sx.data_ptr(), n, wq, sw, yp, Ns, ld,
+                                    code_out, _take_slot(a.device), 32, _stream_ptr(a.device))
+    del keep
+    if rc == _lib.BQ_ERR_UNSUPPORTED:
+        return None
+    _lib.check(rc, "linear_fused")
+    return outs, xq, sx
+
+
 def fp8_linear(x: torch.Tensor, w: FP8Weight) -> torch.Tensor:
     """`F.linear(x, w)` for a single call site; leading dims preserved (braid/model/quant.py:244-252)."""
     *lead, K = x.shape
-    xq, sx = quantize_act(x.reshape(-1, K))
+    x2 = x.reshape(-1, K)
+    fused = linear_fused(x2, (w,)) if x2.is_cuda else None
+    if fused is not None:
+        return fused[0][0].reshape(*lead, w.shape[0])
+    xq, sx = quantize_act(x2)
     return fp8_matmul(xq, sx, w, out_dtype=x.dtype).reshape(*lead, w.shape[0])
 
 
@@ -491,9 +582,14 @@ def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.T
     if not any(isinstance(w, FP8Weight) for w in weights):
         return [F.linear(x, w) for w in weights]
     *lead, K = x.shape
-    xq, sx = quantize_act(x.reshape(-1, K))
+    x2 = x.reshape(-1, K)
     fp8 = [w for w in weights if isinstance(w, FP8Weight)]
-    ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
+    fused = linear_fused(x2, fp8) if x2.is_cuda else None
+    if fused is not None:
+        ys = iter(fused[0])
+    else:
+        xq, sx = quantize_act(x2)
+        ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
     out = []
     for w in weights:
         if isinstance(w, FP8Weight):
@@ -524,19 +620,37 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     the same primitives.
     """
     *lead, K = x.shape
-    xq, sx = quantize_act(x.reshape(-1, K))
-    M = xq.shape[0]
+    x2 = x.reshape(-1, K)
+    M = x2.shape[0]
     I = gate_proj.shape[0]
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
-    fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype,
-                       out=(gu[:, :I], gu[:, I:]))
-    hq, sh = silu_mul_quant(gu[:, :I], gu[:, I:])
-    y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype)
+    halves = (gu[:, :I], gu[:, I:])
+    if linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
+        xq, sx = quantize_act(x2)
+        fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
+    fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1])
+    if fused is not None:
+        y = fused[0][0]
+    else:
+        hq, sh = silu_mul_quant(halves[0], halves[1])
+        y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype)
     return y.reshape(*lead, down_proj.shape[0])
 
 
 def gated_output_projection(o: torch.Tensor, gate: torch.Tensor, o_proj: FP8Weight) -> torch.Tensor:
     """`linear(o * torch.sigmoid(gate), o_proj)` (braid/model/attention.py:215-216) in 2 launches."""
     *lead, K = o.shape
+    o2 = o.reshape(-1, K)
+    g = gate
+    if gate.dim() == o.dim() + 1:        # [..., H, D] per-head view -> [rows, H, D]
+        try:
+            g = gate.view(o2.shape[0], gate.shape[-2], gate.shape[-1])
+        except RuntimeError:
+            g = None
+    elif gate.shape == o.shape:
+        g = gate.reshape(-1, K)
+    fused = linear_fused(o2, (o_proj,), mode="sigmoid_gate", b=g) if g is not None else None
+    if fused is not None:
+        return fused[0][0].reshape(*lead, o_proj.shape[0])
     oq, so = sigmoid_gate_quant(o, gate)
     return fp8_matmul(oq.reshape(-1, K), so, o_proj, out_dtype=o.dtype).reshape(*lead, o_proj.shape[0])

@@ -183,6 +183,36 @@ int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, 
                          void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * Quantize-and-multiply in ONE launch (decode regime, M <= 256): the activation
+ * quantizer of bq_quantize_act / bq_silu_mul_quant / bq_sigmoid_gate_quant runs
+ * inside the weight-streaming GEMM kernel, on the warps that would otherwise
+ * idle until the epilogue, while the producer warp is already streaming
+ * weights.  Codes and scale are also written out (xq_out, sx_out), so they can
+ * be reused.  Results are bit-identical to the separate calls.
+ *
+ * Replaces: braid/model/quant.py:244-252 (`fp8_linear`: quantize_act followed
+ * by fp8_matmul), :260-286 (`project`), and the two halves of the quantized
+ * MLP, braid/model/mlp.py:44-49.
+ *
+ *   mode 1: a = x [M,K] dense                      (b unused)
+ *   mode 2: a = gate, b = up, row strides ld_a/ld_b (SiLU(a)*b, K = columns)
+ *   mode 3: a = o (ld_a), b = gate (ld_b, chunk, chunk_stride as in
+ *           bq_sigmoid_gate_quant)                  (a*sigmoid(b))
+ *   xq_out  device, M*K bytes, 16-byte aligned; sx_out device, one float
+ *   ws      32 bytes of scratch, zeroed once, self-resetting (5 words used)
+ *
+ * Returns BQ_ERR_UNSUPPORTED when the shape needs the prefill kernel (M > 256)
+ * or the launch could not be made fully resident; call the separate entry
+ * points in that case.
+ */
+int bq_linear_w8a8_grouped(const void* a, const void* b, int mode, int act_dtype, int64_t M,
+                           int64_t K, int64_t ld_a, int64_t ld_b, int64_t chunk,
+                           int64_t chunk_stride, void* xq_out, float* sx_out, int n_seg,
+                           const void* const* wq, const float* const* sw, void* const* y,
+                           const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
+                           size_t ws_bytes, void* stream);
+
+/*
  * Copies the sticky device status word of a scratch buffer to the host
  * (synchronises `stream`; never call during capture).  0 means every bounded
  * device wait so far completed; otherwise BQ_ERR_DEVICE_WAIT.  The word is
@@ -192,8 +222,13 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
 
 /*
  * Tuning hooks used by the benchmark and tests; not needed for normal use.
- * bq_set_option("decode_split_k", v)   0 = heuristic, else force a cluster size
- * bq_set_option("decode_stages", v)    0 = heuristic, else force pipeline depth
+ * bq_set_option("decode_split_k", v)    0 = heuristic, else force the K slices per tile
+ * bq_set_option("decode_stages", v)     0 = heuristic, else cap the pipeline depth
+ * bq_set_option("decode_cta_target", v) CTAs a small weight is sliced to reach (default 160)
+ * bq_set_option("decode_smem_cap", v)   0 = none, else cap pipeline bytes per CTA
+ * bq_set_option("stream_max_m", v)      largest M the weight-streaming kernel takes (<= 256)
+ * bq_set_option("gemm_pdl" | "quant_pdl", 0/1)  programmatic dependent launch
+ * bq_set_option("quant_block" | "quant_held", v) quantizer launch shape overrides
  * Returns BQ_ERR_BAD_ARG for an unknown key.
  */
 int bq_set_option(const char* key, int64_t value);

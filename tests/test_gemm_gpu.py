@@ -264,3 +264,75 @@ def test_shape_guards(Q):
     with pytest.raises(ValueError):
         Q.fp8_matmul(xq, sx, bad)
     assert Q.device_status() == 0
+
+
+# ---- quantize-and-multiply in one launch -------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 8, 37, 128, 256])
+@pytest.mark.parametrize("K,Ns", [(4096, (8192, 1024, 1024)), (4096, (4096,)), (256, (512, 272)),
+                                  (12288, (4096,))])
+def test_fused_linear_equals_the_separate_kernels(Q, M, K, Ns):
+    x = randn_cpu((M, K), seed=M + K, scale=1.7).cuda()
+    ws = [Q.quantize_weight(randn_cpu((n, K), seed=50 + i, scale=0.02).cuda()) for i, n in enumerate(Ns)]
+    Q.set_fused_linear(True)
+    try:
+        fused = Q.linear_fused(x, ws)
+    finally:
+        Q.set_fused_linear(False)
+    if fused is None:
+        # allowed only where the launch cannot be fully resident (the widest batch tiles)
+        assert M > 128, "the fused form should take every shape up to 128 rows"
+        return
+    ys, xq, sx = fused
+    xq_ref, sx_ref = Q.quantize_act(x)
+    assert torch.equal(sx, sx_ref)
+    assert torch.equal(xq.view(torch.uint8), xq_ref.view(torch.uint8))
+    for y, y_ref in zip(ys, Q.fp8_matmul_grouped(xq_ref, sx_ref, ws)):
+        assert torch.equal(y, y_ref)
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [4, 128])
+def test_fused_prologues_equal_the_separate_kernels(Q, M):
+    I, H, D = 12288, 16, 256
+    gu = randn_cpu((M, 2 * I), seed=60, scale=2.0).cuda()
+    wd = Q.quantize_weight(randn_cpu((4096, I), seed=61, scale=0.02).cuda())
+    Q.set_fused_linear(True)
+    ys, hq, sh = Q.linear_fused(gu[:, :I], (wd,), mode="silu_mul", b=gu[:, I:])
+    hq_ref, sh_ref = Q.silu_mul_quant(gu[:, :I], gu[:, I:])
+    assert torch.equal(sh, sh_ref) and torch.equal(hq.view(torch.uint8), hq_ref.view(torch.uint8))
+    assert torch.equal(ys[0], Q.fp8_matmul(hq_ref, sh_ref, wd))
+
+    qg = randn_cpu((M, H * 2 * D), seed=62, scale=2.0).cuda()
+    o = randn_cpu((M, H * D), seed=63).cuda()
+    wo = Q.quantize_weight(randn_cpu((4096, H * D), seed=64, scale=0.02).cuda())
+    gate = qg.view(M, H, 2 * D)[..., D:]
+    oq_ref, so_ref = Q.sigmoid_gate_quant(o, gate)
+    want = Q.fp8_matmul(oq_ref, so_ref, wo)
+    for g in (gate, gate.reshape(M, H * D)):          # per-head view and dense copy
+        ys, oq, so = Q.linear_fused(o, (wo,), mode="sigmoid_gate", b=g)
+        assert torch.equal(so, so_ref) and torch.equal(oq.view(torch.uint8), oq_ref.view(torch.uint8))
+        assert torch.equal(ys[0], want)
+    Q.set_fused_linear(False)
+
+
+def test_fused_and_unfused_sublayers_agree_and_repeat(Q):
+    """The public calls can take the one-launch form; switching it on must not change a bit,
+    and 300 back-to-back fused calls must leave the counters clean."""
+    M, H, I = 16, 1024, 2048
+    x = randn_cpu((M, H), seed=70).cuda()
+    wg, wu = (Q.quantize_weight(randn_cpu((I, H), seed=71 + i, scale=0.02).cuda()) for i in range(2))
+    wd = Q.quantize_weight(randn_cpu((H, I), seed=73, scale=0.02).cuda())
+    plain = (Q.mlp_forward(x, wg, wu, wd), Q.project(x, wg, wu), Q.fp8_linear(x, wg))
+    Q.set_fused_linear(True)
+    try:
+        fused = (Q.mlp_forward(x, wg, wu, wd), Q.project(x, wg, wu), Q.fp8_linear(x, wg))
+        for _ in range(300):
+            y = Q.mlp_forward(x, wg, wu, wd)
+    finally:
+        Q.set_fused_linear(False)
+    assert torch.equal(fused[0], plain[0]) and torch.equal(fused[2], plain[2])
+    for a, b in zip(fused[1], plain[1]):
+        assert torch.equal(a, b)
+    assert torch.equal(y, plain[0])
+    assert Q.device_status() == 0
