@@ -690,6 +690,165 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tm_x,
 }
 
 // ---------------------------------------------------------------------------
+// Persistent tile kernel on CTA pairs (prefill regime, cta_group::2)
+// ---------------------------------------------------------------------------
+// Two CTAs on neighbouring SMs share one 256 x 256 output tile: each loads 128
+// activation rows and 128 weight rows per K block (32 KB instead of the 48 KB a
+// lone CTA needs for 128 x 256), the leader issues one MMA that spans both SMs,
+// and each CTA keeps the accumulator of its own 128 rows in its tensor memory.
+// Shared-memory traffic per flop drops by a third, which is what limits the
+// single-CTA kernel.  Roles per CTA as in gemm_tile_kernel; the MMA warp works
+// in the leader only.
+constexpr int kPairStageBytes = 2 * kATileBytes;    // 16 KB activation rows + 16 KB weight rows
+constexpr int kPairStages = 6;
+constexpr int kPairTile = 256;
+
+__global__ void __launch_bounds__(kTileThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
+                 const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar_base = base + kPairStages * kPairStageBytes;
+  auto a_tile = [&](int s) { return base + s * kPairStageBytes; };
+  auto b_tile = [&](int s) { return base + s * kPairStageBytes + kATileBytes; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * kPairStages + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kPairStages + 2 + b); };
+  volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4));
+  volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + kPairTile - 1) / kPairTile;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_x);
+    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tm_w.w[i]);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar(s), 1);     // the leader's producer arrives, bytes of both CTAs expected
+      mbar_init(empty_bar(s), 1);    // one MMA commit per use
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 8);    // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();     // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait_prior_grids();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol = policy_evict_last();
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < p.total_tiles && ok; t += n_pairs) {
+        const int sg = find_segment(p, t);
+        const int local = t - p.seg[sg].tile_begin;
+        const int m0 = (local % m_tiles) * kPairTile + rank * kRowTile;
+        const int n0 = (local / m_tiles) * kPairTile + rank * kRowTile;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kPairStages, use = it / kPairStages;
+          if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
+          tma_load_2d_pair(a_tile(s), &tm_x, full_bar(s), kb * kBK, m0, pol);
+          tma_load_2d_pair(b_tile(s), &tm_w.w[sg], full_bar(s), kb * kBK, n0, pol);
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = idesc_e4m3(kPairTile, kPairTile);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = pair; t < p.total_tiles && ok; t += n_pairs, ++tile_iter) {
+        const int b = tile_iter & 1, use_b = tile_iter >> 1;
+        if (use_b > 0 && !mbar_wait(acc_empty(b), (use_b - 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + b * kPairTile;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kPairStages, use = it / kPairStages;
+          if (!mbar_wait(full_bar(s), use & 1)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(a_tile(s));
+          const uint64_t db = smem_desc_sw128(b_tile(s));
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j)
+            mma_f8_pair(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+          // the stage is free in BOTH CTAs once these MMAs retire
+          mma_commit_pair(empty_bar(s));
+          mma_commit_pair(map_to_cta(empty_bar(s), 1));
+        }
+        if (ok) {
+          mma_commit_pair(acc_full(b));
+          mma_commit_pair(map_to_cta(acc_full(b), 1));
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;
+    int tile_iter = 0;
+    bool ok = true;
+    const uint32_t leader_acc_empty0 = map_to_cta(acc_empty(0), 0);
+    const uint32_t leader_acc_empty1 = map_to_cta(acc_empty(1), 0);
+    for (int t = pair; t < p.total_tiles && ok; t += n_pairs, ++tile_iter) {
+      const int b = tile_iter & 1, use_b = tile_iter >> 1;
+      const int sg = find_segment(p, t);
+      const Segment seg = p.seg[sg];
+      const int local = t - seg.tile_begin;
+      const int m0 = (local % m_tiles) * kPairTile + rank * kRowTile;
+      const int n0 = (local / m_tiles) * kPairTile;
+      if (!mbar_wait(acc_full(b), use_b & 1)) { ok = false; break; }
+      tc_fence_after();
+      const float scale = __ldg(p.sx) * __ldg(seg.sw);
+      const int m = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * kPairTile;
+      for (int c = 0; c < kPairTile; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c, r);
+        tmem_ld_wait();
+        if (m < p.M && (n0 + c) < seg.n) {
+          const long long idx = (long long)m * seg.ldy + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            float4 v = make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
+                                   __uint_as_float(r[j + 2]) * scale,
+                                   __uint_as_float(r[j + 3]) * scale);
+            store_out4(seg.y, idx + j, p.out_dtype, v);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(b == 0 ? leader_acc_empty0 : leader_acc_empty1);
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  cluster_sync_all();     // nobody frees tensor memory while the peer may still use the pair
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, (unsigned int)kErrDeviceWait);
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -743,6 +902,7 @@ int device_sms() {
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
+long long g_opt_pair = 1;       // prefill regime on CTA pairs (cta_group::2)
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -754,7 +914,9 @@ int configure_once() {
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     cudaError_t e2 = cudaFuncSetAttribute(gemm_tile_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    rc = (e1 == cudaSuccess && e2 == cudaSuccess) ? kOk : kErrLaunch;
+    cudaError_t e3 = cudaFuncSetAttribute(gemm_pair_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? kOk : kErrLaunch;
     if (rc != kOk) (void)cudaGetLastError();
   }
   return rc;
@@ -931,6 +1093,34 @@ int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, 
   return kOk;
 }
 
+int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return kErrLaunch;
+  const int smem = kPairStages * kPairStageBytes + kBarrierBytes + 1024;
+  int pairs = p.total_tiles < sms / 2 ? p.total_tiles : sms / 2;
+  if (pairs < 1) pairs = 1;
+  g_last_launch[0] = 2; g_last_launch[1] = 2 * pairs; g_last_launch[2] = 2;
+  g_last_launch[3] = kPairStages; g_last_launch[4] = smem; g_last_launch[5] = kPairTile;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(kTileThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 2 : 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, tm_x, maps, p);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
+  return kOk;
+}
+
 }  // namespace
 
 namespace bq {
@@ -941,6 +1131,7 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
+  if (strcmp(key, "prefill_pair") == 0) { g_opt_pair = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;
@@ -998,8 +1189,10 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.fuse.words = static_cast<unsigned int*>(ws);
   }
 
-  const int w_box_rows = stream_path ? kRowTile : kTileN;
-  p.m_tiles = (int)((M + kRowTile - 1) / kRowTile);
+  const bool pair_path = !stream_path && g_opt_pair != 0;
+  const int w_box_rows = (stream_path || pair_path) ? kRowTile : kTileN;
+  const int tile_n = pair_path ? kPairTile : w_box_rows;
+  p.m_tiles = pair_path ? (int)((M + kPairTile - 1) / kPairTile) : (int)((M + kRowTile - 1) / kRowTile);
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
@@ -1007,7 +1200,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.seg[i].ldy = ldy[i];
     p.seg[i].n = (int)N[i];
     p.seg[i].tile_begin = tiles;
-    const long long nt = (N[i] + w_box_rows - 1) / w_box_rows;
+    const long long nt = (N[i] + tile_n - 1) / tile_n;
     const long long add = stream_path ? nt : nt * p.m_tiles;
     if (tiles + add > 0x3fffffffLL) return kErrTooLarge;
     tiles += (int)add;
@@ -1021,6 +1214,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     return launch_stream(tm_x, maps, p, stream);
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
+  if (pair_path) return launch_pair(tm_x, maps, p, stream);
   return launch_tile(tm_x, maps, p, stream);
 }
 

@@ -259,7 +259,7 @@ def last_gemm_launch() -> dict:
     """What the last GEMM call of this thread launched (kernel, grid, split, stages, smem, tile)."""
     out = (ctypes.c_int64 * 6)()
     _lib.check(_require_lib().bq_last_gemm_launch(out), "last_gemm_launch")
-    return {"kernel": "stream" if out[0] == 0 else "tile", "grid": out[1], "split": out[2],
+    return {"kernel": {0: "stream", 1: "tile", 2: "pair"}.get(int(out[0]), "?"), "grid": out[1], "split": out[2],
             "stages": out[3], "smem": out[4], "mma_n": out[5]}
 
 

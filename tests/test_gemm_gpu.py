@@ -53,7 +53,7 @@ def test_decode_regime_against_the_oracle(Q, M, N, K):
 def test_prefill_regime_against_fp32_dequant_matmul(Q, M, N, K):
     _, _, xq, sx, fw = _operands(Q, M, N, K, seed=M)
     y = Q.fp8_matmul(xq, sx, fw)
-    assert Q.last_gemm_launch()["kernel"] == "tile"
+    assert Q.last_gemm_launch()["kernel"] in ("tile", "pair")
     ref = TS.dequant_matmul(xq, sx, fw.data, fw.scale)
     assert max_rel(y, ref) <= TOL_BF16
     y32 = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
@@ -63,6 +63,22 @@ def test_prefill_regime_against_fp32_dequant_matmul(Q, M, N, K):
         ref_o = torch.from_numpy(oracle.gemm(codes_np(xq[sub]), codes_np(fw.data),
                                              sx.item(), fw.scale.item()))
         assert max_rel(y32[sub].cpu(), ref_o) <= TOL_F32
+
+
+def test_both_prefill_kernels_agree(Q):
+    """The single-CTA tile kernel and the CTA-pair kernel accumulate K in the same order: same bits."""
+    _, _, xq, sx, fw = _operands(Q, 1000, 4096 + 16, 1040, seed=77)
+    try:
+        Q.set_option("prefill_pair", 1)
+        a = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+        assert Q.last_gemm_launch()["kernel"] == "pair"
+        Q.set_option("prefill_pair", 0)
+        b = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
+        assert Q.last_gemm_launch()["kernel"] == "tile"
+    finally:
+        Q.set_option("prefill_pair", 1)
+    assert torch.equal(a, b)
+    assert Q.device_status() == 0
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (128, 4096, 4096), (128, 1024, 4096),
