@@ -58,6 +58,9 @@ struct Segment {
   int tile_begin;      // tile kernel: index of the segment's first tile
   int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
   int cluster_begin;   // stream kernel: index of the segment's first cluster
+  long long total_kb;  // persistent stream kernel: row tiles x K blocks of this weight
+  int ctas;            // persistent stream kernel: CTAs that share this weight
+  int cta_begin;       // persistent stream kernel: first of those CTAs (they wrap around the grid)
 };
 
 // The activation quantizer fused into the stream kernel (mode 0 = not fused: the
@@ -84,6 +87,8 @@ struct GemmParams {
   unsigned int* status;
   int seq;             // launch counter (development builds only)
   FuseParams fuse;
+  unsigned int* flags;   // persistent stream kernel: one word per (weight, CTA), zero between launches
+  float* partials;       // persistent stream kernel: [weight][CTA][mma_n][128] fp32
 };
 
 struct alignas(64) WeightMaps {
@@ -545,6 +550,308 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
 }
 
 // ---------------------------------------------------------------------------
+// Persistent weight-streaming kernel (decode regime, every SM streams all the time)
+// ---------------------------------------------------------------------------
+// One CTA per SM.  The K blocks of each weight, taken row tile by row tile, form
+// one long sequence that is cut into equal contiguous ranges, one per CTA -- so
+// every SM streams the same number of bytes whatever the shapes are.  A range
+// that starts or ends inside a row tile leaves a partial sum: the CTA that holds
+// the beginning of the tile (lowest K) owns it and adds the partial sums of the
+// CTAs that continue the tile, in ascending-K order, from a scratch buffer (L2).
+// The cut points depend on the weight's own shape and the SM count only, never
+// on what else is in the launch, so results do not depend on grouping.
+// Warp roles: 0 = TMA producer (runs ahead across tiles and weights), 1 = MMA
+// issuer, 2..5 = epilogue (tensor memory -> partial/scratch or -> output), with
+// the accumulators rotated through tensor memory so that the epilogue of one tile
+// overlaps the stream of the next.
+constexpr int kPsThreads = 192;
+constexpr int kPsEpiThreads = 128;
+constexpr int kPsChunk = 16;                       // batch rows the epilogue transposes at a time
+
+__device__ __forceinline__ void epi_bar() {       // the four epilogue warps only
+  asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
+struct PsRange {
+  long long r, r1;      // K-block range of this CTA inside the weight's sequence
+  int j;                // index of this CTA among the CTAs of the weight
+};
+
+__device__ __forceinline__ bool ps_range(const Segment& sg, int cta, int grid, PsRange& out) {
+  int j = cta - sg.cta_begin;
+  if (j < 0) j += grid;
+  if (j >= sg.ctas) return false;
+  out.j = j;
+  out.r = (long long)j * sg.total_kb / sg.ctas;
+  out.r1 = (long long)(j + 1) * sg.total_kb / sg.ctas;
+  return out.r < out.r1;
+}
+
+// Walks the K blocks this CTA streams, weight after weight, in the order every role uses.
+struct PsCursor {
+  int w;
+  long long r, r1;
+  __device__ __forceinline__ void init() { w = -1; r = 0; r1 = 0; }
+  // Moves to the next K block; returns false when the CTA has no more work.
+  __device__ __forceinline__ bool next(const GemmParams& p, int cta, int grid, int& tile, int& kb) {
+    while (r >= r1) {
+      if (++w >= p.n_seg) return false;
+      PsRange rg;
+      if (ps_range(p.seg[w], cta, grid, rg)) { r = rg.r; r1 = rg.r1; }
+    }
+    tile = (int)(r / p.k_blocks);
+    kb = (int)(r - (long long)tile * p.k_blocks);
+    ++r;
+    return true;
+  }
+};
+
+__global__ void __launch_bounds__(kPsThreads, 1)
+gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_x,
+                    const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p,
+                    const int smem_tile_bytes) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+  const int b_tile_bytes = p.mma_n * kBK;
+  const uint32_t a_base = base;
+  const uint32_t b_base = base + p.stages * kATileBytes;
+  // after the pipeline: a [16][128] fp32 transpose buffer for the epilogue, then the barriers
+  float* const xpose = reinterpret_cast<float*>(base_ptr + smem_tile_bytes);
+  const uint32_t bar_base = base + smem_tile_bytes + kPsChunk * kRowTile * 4;
+  uint8_t* const bar_ptr = base_ptr + smem_tile_bytes + kPsChunk * kRowTile * 4;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * p.stages + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * p.stages + 4 + b); };
+  volatile uint32_t* const tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * p.stages + 8));
+  volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, grid = gridDim.x;
+  const int kb_per_tile = p.k_blocks;
+  // accumulators rotate through tensor memory: 512 columns / columns per accumulator
+  uint32_t acc_cols = 32;
+  while (acc_cols < static_cast<uint32_t>(p.mma_n)) acc_cols <<= 1;
+  const int n_acc = (512 / acc_cols) > 4 ? 4 : (512 / acc_cols);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_x);
+    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tm_w.w[i]);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);      // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      bool ok = true;
+      PsCursor cw, cx;          // weight-tile loads run ahead of activation-tile loads
+      cw.init();
+      cx.init();
+      int tile, kb, it = 0;
+      // weights do not depend on earlier kernels: fill the pipeline with them first,
+      // then wait for the kernel that produces the activation codes
+      int prefill = 0;
+      while (prefill < p.stages && cw.next(p, cta, grid, tile, kb)) {
+        mbar_expect_tx(full_bar(prefill), kATileBytes + b_tile_bytes);
+        tma_load_2d(a_base + prefill * kATileBytes, &tm_w.w[cw.w], full_bar(prefill), kb * kBK,
+                    tile * kRowTile, pol_w);
+        ++prefill;
+      }
+      pdl_wait_prior_grids();
+      for (int i = 0; i < prefill; ++i) {
+        cx.next(p, cta, grid, tile, kb);
+        tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), kb * kBK, 0, pol_x);
+      }
+      it = prefill;
+      while (ok && cw.next(p, cta, grid, tile, kb)) {
+        const int s = it % p.stages, use = it / p.stages;
+        if (!mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
+        mbar_expect_tx(full_bar(s), kATileBytes + b_tile_bytes);
+        tma_load_2d(a_base + s * kATileBytes, &tm_w.w[cw.w], full_bar(s), kb * kBK, tile * kRowTile,
+                    pol_w);
+        tma_load_2d(b_base + s * b_tile_bytes, &tm_x, full_bar(s), kb * kBK, 0, pol_x);
+        ++it;
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = idesc_e4m3(kRowTile, p.mma_n);
+      int it = 0, seg_iter = 0;
+      bool ok = true;
+      for (int w = 0; w < p.n_seg && ok; ++w) {
+        PsRange rg;
+        if (!ps_range(p.seg[w], cta, grid, rg)) continue;
+        long long r = rg.r;
+        while (r < rg.r1 && ok) {
+          const int tile = (int)(r / kb_per_tile);
+          const long long tile_end = (long long)(tile + 1) * kb_per_tile;
+          const long long seg_end = rg.r1 < tile_end ? rg.r1 : tile_end;
+          const int b = seg_iter % n_acc, use_b = seg_iter / n_acc;
+          if (use_b > 0 && !mbar_wait(acc_empty(b), (use_b - 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + b * acc_cols;
+          bool first = true;
+          for (; r < seg_end; ++r, ++it) {
+            const int s = it % p.stages, use = it / p.stages;
+            if (!mbar_wait(full_bar(s), use & 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
+            const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
+#pragma unroll
+            for (int j = 0; j < kBK / kUmmaK; ++j) {
+              mma_f8(tmem_d, da + 2u * j, db + 2u * j, idesc, (first && j == 0) ? 0u : 1u);
+            }
+            first = false;
+            mma_commit(empty_bar(s));
+          }
+          if (ok) mma_commit(acc_full(b));
+          ++seg_iter;
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+    __syncwarp();
+  } else {
+    // ---- epilogue warps 2..5 --------------------------------------------------------------
+    const int quad = warp & 3;                       // TMEM lanes [32*quad, +32)
+    const int et = threadIdx.x - 64;                 // 0..127 among the epilogue threads
+    const int n_local = quad * 32 + lane;            // weight row inside the tile
+    const size_t part_stride = (size_t)kRowTile * p.mma_n;   // floats per partial tile
+    pdl_wait_prior_grids();                          // outputs / scratch are written only after this
+    const float sx = __ldg(p.sx);
+    int seg_iter = 0;
+    bool ok = true;
+    for (int w = 0; w < p.n_seg && ok; ++w) {
+      const Segment sg = p.seg[w];
+      PsRange rg;
+      if (!ps_range(sg, cta, grid, rg)) continue;
+      const float scale = sx * __ldg(sg.sw);
+      long long r = rg.r;
+      while (r < rg.r1 && ok) {
+        const int tile = (int)(r / kb_per_tile);
+        const long long tile_start = (long long)tile * kb_per_tile;
+        const long long tile_end = tile_start + kb_per_tile;
+        const long long seg_end = rg.r1 < tile_end ? rg.r1 : tile_end;
+        const bool owner = (r == tile_start);        // holds the lowest-K part of the tile
+        const int b = seg_iter % n_acc, use_b = seg_iter / n_acc;
+        // a wait that runs out is recorded, but the warps go on together: leaving the loop
+        // one by one would strand the others at the named barrier
+        if (!mbar_wait(acc_full(b), use_b & 1)) *abort_flag = 1;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * acc_cols;
+        const int row0 = tile * kRowTile;
+        if (!owner) {
+          // continuation of a tile another CTA owns: publish the partial sum
+          float* dst = p.partials + ((size_t)w * grid + rg.j) * part_stride;
+          for (int c = 0; c < p.mma_n; c += 16) {
+            uint32_t v[16];
+            tmem_ld16(taddr + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c + i < p.M) dst[(size_t)(c + i) * kRowTile + n_local] = __uint_as_float(v[i]);
+          }
+          __threadfence();
+          epi_bar();
+          if (et == 0) {
+            unsigned int* flag = p.flags + (size_t)w * grid + rg.j;
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+          }
+        } else {
+          // the CTAs that continue this tile, in ascending K
+          int first_c = rg.j + 1, n_c = 0;
+          if (seg_end < tile_end) {
+            for (int jc = rg.j + 1; jc < sg.ctas; ++jc) {
+              const long long rs = (long long)jc * sg.total_kb / sg.ctas;
+              if (rs >= tile_end) break;
+              ++n_c;
+            }
+            if (et < n_c) {        // one epilogue thread per continuation waits for its flag
+              const unsigned int* flag = p.flags + (size_t)w * grid + first_c + et;
+              const long long t0 = clock64();
+              for (;;) {
+                unsigned int f;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
+                if (f != 0) break;
+                if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
+              }
+            }
+            epi_bar();
+          }
+          for (int c = 0; c < p.mma_n; c += kPsChunk) {
+            uint32_t v[16];
+            tmem_ld16(taddr + c, v);
+            tmem_ld_wait();
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = __uint_as_float(v[i]);
+            for (int k = 0; k < n_c; ++k) {      // ascending K: fixed order
+              const float* src = p.partials + ((size_t)w * grid + first_c + k) * part_stride;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (c + i < p.M) acc[i] += __ldcg(src + (size_t)(c + i) * kRowTile + n_local);
+            }
+            // transpose 16 batch rows x 128 weight rows through shared memory so that
+            // each output row is written as one 256-byte run
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xpose[i * kRowTile + n_local] = acc[i] * scale;
+            epi_bar();
+            {
+              const int n4 = lane * 4;
+              const bool col_ok = (row0 + n4) < sg.n;
+#pragma unroll
+              for (int i = 0; i < kPsChunk / 4; ++i) {
+                const int ml = quad + 4 * i;          // rows quad, quad+4, ...
+                const int m = c + ml;
+                const float4 o = *reinterpret_cast<const float4*>(xpose + ml * kRowTile + n4);
+                if (m < p.M && col_ok)
+                  store_out4(sg.y, (long long)m * sg.ldy + row0 + n4, p.out_dtype, o);
+              }
+            }
+            epi_bar();
+          }
+          if (n_c > 0 && et < n_c) p.flags[(size_t)w * grid + first_c + et] = 0u;   // consumed
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(b));
+        r = seg_end;
+        ++seg_iter;
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, (unsigned int)kErrDeviceWait);
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Persistent tile kernel (prefill regime)
 // ---------------------------------------------------------------------------
 constexpr int kTileN = 256;                       // MMA N = weight rows per tile
@@ -903,6 +1210,7 @@ long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
 long long g_opt_pair = 1;       // prefill regime on CTA pairs (cta_group::2)
+long long g_opt_decode_kernel = 1;   // 1 = cluster kernel (default), 0 = persistent when the scratch allows it, 2 = persistent only
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -916,7 +1224,10 @@ int configure_once() {
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     cudaError_t e3 = cudaFuncSetAttribute(gemm_pair_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? kOk : kErrLaunch;
+    cudaError_t e4 = cudaFuncSetAttribute(gemm_persist_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess && e4 == cudaSuccess)
+             ? kOk : kErrLaunch;
     if (rc != kOk) (void)cudaGetLastError();
   }
   return rc;
@@ -1093,6 +1404,70 @@ int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, 
   return kOk;
 }
 
+// Scratch layout of the persistent stream kernel, after the 64 bytes every GEMM scratch starts
+// with (status word): one flag word per (weight, CTA), then the partial tiles.
+constexpr size_t kPsFlagsOffset = 64;
+constexpr size_t kPsPartialsOffset = 64 + 8192;     // room for 8 weights x 256 CTAs of flags
+
+size_t persist_scratch_bytes(int sms, int n_seg, int mma_n) {
+  return kPsPartialsOffset + (size_t)n_seg * sms * kRowTile * mma_n * sizeof(float);
+}
+
+int launch_persist(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, void* ws,
+                   cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0 || sms > 256) return kErrLaunch;
+  p.mma_n = ((p.M + 15) / 16) * 16;
+  const int stage_bytes = kATileBytes + p.mma_n * kBK;
+  const int grid = sms;
+  // K blocks a CTA takes from one weight: at least 4 (64 KB of weights), and few enough
+  // CTAs per row tile that one epilogue thread can watch each continuation
+  int min_range = (p.k_blocks + 63) / 64;
+  if (min_range < 4) min_range = 4;
+  int next_begin = 0;
+  long long most = 0;
+  for (int i = 0; i < p.n_seg; ++i) {
+    Segment& sg = p.seg[i];
+    const long long tiles = (sg.n + kRowTile - 1) / kRowTile;
+    sg.total_kb = tiles * p.k_blocks;
+    long long c = sg.total_kb / min_range;
+    if (c < 1) c = 1;
+    if (c > grid) c = grid;
+    sg.ctas = (int)c;
+    sg.cta_begin = next_begin;            // small weights start where the previous one stopped
+    next_begin = (next_begin + sg.ctas) % grid;
+    most += (sg.total_kb + sg.ctas - 1) / sg.ctas;
+  }
+  int stages = (kMaxSmem - 2048 - kPsChunk * kRowTile * 4) / stage_bytes;
+  if (stages > 24) stages = 24;
+  if (most < stages) stages = (int)(most < 2 ? 2 : most);
+  if (g_opt_stages > 0 && g_opt_stages < stages) stages = (int)g_opt_stages;
+  if (stages < 1) return kErrUnsupported;
+  p.stages = stages;
+  const int tile_bytes = stages * stage_bytes;
+  const int smem = tile_bytes + kPsChunk * kRowTile * 4 + kBarrierBytes + 1024;
+  if (smem > kMaxSmem) return kErrUnsupported;
+  p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(ws) + kPsFlagsOffset);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kPsPartialsOffset);
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kPsThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 1 : 0;
+  g_last_launch[0] = 3; g_last_launch[1] = grid; g_last_launch[2] = 1;
+  g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_persist_kernel, tm_x, maps, p, tile_bytes);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
+  return kOk;
+}
+
 int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return kErrLaunch;
@@ -1132,6 +1507,11 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "prefill_pair") == 0) { g_opt_pair = value ? 1 : 0; return kOk; }
+  if (strcmp(key, "decode_kernel") == 0) {
+    if (value < 0 || value > 2) return kErrBadArg;
+    g_opt_decode_kernel = value;
+    return kOk;
+  }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;
@@ -1145,7 +1525,19 @@ int bq::gemm_set_option(const char* key, long long value) {
   return kErrBadArg;
 }
 
-extern "C" size_t bq_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 16; }
+extern "C" size_t bq_gemm_workspace_bytes(int64_t M, int64_t, int64_t) {
+  // enough for the persistent kernel with the largest group; 16 bytes select the cluster kernel
+  const int sms = device_sms();
+  if (M <= 0 || M > g_opt_stream_max_m || sms <= 0) return 16;
+  return persist_scratch_bytes(sms, BQ_MAX_SEGMENTS, (int)(((M + 15) / 16) * 16));
+}
+
+extern "C" size_t bq_gemm_scratch_bytes(int64_t M, int n_seg) {
+  const int sms = device_sms();
+  if (M <= 0 || M > g_opt_stream_max_m || sms <= 0 || n_seg < 1) return 16;
+  if (n_seg > BQ_MAX_SEGMENTS) n_seg = BQ_MAX_SEGMENTS;
+  return persist_scratch_bytes(sms, n_seg, (int)(((M + 15) / 16) * 16));
+}
 
 namespace {
 
@@ -1211,6 +1603,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
+    if (!fuse && g_opt_decode_kernel != 1) {
+      const size_t need = persist_scratch_bytes(device_sms(), n_seg, mma_n);
+      if (ws_bytes >= need) return launch_persist(tm_x, maps, p, ws, stream);
+      if (g_opt_decode_kernel == 2) return kErrWorkspace;
+    }
     return launch_stream(tm_x, maps, p, stream);
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;

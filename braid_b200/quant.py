@@ -223,6 +223,34 @@ def _take_slot(device: torch.device) -> int:
     return buf.data_ptr() + slot * _SLOT_BYTES
 
 
+# Scratch of the persistent weight-streaming GEMM: partial sums of row tiles that straddle two
+# SMs.  One buffer per device, grown on demand outside captures; launches that use it are
+# ordered on the stream they run on.
+_gemm_scratch: dict[int, torch.Tensor] = {}
+_PERSISTENT_DECODE = False     # set by set_option("decode_kernel", 0 or 2); the default is the cluster kernel
+
+
+def _gemm_scratch_for(device: torch.device, M: int, n_seg: int) -> tuple[int, int]:
+    """(address, bytes) of a GEMM scratch that is large enough, else of a plain 64-byte slot."""
+    global _launches
+    if not _PERSISTENT_DECODE:
+        return _take_slot(device), 16
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    need = int(_require_lib().bq_gemm_scratch_bytes(M, n_seg))
+    buf = _gemm_scratch.get(idx)
+    if need > 16 and (buf is None or buf.numel() < need):
+        if torch.cuda.is_current_stream_capturing():
+            return _take_slot(device), 16       # cannot grow inside a capture: cluster kernel
+        torch.cuda.synchronize(idx)
+        buf = torch.zeros(need, dtype=torch.uint8, device=torch.device("cuda", idx))
+        torch.cuda.synchronize(idx)
+        _gemm_scratch[idx] = buf
+    if need <= 16 or buf is None:
+        return _take_slot(device), 16
+    _launches += 1
+    return buf.data_ptr(), buf.numel()
+
+
 def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -247,19 +275,29 @@ def device_status(device: torch.device | int | None = None) -> int:
     bad = int(words.max().item())
     if bad:
         words.zero_()
+    big = _gemm_scratch.get(idx)
+    if big is not None:
+        word = big[:16].view(torch.int32)[3:4]
+        if int(word.item()):
+            bad = bad or int(word.item())
+            word.zero_()
     return bad
 
 
 def set_option(key: str, value: int) -> None:
     """Tuning switch of the library (`decode_split_k`, `decode_stages`, `quant_block`, ...)."""
+    global _PERSISTENT_DECODE
     _lib.check(_require_lib().bq_set_option(key.encode(), int(value)), f"set_option({key})")
+    if key == "decode_kernel":
+        _PERSISTENT_DECODE = int(value) != 1
 
 
 def last_gemm_launch() -> dict:
     """What the last GEMM call of this thread launched (kernel, grid, split, stages, smem, tile)."""
     out = (ctypes.c_int64 * 6)()
     _lib.check(_require_lib().bq_last_gemm_launch(out), "last_gemm_launch")
-    return {"kernel": {0: "stream", 1: "tile", 2: "pair"}.get(int(out[0]), "?"), "grid": out[1], "split": out[2],
+    return {"kernel": {0: "stream", 1: "tile", 2: "pair", 3: "persist"}.get(int(out[0]), "?"),
+            "grid": out[1], "split": out[2],
             "stages": out[3], "smem": out[4], "mma_n": out[5]}
 
 
@@ -463,8 +501,9 @@ def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8
         yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
         Ns = (ctypes.c_int64 * n)(*[w.data.shape[0] for w in ws_])
         ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
+        ws_ptr, ws_bytes = _gemm_scratch_for(xq.device, M, n)
         rc = lib.bq_gemm_w8a8_grouped(xq.data_ptr(), sx.data_ptr(), M, K, n, wq, sw, yp, Ns, ld,
-                                      code, _take_slot(xq.device), 16, stream)
+                                      code, ws_ptr, ws_bytes, stream)
         _lib.check(rc, "fp8_matmul")
     return outs
 

@@ -139,12 +139,19 @@ int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t ro
                           void* q_out, float* scale_out, void* ws, size_t ws_bytes, void* stream);
 
 /*
- * Bytes of scratch the GEMM entry points need for a problem of this size
- * (split-K partial sums when the cluster path is not used, plus a status word).
- * May be 0 rows of partials; never less than 16.  Same zero-once contract as
- * the quantizer scratch.
+ * Bytes of scratch the GEMM entry points can use for a problem of this size on
+ * the current device.  16 bytes (just the status word) always work and select
+ * the cluster kernel, which is the default; with the size returned here
+ * (M <= 256) the experimental persistent weight-streaming kernel can be chosen
+ * with bq_set_option("decode_kernel", ...); it keeps partial sums of row tiles
+ * that straddle two SMs in this buffer.  Zero it once (cudaMemset); the kernels
+ * leave it zeroed where it matters.  bq_gemm_workspace_bytes assumes the
+ * largest group (BQ_MAX_SEGMENTS weights); bq_gemm_scratch_bytes takes the
+ * actual number of weights per launch.  Launches that share a scratch buffer
+ * must be ordered on one stream.
  */
 size_t bq_gemm_workspace_bytes(int64_t M, int64_t N_total, int64_t K);
+size_t bq_gemm_scratch_bytes(int64_t M, int n_seg);
 
 /*
  * Per-tensor W8A8 GEMM:  Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, fp32
@@ -222,6 +229,9 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
 
 /*
  * Tuning hooks used by the benchmark and tests; not needed for normal use.
+ * bq_set_option("decode_kernel", v)     1 = cluster kernel (default), 0 = persistent kernel when the
+ *                                       scratch allows, 2 = persistent kernel or BQ_ERR_WORKSPACE
+ * bq_set_option("prefill_pair", 0/1)    prefill regime on CTA pairs (default 1)
  * bq_set_option("decode_split_k", v)    0 = heuristic, else force the K slices per tile
  * bq_set_option("decode_stages", v)     0 = heuristic, else cap the pipeline depth
  * bq_set_option("decode_cta_target", v) CTAs a small weight is sliced to reach (default 160)
@@ -235,7 +245,7 @@ int bq_set_option(const char* key, int64_t value);
 
 /*
  * Describes the launch the last GEMM call on this thread chose:
- * out[0]=kernel (0 decode, 1 prefill) out[1]=grid out[2]=cluster/split
+ * out[0]=kernel (0 cluster stream, 1 tile, 2 CTA-pair tile, 3 persistent stream) out[1]=grid out[2]=cluster/split
  * out[3]=stages out[4]=dynamic smem bytes out[5]=batch tile (MMA N)
  */
 int bq_last_gemm_launch(int64_t out[6]);

@@ -45,7 +45,7 @@ def test_decode_regime_against_the_oracle(Q, M, N, K):
     assert max_rel(y.cpu(), ref) <= TOL_BF16
     y32 = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
     assert max_rel(y32.cpu(), ref) <= TOL_F32
-    assert Q.last_gemm_launch()["kernel"] == "stream"
+    assert Q.last_gemm_launch()["kernel"] in ("stream", "persist")
 
 
 @pytest.mark.parametrize("M,N,K", [(257, 256, 256), (512, 4096, 4096), (1000, 272, 4096),
@@ -124,29 +124,66 @@ def test_run_to_run_determinism_and_split_k(Q):
     _, _, xq, sx, fw = _operands(Q, 128, 4096, 4096, seed=8)
     ref = TS.dequant_matmul(xq, sx, fw.data, fw.scale)
     try:
-        for split in (1, 2, 4, 8):
+        Q.set_option("decode_kernel", 1)          # the cluster kernel: K slices per tile
+        for split in (1, 2, 4):
             Q.set_option("decode_split_k", split)
             a = Q.fp8_matmul(xq, sx, fw)
             assert Q.last_gemm_launch()["split"] == split
             for _ in range(3):
                 assert torch.equal(a, Q.fp8_matmul(xq, sx, fw)), f"split {split} is not deterministic"
             assert max_rel(a, ref) <= TOL_BF16
+        Q.set_option("decode_split_k", 0)
+        Q.set_option("decode_kernel", 2)          # the persistent kernel: equal K ranges per SM
+        a = Q.fp8_matmul(xq, sx, fw)
+        assert Q.last_gemm_launch()["kernel"] == "persist"
+        for _ in range(5):
+            assert torch.equal(a, Q.fp8_matmul(xq, sx, fw)), "persistent kernel is not deterministic"
+        assert max_rel(a, ref) <= TOL_BF16
     finally:
         Q.set_option("decode_split_k", 0)
+        Q.set_option("decode_kernel", 1)
 
 
-def test_pipeline_depth_does_not_change_results(Q):
+@pytest.mark.parametrize("kernel", [1, 2], ids=["cluster", "persistent"])
+def test_pipeline_depth_does_not_change_results(Q, kernel):
     _, _, xq, sx, fw = _operands(Q, 16, 512, 4096, seed=9)
     try:
+        Q.set_option("decode_kernel", kernel)
         Q.set_option("decode_split_k", 1)
         base = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
         for stages in (1, 2, 3, 5):
             Q.set_option("decode_stages", stages)
             assert torch.equal(base, Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32))
-            assert Q.last_gemm_launch()["stages"] == stages
+            assert Q.last_gemm_launch()["stages"] <= stages     # never deeper than the work
     finally:
         Q.set_option("decode_split_k", 0)
         Q.set_option("decode_stages", 0)
+        Q.set_option("decode_kernel", 1)
+
+
+@pytest.mark.parametrize("M", [1, 16, 100, 128, 256])
+@pytest.mark.parametrize("Ns,K", [((4096,), 4096), ((8192, 1024, 1024), 4096), ((12288, 12288), 4096),
+                                  ((4096,), 12288), ((272, 16, 528), 1040), ((1024,), 128)])
+def test_persistent_and_cluster_kernels_agree_within_tolerance(Q, M, Ns, K):
+    """Two different K decompositions of the same product: each within tolerance of the fp32
+    dequant-matmul, and very close to each other."""
+    x = randn_cpu((M, K), seed=M + K + len(Ns)).cuda()
+    ws = [Q.quantize_weight(randn_cpu((n, K), seed=90 + i, scale=0.02).cuda()) for i, n in enumerate(Ns)]
+    xq, sx = Q.quantize_act(x)
+    try:
+        Q.set_option("decode_kernel", 2)
+        a = Q.fp8_matmul_grouped(xq, sx, ws, out_dtype=torch.float32)
+        assert Q.last_gemm_launch()["kernel"] == "persist"
+        Q.set_option("decode_kernel", 1)
+        b = Q.fp8_matmul_grouped(xq, sx, ws, out_dtype=torch.float32)
+        assert Q.last_gemm_launch()["kernel"] == "stream"
+    finally:
+        Q.set_option("decode_kernel", 1)
+    for ya, yb, w in zip(a, b, ws):
+        ref = TS.dequant_matmul(xq, sx, w.data, w.scale)
+        assert max_rel(ya, ref) <= TOL_F32 and max_rel(yb, ref) <= TOL_F32
+        assert max_rel(ya, yb) <= 1e-5
+    assert Q.device_status() == 0
 
 
 @pytest.mark.parametrize("M", [4, 128, 1024])
