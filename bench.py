@@ -247,6 +247,7 @@ def run_reference_arm(args):
 def column_parallel_block(dist, rows_list, steps, warmup):
     """gate_up [2 x 12288, 4096] and down [4096, 12288] N-split over the ranks, bf16 all-gather of
     the h shards and of the output shards (NCCL over NVLink)."""
+    from braid_b200 import quant as Q
     from braid_b200.parallel import ColumnParallelMLP
     out = {}
     for rows in rows_list:
@@ -255,8 +256,21 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         fn = lambda: mlp.forward(x)  # noqa: E731
         ms, _ = timed_replays(fn, steps, warmup, dist=dist)
         flops = 2 * rows * 3 * 4096 * 12288
-        out[f"M{rows}"] = {"ms_per_call": ms / steps, "tflops": flops / (ms / steps * 1e-3) / 1e12,
-                           "all_gather_bytes": mlp.gather_bytes(rows)}
+        entry = {"ms_per_call": ms / steps, "tflops": flops / (ms / steps * 1e-3) / 1e12,
+                 "all_gather_bytes": mlp.gather_bytes(rows)}
+        del mlp
+        # the same MLP, unsharded, on one GPU of the same box (every rank runs it; rank 0 reports)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        mk = lambda n, k: Q.quantize_weight(  # noqa: E731
+            (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+        wg, wu, wd = mk(12288, 4096), mk(12288, 4096), mk(4096, 12288)
+        one = lambda: Q.mlp_forward(x, wg, wu, wd)  # noqa: E731
+        ms1, _ = timed_replays(one, steps, warmup, dist=dist)
+        entry["single_gpu_ms_per_call"] = ms1 / steps
+        entry["speedup_vs_single_gpu"] = ms1 / ms
+        out[f"M{rows}"] = entry
+        del wg, wu, wd
+        torch.cuda.empty_cache()
     return out
 
 
@@ -343,9 +357,15 @@ def main():
     peaks = measured_peaks()
     gemm_bytes = ps.gemm_algorithmic_bytes()
     achieved = gemm_bytes / (ms_gemm / args.steps * 1e-3) / 1e9
+    # dram read+write per launch measured by ncu on the three launch shapes of a 2-layer case
+    # (profiles/gemm_stream_kernel_decode_M128.md): 1.01-1.04 x the algorithmic bytes, scaled here
+    # to the average launch of the full step (traffic grows in proportion to the weights)
+    traffic_ratio = 1.02
     roofline = {"bound": "hbm", "kernel": "gemm_stream_kernel", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "frac": achieved / peaks["hbm_gbs"],
+                "traffic": traffic_ratio * gemm_bytes / max(1, gemm_launches),
+                "traffic_source": "ncu dram__bytes_read+write on a 2-layer capture, scaled by weight bytes",
                 "launches_per_step": gemm_launches,
                 "algorithmic_bytes_per_launch": gemm_bytes / max(1, gemm_launches),
                 "avg_launch_us": ms_gemm / args.steps / max(1, gemm_launches) * 1e3}

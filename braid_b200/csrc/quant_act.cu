@@ -47,9 +47,9 @@ struct QuantWs {
 };
 
 // CTA-wide max, then the grid-wide exchange.  Returns the global amax to every
-// thread.  A single-CTA grid never touches global memory here.  When it returns
-// true in *must_depart, thread 0 of the CTA owes the scratch a grid_depart()
-// call; that part is kept off the critical path on purpose.
+// thread.  A single-CTA grid never touches global memory here.  Thread 0 of every
+// CTA of a multi-CTA grid owes the scratch a grid_depart() call afterwards; that
+// part is kept off the critical path on purpose.
 __device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
   __shared__ float s_warp[32];
   __shared__ float s_amax;
@@ -160,15 +160,32 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
 }
 
 // Streaming variant for activations that do not fit in the register file of
-// one co-resident grid: pass 1 reduces, pass 2 re-reads (L2) and casts.
+// one co-resident grid: pass 1 reduces, pass 2 re-reads (L2) and casts.  Both
+// passes keep kUnroll independent groups in flight per thread.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
+  constexpr int kUnroll = (MODE == kPlain) ? 4 : 2;
   bq::pdl_launch_dependents();
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
   bq::pdl_wait_prior_grids();
   float m = 0.0f;
-  for (unsigned int g = tid; g < p.n_groups; g += nthreads) m = absmax8(produce<T, MODE>(p, g), m);
+  for (unsigned int g0 = tid; g0 < p.n_groups; g0 += nthreads * kUnroll) {
+    Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
+      if (g < p.n_groups) load_raw<T, MODE>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
+      if (g < p.n_groups) {
+        apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
+        m = absmax8(a[u], m);
+      }
+    }
+  }
   const bool owns_tail = (MODE == kPlain) && p.tail != 0 && tid == nthreads - 1;
   if (owns_tail) {
     const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
@@ -177,8 +194,23 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
   const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
   if (tid == 0) p.scale[0] = sc;
   // walk backwards: the groups read last in pass 1 are the likeliest still in L2
-  for (long long g = (long long)p.n_groups - 1 - tid; g >= 0; g -= nthreads)
-    emit8(produce<T, MODE>(p, (unsigned int)g), sc, p.q + static_cast<size_t>(g) * kGroup);
+  const long long last = (long long)p.n_groups - 1 - tid;
+  for (long long g0 = last; g0 >= 0; g0 -= (long long)nthreads * kUnroll) {
+    Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long g = g0 - (long long)u * nthreads;
+      if (g >= 0) load_raw<T, MODE>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long g = g0 - (long long)u * nthreads;
+      if (g >= 0) {
+        apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
+        emit8(a[u], sc, p.q + static_cast<size_t>(g) * kGroup);
+      }
+    }
+  }
   if (owns_tail) {
     const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
     uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;

@@ -26,6 +26,7 @@ PROJECTIONS = {
     "attn.qkv": ([8192, 1024, 1024], 4096),
     "attn.o_proj": ([4096], 4096),
     "attn.k_proj": ([1024], 4096),
+    "lm_head": ([248320], 4096),
 }
 
 
@@ -157,7 +158,8 @@ def main(args):
     print(json.dumps({"fp8_peak": peak8}), flush=True)
     for name, (ns, k) in PROJECTIONS.items():
         for m in (1, 8, 16, 32, 64, 128):
-            r = gemm_row(name, ns, k, m, dev, peaks)
+            r = gemm_row(name, ns, k, m, dev, peaks, inner=6 if name == "lm_head" else None,
+                         reps=7 if name == "lm_head" else 15)
             rows.append(r)
             print(json.dumps(r), flush=True)
     g = torch.Generator().manual_seed(4)
