@@ -283,6 +283,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--only", default=None, help="with --sweep: one projection name, at --rows")
     ap.add_argument("--no-library-arm", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -154,6 +154,15 @@ def main(args):
     out_dir = Path("gpurun_out")
     out_dir.mkdir(exist_ok=True)
     rows = []
+    only = getattr(args, "only", None)
+    if only:
+        # one projection at one row count (what the ncu captures of single kernels run):
+        # a handful of launches, no library arm
+        ns, k = PROJECTIONS[only]
+        r = gemm_row(only, ns, k, args.rows, dev, peaks, inner=4, reps=3, library=False)
+        print(json.dumps(r), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
     peak8 = fp8_library_peak(dev)
     print(json.dumps({"fp8_peak": peak8}), flush=True)
     for name, (ns, k) in PROJECTIONS.items():
