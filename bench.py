@@ -373,6 +373,11 @@ def main():
     step_bytes = gemm_bytes + ps.quant_algorithmic_bytes()
     status = Q.device_status()
 
+    # ---- the step without the 48 bf16 gate projections: this package's kernels only ----------
+    g_fp8, _ = capture(lambda: ps.step_b200(static_x, bf16_gates=False))
+    ms_fp8, _ = timed_replays(g_fp8.replay, args.steps, args.warmup, dist=None)
+    del g_fp8
+
     # ---- the same step built from the library GEMM + torch-spelling quantizer ---------------
     library = None
     if not args.no_library_arm and rank == 0:
@@ -425,6 +430,9 @@ def main():
                               "frac_of_hbm": step_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
                               "tflops": shapes.step_flops(args.rows) * args.layers / shapes.n_layers
                               / (ms_per_step * 1e-3) / 1e12},
+            "fp8_kernels_only": {"ms_per_step": ms_fp8 / args.steps,
+                                 "what": "the step without the 48 bf16 gate GEMMs (F.linear) the "
+                                         "reference keeps in bf16: 256 launches, all of this library"},
             "cpu_baseline": cpu,
             "library_baseline": library,
             "column_parallel": colpar,

@@ -129,11 +129,16 @@ class ProjectionSet:
         return total
 
     # -- the step, this package's kernels ------------------------------------------------------
-    def step_b200(self, x: torch.Tensor) -> torch.Tensor:
+    def step_b200(self, x: torch.Tensor, bf16_gates: bool = True) -> torch.Tensor:
+        """`bf16_gates=False` leaves out the two tiny bf16 projections (a, b) the reference keeps
+        in bf16: the step then contains this package's kernels only."""
         s = self.shapes
         y = x
         for ws in self.layers:
-            if "qkv" in ws:
+            if "qkv" in ws and not bf16_gates:
+                Q.project(x, ws["qkv"], ws["z"])
+                y = Q.linear(self.core, ws["out"])
+            elif "qkv" in ws:
                 qkv, z, a, b = Q.project(x, ws["qkv"], ws["z"], ws["a"], ws["b"])
                 y = Q.linear(self.core, ws["out"])
             else:
