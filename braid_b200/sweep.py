@@ -118,6 +118,43 @@ def quant_row(kind, m, cols, dev, peaks, reps=15):
             "gbs": bytes_ / (ms * 1e-3) / 1e9, "frac_hbm": bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 
 
+def mlp_block_row(m, dev, peaks, hidden=4096, inter=12288, reps=11):
+    """The whole quantized MLP block of one layer (BASELINE config 2): quantize -> gate|up GEMM ->
+    SiLU*mul fused into the quantization of the intermediate -> down GEMM, beside the reference's
+    spelling of the same block on the same GPU (torch quantizer, three `torch._scaled_mm`)."""
+    import torch.nn.functional as F
+    n_bank = max(2, (1 << 30) // (3 * hidden * inter))
+    g = torch.Generator(device=dev).manual_seed(2)
+
+    def w(n, k):
+        data = torch.randint(0, 120, (n, k), generator=g, device=dev, dtype=torch.uint8).view(Q.FP8)
+        return Q.FP8Weight(data, torch.full((1, 1), 0.01, device=dev), (n, k))
+
+    bank = [(w(inter, hidden), w(inter, hidden), w(hidden, inter)) for _ in range(n_bank)]
+    x = torch.randn(m, hidden, device=dev).to(torch.bfloat16)
+    inner = 8
+    ms = _time_graph(lambda i: Q.mlp_forward(x, *bank[i]), n_bank, inner, reps)
+
+    def lib_quant(t):
+        scale = (t.float().abs().amax() / Q.FP8_MAX).clamp(min=Q.EPS).reshape(1, 1)
+        return (t.float() / scale).clamp(-Q.FP8_MAX, Q.FP8_MAX).to(Q.FP8), scale
+
+    def lib(i):
+        wg, wu, wd = bank[i]
+        xq, sx = lib_quant(x)
+        mm = lambda a, s, ww: torch._scaled_mm(a, ww.data.t(), scale_a=s, scale_b=ww.scale,  # noqa: E731
+                                               out_dtype=torch.bfloat16)
+        h = F.silu(mm(xq, sx, wg)) * mm(xq, sx, wu)
+        hq, sh = lib_quant(h)
+        return mm(hq, sh, wd)
+
+    ms_lib = _time_graph(lib, n_bank, inner, reps)
+    weight_bytes = 3 * hidden * inter
+    return {"block": "mlp", "M": m, "us": ms * 1e3, "lib_us": ms_lib * 1e3, "speedup_vs_lib": ms_lib / ms,
+            "weight_gbs": weight_bytes / (ms * 1e-3) / 1e9,
+            "frac_hbm": weight_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "launches": 4}
+
+
 def fp8_library_peak(dev, seconds=2.0):
     """Dense FP8 peak the way the bf16 peak file was taken: `torch._scaled_mm` 8192^3, best of
     10 (burst) and back to back for `seconds` (sustained)."""
@@ -171,6 +208,10 @@ def main(args):
                          reps=7 if name == "lm_head" else 15)
             rows.append(r)
             print(json.dumps(r), flush=True)
+    for m in (1, 8, 16, 32, 64, 128):
+        r = mlp_block_row(m, dev, peaks)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
     g = torch.Generator().manual_seed(4)
     ragged = int(torch.randint(64, 1025, (16,), generator=g).sum().item())
     for name in ("mlp.gate_up", "mlp.down", "gdn.in_proj_qkv_z", "gdn.out_proj"):
