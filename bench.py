@@ -244,6 +244,31 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------
+def run_engine_compare(args):
+    """Whole-engine decode step of the reference (an install under baseline/_ref), stock and with
+    this package installed into it.  Not the headline metric: the mixers, norms and cache are the
+    reference's own code in every arm; only the FP8 projection path is swapped."""
+    root = Path(__file__).resolve().parent
+    ref = root / "baseline" / "_ref"
+    if not (ref / "braid" / "model" / "engine.py").exists():
+        print(json.dumps({"metric": "engine_decode_tokens_per_s",
+                          "unavailable": "no install of the reference under baseline/_ref"}))
+        return
+    sys.path.insert(0, str(ref))
+    sys.path.insert(0, str(root / "baseline"))
+    import ref_kernels
+    from braid_b200 import engine_dropin
+    use_kernels = ref_kernels.available()
+    if use_kernels:
+        ref_kernels.attach()
+    torch.cuda.set_device(0)
+    res = engine_dropin.compare_arms(torch.device("cuda", 0), layers=args.layers, vocab=args.vocab,
+                                     batch=args.rows, steps=args.steps, prompt_len=args.prompt_len,
+                                     use_kernels=use_kernels)
+    res = {"metric": "engine_decode_tokens_per_s", "unit": "tok/s", "n_gpus": 1, **res}
+    print(json.dumps(res), flush=True)
+
+
 def column_parallel_block(dist, rows_list, steps, warmup):
     """gate_up [2 x 12288, 4096] and down [4096, 12288] N-split over the ranks, bf16 all-gather of
     the h shards and of the output shards (NCCL over NVLink)."""
@@ -286,6 +311,11 @@ def main():
     ap.add_argument("--only", default=None, help="with --sweep: one projection name, at --rows")
     ap.add_argument("--no-library-arm", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--engine", action="store_true",
+                    help="the reference's whole graphed decode step (installed under baseline/_ref) "
+                         "stock vs on these kernels; one GPU, its own JSON line")
+    ap.add_argument("--vocab", type=int, default=248320)
+    ap.add_argument("--prompt-len", type=int, default=128)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -296,6 +326,10 @@ def main():
     if args.sweep:
         from braid_b200 import sweep
         sweep.main(args)
+        return
+
+    if args.engine:
+        run_engine_compare(args)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

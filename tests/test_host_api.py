@@ -169,3 +169,54 @@ def test_install_into_rebinds_a_reference_shaped_module():
     assert "fake_ref_mlp.fp8_matmul" in done and ref._FUSED_STATE == "active"
     w = quant.quantize_weight(torch.randn(16, 16, dtype=torch.bfloat16))
     assert adopt_weight(w).data is w.data
+
+
+# -- engine drop-in helpers (host side; the reference install is optional) ---------------------------
+def _ref_install():
+    from pathlib import Path
+    ref = Path(__file__).resolve().parent.parent / "baseline" / "_ref"
+    return ref if (ref / "braid" / "model" / "engine.py").exists() else None
+
+
+def test_text_config_is_the_9b_shape():
+    from braid_b200.engine_dropin import text_config
+    from braid_b200.projection_set import StackShapes
+    c, s = text_config(), StackShapes()
+    assert (c["hidden_size"], c["intermediate_size"], c["num_hidden_layers"]) == (s.hidden, s.intermediate, s.n_layers)
+    assert c["layer_types"].count("full_attention") == 8 and c["layer_types"][3] == "full_attention"
+    assert 2 * c["num_attention_heads"] * c["head_dim"] == s.attn_q
+    assert c["num_key_value_heads"] * c["head_dim"] == s.attn_kv
+    assert c["linear_num_value_heads"] * c["linear_value_head_dim"] == s.gdn_inner
+    assert (2 * c["linear_num_key_heads"] * c["linear_key_head_dim"]
+            + c["linear_num_value_heads"] * c["linear_value_head_dim"]) == s.gdn_qkv
+    assert text_config(layers=8, vocab=4096)["vocab_size"] == 4096
+
+
+@pytest.mark.skipif(_ref_install() is None, reason="no reference install under baseline/_ref")
+def test_random_checkpoint_runs_through_the_reference_engine_on_cpu():
+    """A CPU-sized stack of the same structure: the reference's loader validation accepts the
+    tensors and its engine decodes with every group quantized (stock torch arm)."""
+    import sys
+    ref = _ref_install()
+    sys.path.insert(0, str(ref))
+    try:
+        from braid_b200 import engine_dropin as E
+        cfg = E.text_config(layers=4, vocab=1024, hidden_size=64, intermediate_size=128,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                            linear_num_value_heads=4, linear_num_key_heads=2,
+                            linear_value_head_dim=16, linear_key_head_dim=16,
+                            rope_parameters={"rope_type": "default", "rope_theta": 1e7,
+                                             "partial_rotary_factor": 0.25, "mrope_section": [2, 1, 1],
+                                             "mrope_interleaved": True})
+        ck = E.random_checkpoint(cfg, "cpu", torch.bfloat16)
+        assert ck.config.gdn_layers == (0, 1, 2) and ck.config.attention_layers == (3,)
+        eng = E.build_engine(ck, quant="all", use_kernels=False, state_dtype=torch.float32)
+        cache = eng.allocate_cache(32, max_slots=3)
+        E.seed_cache(eng, cache, 3, 5)
+        out = eng.decode_step(torch.tensor([[1], [2], [3]]), cache.select([0, 1, 2]))
+        assert out.shape == (3, 1024) and torch.isfinite(out.float()).all()
+        assert " 3/3 " in eng.quant_report() or "fp8" in eng.quant_report()
+    finally:
+        sys.path.remove(str(ref))
+        for name in [m for m in sys.modules if m == "braid" or m.startswith("braid.")]:
+            del sys.modules[name]
