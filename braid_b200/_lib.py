@@ -34,6 +34,10 @@ SIGNATURES = {
     "bq_silu_mul_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_sigmoid_gate_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64,
                                      _vp, _vp, _vp, _sz, _vp]),
+    "bq_rmsnorm_quant": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp,
+                                _vp, _sz, _vp]),
+    "bq_gated_rmsnorm_quant": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,
+                                      _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "bq_gemm_scratch_bytes": (_sz, [_i64, _int]),
     "bq_gemm_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),

@@ -21,8 +21,9 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libbraid_b200.so"
-SOURCES = ("quant_act.cu", "gemm_w8a8.cu", "cabi.cu")
-HEADERS = (CSRC / "ptx.cuh", PKG.parent / "include" / "braid_b200.h")
+SOURCES = ("quant_act.cu", "norm_quant.cu", "gemm_w8a8.cu", "cabi.cu")
+HEADERS = (CSRC / "ptx.cuh", CSRC / "quant_device.cuh", CSRC / "grid_amax.cuh",
+           PKG.parent / "include" / "braid_b200.h")
 
 
 def nvcc_path() -> str:

@@ -112,11 +112,25 @@ def random_checkpoint(cfg_dict: dict, device, dtype: torch.dtype = torch.bfloat1
 _SAVED: dict[tuple[str, str], object] = {}
 
 
-def activate(fuse_mlp: bool = True) -> list[str]:
-    """Rebind every module of the reference that holds quant names onto this package and, with
-    `fuse_mlp`, swap `MLP.forward` (braid/model/mlp.py:34-49) for the fused four-launch form.
-    Engines must be BUILT after activating: their weights are then this package's `FP8Weight`."""
-    for name in _PATCHED:
+def _swap(mod_name: str, cls_name: str, attrs: tuple[str, ...], fn, done: list[str]) -> None:
+    cls = getattr(sys.modules[mod_name], cls_name)
+    key = (mod_name, f"{cls_name}.{attrs[0]}")
+    if key not in _SAVED:
+        _SAVED[key] = (cls_name, attrs, tuple(getattr(cls, a) for a in attrs))
+    for a in attrs:
+        setattr(cls, a, fn)
+    done.append(f"{mod_name}.{cls_name}.{attrs[0]}")
+
+
+def activate(fuse_mlp: bool = True, fuse_norms: bool = True) -> list[str]:
+    """Rebind every module of the reference that holds quant names onto this package.  With
+    `fuse_mlp`, `MLP.forward` (braid/model/mlp.py:34-49) becomes the fused four-launch form; with
+    `fuse_norms`, `DecoderLayer.forward` (braid/model/layer.py:37-60) and
+    `GatedDeltaNet._readout` (braid/model/gdn.py:373-387) become the forms whose norms run inside
+    the quantizer of the consumer.  Engines must be BUILT after activating: their weights are
+    then this package's `FP8Weight`."""
+    fuse_mlp = fuse_mlp or fuse_norms      # the fused layer hands the MLP a quantized activation
+    for name in _PATCHED + ("braid.model.layer",):
         importlib.import_module(name)
     names = integrate._REBOUND + ("FP8Weight", "quantize_weight", "maybe_quantize", "_FUSED",
                                   "_FUSED_STATE")
@@ -127,12 +141,11 @@ def activate(fuse_mlp: bool = True) -> list[str]:
                 _SAVED[(mod_name, n)] = getattr(mod, n)
     done = integrate.install_into(sys.modules["braid.model.quant"], _PATCHED[1:])
     if fuse_mlp:
-        mlp_cls = sys.modules["braid.model.mlp"].MLP
-        if ("braid.model.mlp", "MLP.forward") not in _SAVED:
-            _SAVED[("braid.model.mlp", "MLP.forward")] = (mlp_cls.forward, mlp_cls.__call__)
-        mlp_cls.forward = integrate.fused_mlp_forward
-        mlp_cls.__call__ = integrate.fused_mlp_forward
-        done.append("braid.model.mlp.MLP.forward")
+        _swap("braid.model.mlp", "MLP", ("forward", "__call__"), integrate.fused_mlp_forward, done)
+    if fuse_norms:
+        _swap("braid.model.layer", "DecoderLayer", ("forward", "__call__"),
+              integrate.fused_layer_forward, done)
+        _swap("braid.model.gdn", "GatedDeltaNet", ("_readout",), integrate.fused_gdn_readout, done)
     return done
 
 
@@ -142,8 +155,10 @@ def deactivate() -> None:
         mod = sys.modules.get(mod_name)
         if mod is None:
             continue
-        if n == "MLP.forward":
-            mod.MLP.forward, mod.MLP.__call__ = value
+        if isinstance(value, tuple) and len(value) == 3 and isinstance(value[1], tuple):
+            cls_name, attrs, originals = value
+            for a, fn in zip(attrs, originals):
+                setattr(getattr(mod, cls_name), a, fn)
         else:
             setattr(mod, n, value)
     _SAVED.clear()
@@ -230,7 +245,14 @@ def compare_arms(device, layers: int = 32, vocab: int = 248320, batch: int = 128
     through this package.  Engines are built one after another so only one is resident."""
     import gc
     ckpt = random_checkpoint(text_config(layers, vocab), device, seed=seed)
-    out: dict = {"config": {"layers": layers, "vocab": vocab, "batch": batch, "steps": steps,
+    out: dict = {"arms": {
+        "reference_fp8": "stock reference, quant=all: torch._scaled_mm + its own fused quantizer",
+        "reference_bf16": "stock reference, no quantization",
+        "b200_fp8_projections_only": "quantizer, prologues, grouped GEMMs and fused MLP from this "
+                                     "package; norms stay torch kernels",
+        "b200_fp8": "as above, plus the pre-norms and the gated readout norm fused into the "
+                    "quantizer of the sublayer they feed"},
+        "config": {"layers": layers, "vocab": vocab, "batch": batch, "steps": steps,
                             "prompt_len": prompt_len, "max_len": max_len, "state_dtype": "fp16",
                             "mixer_kernels": "reference CUDA kernels" if use_kernels else "torch path",
                             "weights": "random init N(0,0.02), 9B shape", "arm": "graphed-kvbucket"}}
@@ -253,8 +275,11 @@ def compare_arms(device, layers: int = 32, vocab: int = 248320, batch: int = 128
     run("reference_fp8", "all")
     if bf16_arm:
         run("reference_bf16", "")
-    activate()
     try:
+        activate(fuse_norms=False)
+        run("b200_fp8_projections_only", "all")
+        deactivate()
+        activate(fuse_norms=True)
         run("b200_fp8", "all")
     finally:
         deactivate()

@@ -55,3 +55,41 @@ def fused_mlp_forward(self, x):
     if not isinstance(self.gate_proj, Q.FP8Weight):
         return F.linear(F.silu(F.linear(x, self.gate_proj)) * F.linear(x, self.up_proj), self.down_proj)
     return Q.mlp_forward(x, self.gate_proj, self.up_proj, self.down_proj)
+
+
+def fused_layer_forward(self, x, cos, sin, cache=None, slots=None, positions=None, kv_len=None,
+                        attn_mask=None, slots_i32=None, seq_lens=None):
+    """Replacement for `DecoderLayer.forward` (braid/model/layer.py:37-60): each pre-norm is fused
+    into the quantizer of the sublayer it feeds, so the mixer's `project` and the MLP receive an
+    already-quantized activation.  A sublayer whose weights are not FP8 gets the plain norm.  The
+    GDN mixer also reads the normalised activation unquantized (its bf16 a/b gates,
+    braid/model/gdn.py:73-81), so that one is written out as well."""
+    eps = self.cfg.rms_norm_eps
+    if self.mixer.quantized:
+        h = Q.rms_norm_quant(x, self.input_layernorm, eps, keep_dense=self.is_gdn)
+    else:
+        h = Q.torch_rms_norm(x, self.input_layernorm, eps)
+    if self.is_gdn:
+        h = self.mixer(h, cache=cache, slots=slots, slots_i32=slots_i32, seq_lens=seq_lens)
+    else:
+        h = self.mixer(h, cos, sin, attn_mask=attn_mask, cache=cache, slots=slots,
+                       positions=positions, kv_len=kv_len, seq_lens=seq_lens)
+    x = x + h
+    if self.mlp.quantized:
+        h = Q.rms_norm_quant(x, self.post_attention_layernorm, eps)
+    else:
+        h = Q.torch_rms_norm(x, self.post_attention_layernorm, eps)
+    return x + self.mlp(h)
+
+
+def fused_gdn_readout(self, z, y, B, T, dtype):
+    """Replacement for `GatedDeltaNet._readout` (braid/model/gdn.py:373-387): the cast of the scan
+    output, the gated norm and the quantization of out_proj's input in one launch."""
+    g = self.g
+    if not isinstance(self.out_proj, Q.FP8Weight) or z.dtype != dtype:
+        core = Q.torch_rms_norm_gated(y.to(dtype).reshape(-1, g.head_dim), z.reshape(-1, g.head_dim),
+                                      self.norm, self.cfg.rms_norm_eps)
+        return Q.linear(core.reshape(B, T, g.inner_size), self.out_proj)
+    core = Q.gated_rms_norm_quant(y.reshape(B, T, g.inner_size), z.reshape(B, T, g.inner_size),
+                                  self.norm, self.cfg.rms_norm_eps, g.head_dim)
+    return Q.linear(core, self.out_proj)

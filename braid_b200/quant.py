@@ -415,6 +415,112 @@ def sigmoid_gate_quant(o: torch.Tensor, gate: torch.Tensor,
     return q.reshape(*o.shape[:-1], cols), scale
 
 
+# ---------------------------------------------------------------------------
+# norms fused into the quantizer of their consumer
+# ---------------------------------------------------------------------------
+class QuantizedActivation:
+    """An activation that arrives already quantized: e4m3 codes `[rows, K]`, its `[1, 1]` scale
+    and, when a consumer still needs it unquantized (bf16 weights in a mixed `project`), the dense
+    tensor.  Carries `shape` / `dtype` / `device` of the activation it stands for, which is all
+    the reference's mixers read from their input before handing it to `project`
+    (braid/model/gdn.py:239-255, braid/model/attention.py:168-173)."""
+
+    __slots__ = ("q", "scale", "dense", "shape", "dtype", "device")
+
+    def __init__(self, q, scale, shape, dtype, dense=None):
+        self.q, self.scale, self.dense = q, scale, dense
+        self.shape, self.dtype, self.device = torch.Size(shape), dtype, q.device
+
+    def dim(self) -> int:
+        return len(self.shape)
+
+    def require_dense(self) -> torch.Tensor:
+        if self.dense is None:
+            raise ValueError("this activation was produced without its dense form "
+                             "(ask the norm for it: keep_dense=True)")
+        return self.dense
+
+
+def torch_rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    """The reference's spelling (braid/model/norm.py:31-45): fp32 norm, one cast back."""
+    return F.rms_norm(x.float(), (x.shape[-1],), gamma, eps).type_as(x)
+
+
+def torch_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, gamma: torch.Tensor,
+                         eps: float) -> torch.Tensor:
+    """The reference's gated form (braid/model/norm.py:48-71): normalise, round, gamma, silu(gate)."""
+    dt = x.dtype
+    xf = F.rms_norm(x.float(), (x.shape[-1],), None, eps)
+    return ((gamma * xf.to(dt)) * F.silu(gate.float())).to(dt)
+
+
+def rms_norm_quant(x: torch.Tensor, gamma: torch.Tensor, eps: float,
+                   keep_dense: bool = False) -> QuantizedActivation:
+    """`quantize_act(rms_norm(x, gamma, eps))` in one launch (braid/model/layer.py:49,59 feeding
+    `project` / the MLP).  Bit-identical to the two steps; inputs the kernel does not take (more
+    rows than fit on the device at once, odd strides) run the two steps."""
+    _check_cuda(x, "rms_norm_quant")
+    K = x.shape[-1]
+    code = _DTYPE_CODE.get(x.dtype)
+    if code is None:
+        raise ValueError(f"activation must be fp32, bf16 or fp16, got {x.dtype}")
+    if gamma.dtype is not torch.float32 or gamma.numel() != K:
+        raise ValueError("gamma must be an fp32 vector of the activation's width")
+    if not _quantizers_off() and x.numel() and K % 4 == 0 and gamma.is_contiguous():
+        lib = _require_lib()
+        x2 = _as_rows(x, K)
+        rows = x2.shape[0]
+        q = torch.empty((rows, K), dtype=FP8, device=x.device)
+        scale = torch.empty((1, 1), dtype=torch.float32, device=x.device)
+        h = torch.empty((rows, K), dtype=x.dtype, device=x.device) if keep_dense else None
+        rc = lib.bq_rmsnorm_quant(x2.data_ptr(), code, rows, K, x2.stride(0), gamma.data_ptr(),
+                                  float(eps), h.data_ptr() if keep_dense else None, K, q.data_ptr(),
+                                  scale.data_ptr(), _take_slot(x.device), 16, _stream_ptr(x.device))
+        if rc not in (_lib.BQ_ERR_TOO_LARGE, _lib.BQ_ERR_UNSUPPORTED):
+            _lib.check(rc, "rms_norm_quant")
+            return QuantizedActivation(q, scale, x.shape, x.dtype,
+                                       h.reshape(x.shape) if keep_dense else None)
+    h = torch_rms_norm(x, gamma, eps)
+    q, scale = quantize_act(h.reshape(-1, K))
+    return QuantizedActivation(q, scale, x.shape, x.dtype, h if keep_dense else None)
+
+
+def gated_rms_norm_quant(y: torch.Tensor, z: torch.Tensor, gamma: torch.Tensor, eps: float,
+                         head_dim: int) -> QuantizedActivation:
+    """`quantize_act(rms_norm_gated(y.to(z.dtype), z, gamma, eps))` in one launch: the GDN readout
+    feeding out_proj (braid/model/gdn.py:373-387).  `y` is `[..., H, D]` or `[..., H*D]`, the fp32
+    scan output or already of `z`'s type; `z` is `[..., H*D]`.  Returns the `[..., H*D]` activation."""
+    _check_cuda(z, "gated_rms_norm_quant")
+    width = z.shape[-1]
+    heads = width // head_dim
+    lead = z.shape[:-1]
+    code = _DTYPE_CODE.get(z.dtype)
+    ycode = _DTYPE_CODE.get(y.dtype)
+    if code is None or ycode is None or (y.dtype != z.dtype and y.dtype is not torch.float32):
+        raise ValueError("z must be fp32/bf16/fp16 and y either fp32 or z's type")
+    if gamma.dtype is not torch.float32 or gamma.numel() != head_dim:
+        raise ValueError("gamma must be an fp32 vector of head_dim entries")
+    y2 = _as_rows(y.reshape(*lead, width) if y.shape[-1] != width else y, width)
+    z2 = _as_rows(z, width)
+    rows = z2.shape[0]
+    if (not _quantizers_off() and rows and head_dim == 128 and heads * head_dim == width
+            and heads <= 64 and gamma.is_contiguous()):
+        lib = _require_lib()
+        q = torch.empty((rows, width), dtype=FP8, device=z.device)
+        scale = torch.empty((1, 1), dtype=torch.float32, device=z.device)
+        rc = lib.bq_gated_rmsnorm_quant(y2.data_ptr(), ycode, y2.stride(0), z2.data_ptr(), code,
+                                        z2.stride(0), gamma.data_ptr(), float(eps), rows, heads,
+                                        head_dim, q.data_ptr(), scale.data_ptr(),
+                                        _take_slot(z.device), 16, _stream_ptr(z.device))
+        if rc not in (_lib.BQ_ERR_TOO_LARGE, _lib.BQ_ERR_UNSUPPORTED):
+            _lib.check(rc, "gated_rms_norm_quant")
+            return QuantizedActivation(q, scale, (*lead, width), z.dtype)
+    core = torch_rms_norm_gated(y2.to(z.dtype).reshape(-1, head_dim), z2.reshape(-1, head_dim),
+                                gamma, eps).reshape(rows, width)
+    q, scale = quantize_act(core)
+    return QuantizedActivation(q, scale, (*lead, width), z.dtype)
+
+
 def _as_rows(t: torch.Tensor, cols: int) -> torch.Tensor:
     """A `[rows, cols]` view with a contiguous last axis and one row stride (copy if needed)."""
     if t.dim() == 2 and t.stride(1) == 1:
@@ -598,6 +704,8 @@ def linear_fused(a: torch.Tensor, weights: Sequence[FP8Weight], *, mode: str = "
 def fp8_linear(x: torch.Tensor, w: FP8Weight) -> torch.Tensor:
     """`F.linear(x, w)` for a single call site; leading dims preserved (braid/model/quant.py:244-252)."""
     *lead, K = x.shape
+    if isinstance(x, QuantizedActivation):
+        return fp8_matmul(x.q, x.scale, w, out_dtype=x.dtype).reshape(*lead, w.shape[0])
     x2 = x.reshape(-1, K)
     fused = linear_fused(x2, (w,)) if x2.is_cuda else None
     if fused is not None:
@@ -608,7 +716,9 @@ def fp8_linear(x: torch.Tensor, w: FP8Weight) -> torch.Tensor:
 
 def linear(x: torch.Tensor, w: torch.Tensor | FP8Weight) -> torch.Tensor:
     """Dispatch on the weight's type (braid/model/quant.py:255-257)."""
-    return fp8_linear(x, w) if isinstance(w, FP8Weight) else F.linear(x, w)
+    if isinstance(w, FP8Weight):
+        return fp8_linear(x, w)
+    return F.linear(x.require_dense() if isinstance(x, QuantizedActivation) else x, w)
 
 
 def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.Tensor]:
@@ -618,23 +728,28 @@ def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.T
     weights of the call go through one grouped launch; weights left in bf16 take
     `F.linear` untouched, so mixed sets (GDN's qkv/z with its bf16 a/b gates) work.
     """
+    pre = x if isinstance(x, QuantizedActivation) else None
     if not any(isinstance(w, FP8Weight) for w in weights):
-        return [F.linear(x, w) for w in weights]
+        dense = pre.require_dense() if pre is not None else x
+        return [F.linear(dense, w) for w in weights]
     *lead, K = x.shape
-    x2 = x.reshape(-1, K)
     fp8 = [w for w in weights if isinstance(w, FP8Weight)]
-    fused = linear_fused(x2, fp8) if x2.is_cuda else None
-    if fused is not None:
-        ys = iter(fused[0])
+    if pre is not None:
+        ys = iter(fp8_matmul_grouped(pre.q, pre.scale, fp8, out_dtype=pre.dtype))
     else:
-        xq, sx = quantize_act(x2)
-        ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
+        x2 = x.reshape(-1, K)
+        fused = linear_fused(x2, fp8) if x2.is_cuda else None
+        if fused is not None:
+            ys = iter(fused[0])
+        else:
+            xq, sx = quantize_act(x2)
+            ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
     out = []
     for w in weights:
         if isinstance(w, FP8Weight):
             out.append(next(ys).reshape(*lead, w.shape[0]))
         else:
-            out.append(F.linear(x, w))
+            out.append(F.linear(pre.require_dense() if pre is not None else x, w))
     return out
 
 
@@ -659,12 +774,15 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     the same primitives.
     """
     *lead, K = x.shape
-    x2 = x.reshape(-1, K)
-    M = x2.shape[0]
+    pre = x if isinstance(x, QuantizedActivation) else None
+    x2 = None if pre is not None else x.reshape(-1, K)
+    M = pre.q.shape[0] if pre is not None else x2.shape[0]
     I = gate_proj.shape[0]
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     halves = (gu[:, :I], gu[:, I:])
-    if linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
+    if pre is not None:
+        fp8_matmul_grouped(pre.q, pre.scale, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
+    elif linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
         xq, sx = quantize_act(x2)
         fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
     fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1])

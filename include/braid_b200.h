@@ -139,6 +139,50 @@ int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t ro
                           void* q_out, float* scale_out, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * RMSNorm fused into the quantizer: h = T(gamma * (rstd * x)), rstd = rsqrt(mean(x^2) + eps),
+ * computed in fp32 from the fp32-widened input with ONE rounding to the activation type T,
+ * then amax / scale / e4m3 codes of h as bq_quantize_act produces them.  The sum of squares
+ * follows the reduction order of the kernel torch runs for `F.rms_norm` on a CUDA device, so h,
+ * the scale and the codes are bit-identical to the reference's two steps.
+ *
+ * Replaces: braid/model/norm.py:31-45 (`rms_norm`) at braid/model/layer.py:49 and :59,
+ * together with the `quantize_act` of the consumer (`project` at braid/model/gdn.py:254 and
+ * braid/model/attention.py:173; braid/model/mlp.py:45).
+ *
+ *   x        device, [rows, cols] of `dtype`, row stride ld_x (elements); cols % 4 == 0,
+ *            cols <= 8192; rows are limited to what is co-resident on the device
+ *            (one 128-thread CTA per row, BQ_ERR_TOO_LARGE beyond that)
+ *   gamma    device, cols floats: the EFFECTIVE gamma (1 + W already folded, loader.py:196-199)
+ *   h_out    device or NULL: the normalised activation in `dtype`, row stride ld_h — needed
+ *            only when a consumer reads it unquantized (the bf16 a/b gates of the GDN layer)
+ *   q_out    device, rows*cols bytes, contiguous
+ */
+int bq_rmsnorm_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                     const float* gamma, float eps, void* h_out, int64_t ld_h, void* q_out,
+                     float* scale_out, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Gated RMSNorm of the GDN readout fused into the quantizer of out_proj's input:
+ *   core = T(y);  xn = T(rstd * core) per 128-wide head;  h = T((gamma * xn) * silu(float(z)))
+ * with the fp32 arithmetic and the three roundings of the reference's spelling, then amax /
+ * scale / codes of h.  `y` may be the fp32 scan output (rounded to T first, as the reference
+ * does) or already of type T.
+ *
+ * Replaces: braid/model/gdn.py:383-387 (`_readout`: `y.to(dtype)`, `rms_norm_gated`
+ * braid/model/norm.py:48-71, and the `quantize_act` inside `linear(core, out_proj)`).
+ *
+ *   y        device, [rows, heads*head_dim] of y_dtype (BQ_DTYPE_F32 or `dtype`), stride ld_y
+ *   z        device, [rows, heads*head_dim] of `dtype`, stride ld_z
+ *   gamma    device, head_dim floats (stored directly: no 1 + W for the gated norm)
+ *   head_dim must be 128; heads <= 64
+ *   q_out    device, rows*heads*head_dim bytes, contiguous [rows, heads*head_dim]
+ */
+int bq_gated_rmsnorm_quant(const void* y, int y_dtype, int64_t ld_y, const void* z, int dtype,
+                           int64_t ld_z, const float* gamma, float eps, int64_t rows, int64_t heads,
+                           int64_t head_dim, void* q_out, float* scale_out, void* ws,
+                           size_t ws_bytes, void* stream);
+
+/*
  * Bytes of scratch the GEMM entry points can use for a problem of this size on
  * the current device.  16 bytes (just the status word) always work and select
  * the cluster kernel, which is the default; with the size returned here

@@ -67,12 +67,13 @@ def _prefilled(E, eng, rows):
     return cache
 
 
+@pytest.mark.parametrize("fuse_norms", [True, False], ids=["norms_fused", "norms_torch"])
 @pytest.mark.parametrize("quant", ["mlp", "attn", "gdn", "head", "all"])
-def test_every_quant_group_captures_and_replays_identically(Q, ref_engine_env, quant):
+def test_every_quant_group_captures_and_replays_identically(Q, ref_engine_env, quant, fuse_norms):
     E, ckpt, use_kernels = ref_engine_env
     import importlib
     graph_mod = importlib.import_module("braid.model.graph")
-    E.activate()
+    E.activate(fuse_norms=fuse_norms)
     eng = cache = dec = None
     try:
         eng = E.build_engine(ckpt, quant=quant, use_kernels=use_kernels)
@@ -115,8 +116,9 @@ def _truncated(ckpt, layers):
 def _first_step_logits(E, ckpt, use_kernels):
     tokens = torch.arange(100, 100 + B, device="cuda")[:, None]
     logits = {}
-    for name, quant, ours in (("stock", "all", False), ("bf16", "", False), ("b200", "all", True)):
-        E.activate() if ours else E.deactivate()
+    for name, quant, ours in (("stock", "all", False), ("bf16", "", False), ("b200", "all", True),
+                              ("b200_norms_torch", "all", True)):
+        E.activate(fuse_norms=(name == "b200")) if ours else E.deactivate()
         eng = E.build_engine(ckpt, quant=quant, use_kernels=use_kernels)
         cache = _prefilled(E, eng, B)
         logits[name] = eng.decode_step(tokens, cache.select(list(range(B)))).clone()
@@ -141,7 +143,11 @@ def test_engine_on_these_kernels_tracks_the_stock_engine(Q, ref_engine_env):
     assert near["cosine"] > 0.999 and near["rel_l2"] < 0.05, near
     assert near["argmax_match"] == 1.0, near
 
+    # fusing the norms changes no bit anywhere in the engine
+    assert torch.equal(one["b200"], one["b200_norms_torch"])
+
     deep = _first_step_logits(E, ckpt, use_kernels)
+    assert torch.equal(deep["b200"], deep["b200_norms_torch"])
     ours_vs_stock = E.logits_agreement(deep["b200"], deep["stock"])
     stock_vs_bf16 = E.logits_agreement(deep["stock"], deep["bf16"])
     ours_vs_bf16 = E.logits_agreement(deep["b200"], deep["bf16"])
@@ -155,9 +161,19 @@ def test_activate_is_reversible(Q, ref_engine_env):
     rq = importlib.import_module("braid.model.quant")
     mlp = importlib.import_module("braid.model.mlp")
     E.deactivate()
-    stock = (rq.quantize_act, rq.fp8_matmul, mlp.fp8_matmul, mlp.MLP.forward, rq.FP8Weight)
+    layer = importlib.import_module("braid.model.layer")
+    gdn = importlib.import_module("braid.model.gdn")
+
+    def state():
+        return (rq.quantize_act, rq.fp8_matmul, mlp.fp8_matmul, mlp.MLP.forward, rq.FP8Weight,
+                layer.DecoderLayer.forward, layer.DecoderLayer.__call__, gdn.GatedDeltaNet._readout)
+
+    stock = state()
     done = E.activate()
     assert "braid.model.mlp.MLP.forward" in done and rq.fp8_matmul is Q.fp8_matmul
+    assert "braid.model.layer.DecoderLayer.forward" in done
+    assert "braid.model.gdn.GatedDeltaNet._readout" in done
     assert mlp.fp8_matmul is Q.fp8_matmul and rq.FP8Weight is Q.FP8Weight
+    assert all(a is not b for a, b in zip(state(), stock))
     E.deactivate()
-    assert (rq.quantize_act, rq.fp8_matmul, mlp.fp8_matmul, mlp.MLP.forward, rq.FP8Weight) == stock
+    assert state() == stock
