@@ -110,6 +110,30 @@ def quant_row(kind, m, cols, dev, peaks, reps=15):
         xs = [torch.randn(m, 2 * cols, device=dev).to(torch.bfloat16) for _ in range(n_bank)]
         fn = lambda i: Q.silu_mul_quant(xs[i][:, :cols], xs[i][:, cols:])  # noqa: E731
         bytes_ = 5 * m * cols
+    elif kind in ("rms_norm", "rms_norm_dense"):
+        xs = [torch.randn(m, cols, device=dev).to(torch.bfloat16) for _ in range(n_bank)]
+        gamma = 1.0 + 0.02 * torch.randn(cols, device=dev)
+        dense = kind == "rms_norm_dense"
+        fn = lambda i: Q.rms_norm_quant(xs[i], gamma, 1e-6, keep_dense=dense).q  # noqa: E731
+        bytes_ = (5 if dense else 3) * m * cols
+    elif kind == "gated_rms_norm":
+        xs = [(torch.randn(m, cols, device=dev), torch.randn(m, cols, device=dev).to(torch.bfloat16))
+              for _ in range(n_bank)]
+        gamma = 1.0 + 0.02 * torch.randn(128, device=dev)
+        fn = lambda i: Q.gated_rms_norm_quant(xs[i][0], xs[i][1], gamma, 1e-6, 128).q  # noqa: E731
+        bytes_ = 7 * m * cols
+    elif kind in ("rms_norm_torch", "gated_rms_norm_torch"):
+        # the reference's spelling on the same GPU: norm as torch kernels, then this package's quantizer
+        xs = [(torch.randn(m, cols, device=dev).to(torch.bfloat16),
+               torch.randn(m, cols, device=dev).to(torch.bfloat16)) for _ in range(n_bank)]
+        if kind == "rms_norm_torch":
+            gamma = 1.0 + 0.02 * torch.randn(cols, device=dev)
+            fn = lambda i: Q.quantize_act(Q.torch_rms_norm(xs[i][0], gamma, 1e-6))  # noqa: E731
+        else:
+            gamma = 1.0 + 0.02 * torch.randn(128, device=dev)
+            fn = lambda i: Q.quantize_act(Q.torch_rms_norm_gated(  # noqa: E731
+                xs[i][0].reshape(-1, 128), xs[i][1].reshape(-1, 128), gamma, 1e-6).reshape(m, cols))
+        bytes_ = 3 * m * cols
     else:
         raise ValueError(kind)
     inner = max(8, min(128, int(5e8 // bytes_)))
@@ -192,6 +216,17 @@ def main(args):
     out_dir.mkdir(exist_ok=True)
     rows = []
     only = getattr(args, "only", None)
+    if only in ("rms_norm", "rms_norm_dense", "gated_rms_norm"):
+        print(json.dumps(quant_row(only, args.rows, 4096, dev, peaks, reps=3)), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
+    if only == "norms":
+        for kind in ("rms_norm", "rms_norm_dense", "rms_norm_torch", "gated_rms_norm",
+                     "gated_rms_norm_torch"):
+            for m in (1, 16, 128):
+                print(json.dumps(quant_row(kind, m, 4096, dev, peaks)), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
     if only:
         # one projection at one row count (what the ncu captures of single kernels run):
         # a handful of launches, no library arm
@@ -230,5 +265,10 @@ def main(args):
         r = quant_row("silu_mul", m, 12288, dev, peaks)
         rows.append(r)
         print(json.dumps(r), flush=True)
+    for kind in ("rms_norm", "rms_norm_dense", "rms_norm_torch", "gated_rms_norm", "gated_rms_norm_torch"):
+        for m in (1, 16, 128):
+            r = quant_row(kind, m, 4096, dev, peaks)
+            rows.append(r)
+            print(json.dumps(r), flush=True)
     (out_dir / "sweep.json").write_text(json.dumps({"fp8_peak": peak8, "rows": rows}, indent=1))
     print(json.dumps({"device_status": Q.device_status()}), flush=True)
