@@ -54,6 +54,10 @@ struct Segment {
   const float* sw;     // device: weight dequant scale
   void* y;             // device: output base of this segment
   long long ldy;       // row stride of y, elements
+  const void* res;     // stream kernel: optional residual [M, n] of the output type, added after
+                       // the output has been rounded to that type (two roundings, as the separate
+                       // GEMM and add kernels give)
+  long long ld_res;
   int n;               // weight rows (output columns) of this segment
   int tile_begin;      // tile kernel: index of the segment's first tile
   int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
@@ -166,15 +170,54 @@ struct EpilogueArgs {
   void* y;
   long long ldy;
   int out_dtype;
+  const void* res;
+  long long ld_res;
 };
+
+// Four residual values of the output type, as raw bits (16 bytes cover the widest case).
+__device__ __forceinline__ uint4 load_res4(const void* res, long long idx, int out_dtype) {
+  uint4 r = make_uint4(0u, 0u, 0u, 0u);
+  if (out_dtype == BQ_DTYPE_F32) {
+    r = __ldg(reinterpret_cast<const uint4*>(static_cast<const float*>(res) + idx));
+  } else {
+    const uint2 h = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(res) + idx));
+    r.x = h.x; r.y = h.y;
+  }
+  return r;
+}
+
+// out = T(float(T(v)) + float(res)): the GEMM's own rounding, then the add's.
+__device__ __forceinline__ float4 add_res4(float4 v, uint4 raw, int out_dtype) {
+  if (out_dtype == BQ_DTYPE_BF16) {
+    const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    v.x = __bfloat162float(__float2bfloat16_rn(v.x)) + __bfloat162float(r0.x);
+    v.y = __bfloat162float(__float2bfloat16_rn(v.y)) + __bfloat162float(r0.y);
+    v.z = __bfloat162float(__float2bfloat16_rn(v.z)) + __bfloat162float(r1.x);
+    v.w = __bfloat162float(__float2bfloat16_rn(v.w)) + __bfloat162float(r1.y);
+  } else if (out_dtype == BQ_DTYPE_F16) {
+    const __half2 r0 = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 r1 = *reinterpret_cast<const __half2*>(&raw.y);
+    v.x = __half2float(__float2half_rn(v.x)) + __half2float(r0.x);
+    v.y = __half2float(__float2half_rn(v.y)) + __half2float(r0.y);
+    v.z = __half2float(__float2half_rn(v.z)) + __half2float(r1.x);
+    v.w = __half2float(__float2half_rn(v.w)) + __half2float(r1.y);
+  } else {
+    // intrinsics: a plain + would be contracted with the scaling multiply into one fma
+    v.x = __fadd_rn(v.x, __uint_as_float(raw.x)); v.y = __fadd_rn(v.y, __uint_as_float(raw.y));
+    v.z = __fadd_rn(v.z, __uint_as_float(raw.z)); v.w = __fadd_rn(v.w, __uint_as_float(raw.w));
+  }
+  return v;
+}
 
 // Sums the SPLIT partial tiles of this CTA's rows in rank order (fixed order:
 // the result does not depend on timing) and stores them.  Every thread asks
 // for all the partials of a batch of rows before it uses any of them, so the
 // remote shared-memory latency is paid once per batch, not once per load.
-template <int SPLIT>
+template <int SPLIT, bool RES>
 __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
-  constexpr int kRows = 16 / SPLIT;          // rows in flight per thread
+  // rows in flight per thread (half as many when residual values are held as well)
+  constexpr int kRows = (RES && SPLIT < 8) ? 8 / SPLIT : 16 / SPLIT;
   constexpr int kWarps = 8;
   const int n4 = e.lane * 4;                 // 4 consecutive output columns
   for (int m0 = e.m_begin + e.warp; m0 < e.m_end; m0 += kWarps * kRows) {
@@ -193,6 +236,15 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
         }
       }
     }
+    uint4 rraw[RES ? kRows : 1];
+    if constexpr (RES) {
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) {
+        const int m = m0 + i * kWarps;
+        if (m < e.m_end && e.col_ok)
+          rraw[i] = load_res4(e.res, (long long)m * e.ld_res + e.row0 + n4, e.out_dtype);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < kRows; ++i) {
       const int m = m0 + i * kWarps;
@@ -203,6 +255,9 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
           acc.x += v[i][r].x; acc.y += v[i][r].y; acc.z += v[i][r].z; acc.w += v[i][r].w;
         }
         acc.x *= e.scale; acc.y *= e.scale; acc.z *= e.scale; acc.w *= e.scale;
+        if constexpr (RES) {
+          if (e.col_ok) acc = add_res4(acc, rraw[i], e.out_dtype);
+        }
         if (e.col_ok) store_out4(e.y, (long long)m * e.ldy + e.row0 + n4, e.out_dtype, acc);
       }
     }
@@ -533,12 +588,21 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const uint32_t part_addr = smem_u32(part);
     const int peer0 = group * split;
     const EpilogueArgs ea{part, part_addr, peer0, m_begin, m_end, warp, lane, row0, scale, col_ok,
-                          seg.y, seg.ldy, p.out_dtype};
-    switch (split) {
-      case 1: reduce_store<1>(ea); break;
-      case 2: reduce_store<2>(ea); break;
-      case 4: reduce_store<4>(ea); break;
-      default: reduce_store<8>(ea); break;
+                          seg.y, seg.ldy, p.out_dtype, seg.res, seg.ld_res};
+    if (seg.res == nullptr) {
+      switch (split) {
+        case 1: reduce_store<1, false>(ea); break;
+        case 2: reduce_store<2, false>(ea); break;
+        case 4: reduce_store<4, false>(ea); break;
+        default: reduce_store<8, false>(ea); break;
+      }
+    } else {
+      switch (split) {
+        case 1: reduce_store<1, true>(ea); break;
+        case 2: reduce_store<2, true>(ea); break;
+        case 4: reduce_store<4, true>(ea); break;
+        default: reduce_store<8, true>(ea); break;
+      }
     }
   }
   // nobody leaves while a peer may still read its staging buffer
@@ -1544,7 +1608,8 @@ namespace {
 int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
                 const void* const* wq, const float* const* sw, void* const* y, const int64_t* N,
                 const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
-                const FuseParams* fuse) {
+                const FuseParams* fuse, const void* const* res = nullptr,
+                const int64_t* ld_res = nullptr) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
@@ -1562,6 +1627,12 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   }
   const bool stream_path = M <= g_opt_stream_max_m;
   if (fuse && !stream_path) return kErrUnsupported;   // the fused form exists for the decode regime
+  if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
+    if (!stream_path || ld_res == nullptr) return kErrUnsupported;
+    for (int i = 0; i < n_seg; ++i)
+      if (res[i] && (ld_res[i] < N[i] || ld_res[i] % 4 || !aligned_to(res[i], out_align)))
+        return kErrUnsupported;
+  }
   if (int rc = configure_once()) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
@@ -1590,6 +1661,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.seg[i].sw = sw[i];
     p.seg[i].y = y[i];
     p.seg[i].ldy = ldy[i];
+    p.seg[i].res = res ? res[i] : nullptr;
+    p.seg[i].ld_res = res ? ld_res[i] : 0;
     p.seg[i].n = (int)N[i];
     p.seg[i].tile_begin = tiles;
     const long long nt = (N[i] + tile_n - 1) / tile_n;
@@ -1603,7 +1676,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    if (!fuse && g_opt_decode_kernel != 1) {
+    if (!fuse && !res && g_opt_decode_kernel != 1) {
       const size_t need = persist_scratch_bytes(device_sms(), n_seg, mma_n);
       if (ws_bytes >= need) return launch_persist(tm_x, maps, p, ws, stream);
       if (g_opt_decode_kernel == 2) return kErrWorkspace;
@@ -1676,6 +1749,22 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
   const int64_t ldys[1] = {ldy};
   return bq_gemm_w8a8_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes,
                               stream);
+}
+
+extern "C" int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const float* sw,
+                                     const void* residual, int64_t ld_res, void* y, int out_dtype,
+                                     int64_t M, int64_t N, int64_t K, int64_t ldy, void* ws,
+                                     size_t ws_bytes, void* stream) {
+  if (residual == nullptr) return kErrBadArg;
+  const void* wqs[1] = {wq};
+  const float* sws[1] = {sw};
+  void* ys[1] = {y};
+  const int64_t Ns[1] = {N};
+  const int64_t ldys[1] = {ldy};
+  const void* rs[1] = {residual};
+  const int64_t ldrs[1] = {ld_res};
+  return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes, stream,
+                     nullptr, rs, ldrs);
 }
 
 #ifdef BQ_PHASES

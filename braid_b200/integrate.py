@@ -49,12 +49,14 @@ def adopt_weight(w) -> Q.FP8Weight:
     return Q.FP8Weight(data=w.data, scale=w.scale, shape=tuple(w.shape))
 
 
-def fused_mlp_forward(self, x):
-    """Replacement for `MLP.forward` (braid/model/mlp.py:34-49): quantized branch in 4 launches."""
+def fused_mlp_forward(self, x, residual=None):
+    """Replacement for `MLP.forward` (braid/model/mlp.py:34-49): quantized branch in 4 launches;
+    `residual`, if given, is added in the epilogue of the down projection."""
     import torch.nn.functional as F
     if not isinstance(self.gate_proj, Q.FP8Weight):
-        return F.linear(F.silu(F.linear(x, self.gate_proj)) * F.linear(x, self.up_proj), self.down_proj)
-    return Q.mlp_forward(x, self.gate_proj, self.up_proj, self.down_proj)
+        y = F.linear(F.silu(F.linear(x, self.gate_proj)) * F.linear(x, self.up_proj), self.down_proj)
+        return y if residual is None else residual + y
+    return Q.mlp_forward(x, self.gate_proj, self.up_proj, self.down_proj, residual=residual)
 
 
 def fused_layer_forward(self, x, cos, sin, cache=None, slots=None, positions=None, kv_len=None,
@@ -63,22 +65,27 @@ def fused_layer_forward(self, x, cos, sin, cache=None, slots=None, positions=Non
     into the quantizer of the sublayer it feeds, so the mixer's `project` and the MLP receive an
     already-quantized activation.  A sublayer whose weights are not FP8 gets the plain norm.  The
     GDN mixer also reads the normalised activation unquantized (its bf16 a/b gates,
-    braid/model/gdn.py:73-81), so that one is written out as well."""
+    braid/model/gdn.py:73-81), so that one is written out as well.  Both residual adds
+    (layer.py:57,60) ride in the epilogue of the projection that produces the summand: the
+    mixer's out_proj / o_proj through `residual_into`, the MLP's down_proj directly."""
     eps = self.cfg.rms_norm_eps
     if self.mixer.quantized:
         h = Q.rms_norm_quant(x, self.input_layernorm, eps, keep_dense=self.is_gdn)
     else:
         h = Q.torch_rms_norm(x, self.input_layernorm, eps)
-    if self.is_gdn:
-        h = self.mixer(h, cache=cache, slots=slots, slots_i32=slots_i32, seq_lens=seq_lens)
-    else:
-        h = self.mixer(h, cos, sin, attn_mask=attn_mask, cache=cache, slots=slots,
-                       positions=positions, kv_len=kv_len, seq_lens=seq_lens)
-    x = x + h
+    # the residual add rides in the epilogue of the mixer's output projection when that is FP8
+    out_w = self.mixer.out_proj if self.is_gdn else self.mixer.o_proj
+    with Q.residual_into(out_w if isinstance(out_w, Q.FP8Weight) else None, x) as slot:
+        if self.is_gdn:
+            h = self.mixer(h, cache=cache, slots=slots, slots_i32=slots_i32, seq_lens=seq_lens)
+        else:
+            h = self.mixer(h, cos, sin, attn_mask=attn_mask, cache=cache, slots=slots,
+                           positions=positions, kv_len=kv_len, seq_lens=seq_lens)
+    x = h if slot.taken else x + h
     if self.mlp.quantized:
         h = Q.rms_norm_quant(x, self.post_attention_layernorm, eps)
-    else:
-        h = Q.torch_rms_norm(x, self.post_attention_layernorm, eps)
+        return fused_mlp_forward(self.mlp, h, residual=x)
+    h = Q.torch_rms_norm(x, self.post_attention_layernorm, eps)
     return x + self.mlp(h)
 
 

@@ -555,12 +555,37 @@ def _check_gemm_inputs(xq: torch.Tensor, sx: torch.Tensor) -> None:
 
 
 def fp8_matmul(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight,
-               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+               out_dtype: torch.dtype = torch.bfloat16,
+               residual: torch.Tensor | None = None) -> torch.Tensor:
     """The GEMM alone on an already-quantized `[M, K]` activation (braid/model/quant.py:232-241).
 
-    `(xq * sx) @ (w.data * w.scale)^T`, fp32 accumulation, `out_dtype` result.
+    `(xq * sx) @ (w.data * w.scale)^T`, fp32 accumulation, `out_dtype` result.  With `residual`
+    (`[M, N]`, `out_dtype`) the result is `residual + that`, the add running in the GEMM's
+    epilogue with the two roundings of the separate kernels (decode sizes; larger M adds after).
     """
-    return fp8_matmul_grouped(xq, sx, (w,), out_dtype=out_dtype)[0]
+    if residual is None:
+        return fp8_matmul_grouped(xq, sx, (w,), out_dtype=out_dtype)[0]
+    _check_gemm_inputs(xq, sx)
+    M, K = xq.shape
+    N = w.data.shape[0]
+    if residual.shape != (M, N) or residual.dtype != out_dtype or not residual.is_cuda:
+        raise ValueError(f"residual must be a [{M}, {N}] {out_dtype} CUDA tensor")
+    code = _DTYPE_CODE.get(out_dtype)
+    if (M == 0 or code is None or residual.stride(1) != 1 or w.data.shape[1] != K
+            or not w.data.is_contiguous()):
+        return residual + fp8_matmul_grouped(xq, sx, (w,), out_dtype=out_dtype)[0]
+    lib = _require_lib()
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    y = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    ws_ptr, ws_bytes = _gemm_scratch_for(xq.device, M, 1)
+    rc = lib.bq_gemm_w8a8_residual(xq.data_ptr(), w.data.data_ptr(), sx.data_ptr(), w.scale.data_ptr(),
+                                   residual.data_ptr(), residual.stride(0), y.data_ptr(), code,
+                                   M, N, K, N, ws_ptr, ws_bytes, _stream_ptr(xq.device))
+    if rc == _lib.BQ_ERR_UNSUPPORTED:
+        return residual + fp8_matmul_grouped(xq, sx, (w,), out_dtype=out_dtype)[0]
+    _lib.check(rc, "fp8_matmul")
+    return y
 
 
 def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8Weight],
@@ -701,24 +726,64 @@ def linear_fused(a: torch.Tensor, weights: Sequence[FP8Weight], *, mode: str = "
     return outs, xq, sx
 
 
-def fp8_linear(x: torch.Tensor, w: FP8Weight) -> torch.Tensor:
-    """`F.linear(x, w)` for a single call site; leading dims preserved (braid/model/quant.py:244-252)."""
+# A residual waiting for the output projection of a mixer: set by the caller of the mixer
+# (`residual_into`), taken by the first `fp8_linear` on exactly that weight.
+_PENDING_RESIDUAL: list | None = None
+
+
+class residual_into:
+    """`with residual_into(w, r) as slot:` — the next `linear(·, w)` inside the block returns
+    `r + linear(·, w)` with the add in the GEMM epilogue, and `slot.taken` says whether it did.
+    Lets the decoder layer fuse its residual add into a projection that is called deep inside the
+    reference's mixer code (braid/model/gdn.py:387, braid/model/attention.py:216) without
+    touching that code."""
+
+    def __init__(self, w, residual: torch.Tensor):
+        self.w, self.residual, self.taken = w, residual, False
+
+    def __enter__(self):
+        global _PENDING_RESIDUAL
+        self._outer, _PENDING_RESIDUAL = _PENDING_RESIDUAL, self
+        return self
+
+    def __exit__(self, *exc):
+        global _PENDING_RESIDUAL
+        _PENDING_RESIDUAL = self._outer
+        return False
+
+
+def _claim_residual(w, lead, n, dtype):
+    slot = _PENDING_RESIDUAL
+    if (slot is None or slot.taken or slot.w is not w or slot.residual.dtype != dtype
+            or tuple(slot.residual.shape) != (*lead, n)):
+        return None
+    slot.taken = True
+    return slot.residual.reshape(-1, n)
+
+
+def fp8_linear(x: torch.Tensor, w: FP8Weight, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """`F.linear(x, w)` for a single call site; leading dims preserved (braid/model/quant.py:244-252).
+    `residual` (same shape as the result) is added in the GEMM epilogue."""
     *lead, K = x.shape
+    N = w.shape[0]
+    res2 = residual.reshape(-1, N) if residual is not None else _claim_residual(w, lead, N, x.dtype)
     if isinstance(x, QuantizedActivation):
-        return fp8_matmul(x.q, x.scale, w, out_dtype=x.dtype).reshape(*lead, w.shape[0])
+        return fp8_matmul(x.q, x.scale, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
     x2 = x.reshape(-1, K)
-    fused = linear_fused(x2, (w,)) if x2.is_cuda else None
+    fused = linear_fused(x2, (w,)) if (x2.is_cuda and res2 is None) else None
     if fused is not None:
-        return fused[0][0].reshape(*lead, w.shape[0])
+        return fused[0][0].reshape(*lead, N)
     xq, sx = quantize_act(x2)
-    return fp8_matmul(xq, sx, w, out_dtype=x.dtype).reshape(*lead, w.shape[0])
+    return fp8_matmul(xq, sx, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor | FP8Weight) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor | FP8Weight,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
     """Dispatch on the weight's type (braid/model/quant.py:255-257)."""
     if isinstance(w, FP8Weight):
-        return fp8_linear(x, w)
-    return F.linear(x.require_dense() if isinstance(x, QuantizedActivation) else x, w)
+        return fp8_linear(x, w, residual)
+    y = F.linear(x.require_dense() if isinstance(x, QuantizedActivation) else x, w)
+    return y if residual is None else residual + y
 
 
 def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.Tensor]:
@@ -765,7 +830,7 @@ def maybe_quantize(w: torch.Tensor, enabled: bool) -> torch.Tensor | FP8Weight:
 # fused sublayer tails (what the reference spells as separate bf16 kernels)
 # ---------------------------------------------------------------------------
 def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
-                down_proj: FP8Weight) -> torch.Tensor:
+                down_proj: FP8Weight, residual: torch.Tensor | None = None) -> torch.Tensor:
     """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 4 launches.
 
     quantize(x) -> one grouped GEMM writing gate|up into one `[M, 2I]` buffer ->
@@ -785,12 +850,13 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     elif linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
         xq, sx = quantize_act(x2)
         fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
-    fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1])
+    res2 = residual.reshape(-1, down_proj.shape[0]) if residual is not None else None
+    fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1]) if res2 is None else None
     if fused is not None:
         y = fused[0][0]
     else:
         hq, sh = silu_mul_quant(halves[0], halves[1])
-        y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype)
+        y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype, residual=res2)
     return y.reshape(*lead, down_proj.shape[0])
 
 
@@ -810,4 +876,6 @@ def gated_output_projection(o: torch.Tensor, gate: torch.Tensor, o_proj: FP8Weig
     if fused is not None:
         return fused[0][0].reshape(*lead, o_proj.shape[0])
     oq, so = sigmoid_gate_quant(o, gate)
-    return fp8_matmul(oq.reshape(-1, K), so, o_proj, out_dtype=o.dtype).reshape(*lead, o_proj.shape[0])
+    res2 = _claim_residual(o_proj, lead, o_proj.shape[0], o.dtype)
+    return fp8_matmul(oq.reshape(-1, K), so, o_proj, out_dtype=o.dtype,
+                      residual=res2).reshape(*lead, o_proj.shape[0])

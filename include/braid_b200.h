@@ -220,6 +220,26 @@ int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* s
                  void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * bq_gemm_w8a8 with the residual add of the decoder layer in the epilogue:
+ *   y = T(float(T(acc * sx * sw)) + float(residual))
+ * i.e. the GEMM's own rounding to the output type T followed by the add's rounding, which is
+ * what the reference's separate kernels produce.  Decode regime only (M <= 256): larger M
+ * returns BQ_ERR_UNSUPPORTED and the caller adds separately.
+ *
+ * Replaces: `x = x + h` after the mixer's output projection and `x + self.mlp(h)`
+ * (braid/model/layer.py:57,60), fused into `linear(core, out_proj)` (braid/model/gdn.py:387),
+ * `linear(o, o_proj)` (braid/model/attention.py:216) and `linear(h, down_proj)`
+ * (braid/model/mlp.py:49).
+ *
+ *   residual  device, [M,N] of out_dtype, row stride ld_res elements (ld_res >= N, % 4 == 0);
+ *             may not overlap y
+ */
+int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const float* sw,
+                          const void* residual, int64_t ld_res, void* y, int out_dtype,
+                          int64_t M, int64_t N, int64_t K, int64_t ldy,
+                          void* ws, size_t ws_bytes, void* stream);
+
+/*
  * Several projections of ONE quantized activation in a single launch: segment
  * i computes Y_i[M,N_i] = (Xq . Wq_i^T) * sx * sw_i with its own weight scale,
  * so results are bit-identical to n_seg separate bq_gemm_w8a8 calls.  The

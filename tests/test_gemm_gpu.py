@@ -389,3 +389,48 @@ def test_fused_and_unfused_sublayers_agree_and_repeat(Q):
         assert torch.equal(a, b)
     assert torch.equal(y, plain[0])
     assert Q.device_status() == 0
+
+
+# -- residual add in the epilogue ---------------------------------------------------------------
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+@pytest.mark.parametrize("M", [1, 8, 37, 128, 256, 512])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (4096, 12288), (1024, 4096), (272, 256), (16, 16)])
+def test_residual_epilogue_equals_gemm_then_add(Q, dt, M, N, K):
+    """`residual + fp8_matmul(...)` as torch evaluates it (GEMM output rounded to the output type,
+    then the add rounds again) against the add done in the GEMM epilogue: bit-equal for every K
+    split (1, 2, 4), ragged M, and the prefill sizes that fall back to a separate add."""
+    if dt is not torch.bfloat16 and (N, K) not in ((4096, 4096), (272, 256)):
+        pytest.skip("dtype variants on two shapes")
+    _, _, xq, sx, fw = _operands(Q, M, N, K, seed=M + N)
+    res = randn_cpu((M, N), seed=7, dtype=dt, scale=0.5).cuda()
+    want = res + Q.fp8_matmul(xq, sx, fw, out_dtype=dt)
+    got = Q.fp8_matmul(xq, sx, fw, out_dtype=dt, residual=res)
+    assert got.dtype is dt and got.shape == (M, N)
+    assert torch.equal(got, want), f"{int((got != want).sum())} of {got.numel()} differ"
+
+
+def test_residual_strided_scoped_and_through_the_sublayers(Q):
+    H, I, M = 4096, 12288, 16
+    x = randn_cpu((M, 1, H), seed=1).cuda()
+    mk = lambda n, k, s: Q.quantize_weight(randn_cpu((n, k), seed=s, scale=0.02).cuda())  # noqa: E731
+    w_out, wg, wu, wd = mk(H, H, 2), mk(I, H, 3), mk(I, H, 4), mk(H, I, 5)
+    wide = randn_cpu((M, 2 * H), seed=6).cuda()
+    res = wide[:, H:]                                           # row stride 2H
+    xq, sx = Q.quantize_act(x.reshape(M, H))
+    assert torch.equal(Q.fp8_matmul(xq, sx, w_out, residual=res), res + Q.fp8_matmul(xq, sx, w_out))
+    r3 = randn_cpu((M, 1, H), seed=8).cuda()
+    assert torch.equal(Q.linear(x, w_out, residual=r3), r3 + Q.linear(x, w_out))
+    assert torch.equal(Q.mlp_forward(x, wg, wu, wd, residual=r3), r3 + Q.mlp_forward(x, wg, wu, wd))
+    # the scoped form: only the named weight takes the residual, and only once
+    with Q.residual_into(w_out, r3) as slot:
+        a = Q.linear(x, wd_t := mk(H, H, 9))                    # another weight: untouched
+        assert not slot.taken
+        b = Q.linear(x, w_out)
+        assert slot.taken
+        c = Q.linear(x, w_out)                                  # second call: plain again
+    assert torch.equal(a, Q.linear(x, wd_t))
+    assert torch.equal(b, r3 + Q.linear(x, w_out)) and torch.equal(c, Q.linear(x, w_out))
+    with Q.residual_into(None, r3) as slot:
+        assert torch.equal(Q.linear(x, w_out), c) and not slot.taken
+    with pytest.raises(ValueError):
+        Q.fp8_matmul(xq, sx, w_out, residual=r3.reshape(M, H)[:, :128])
