@@ -43,6 +43,8 @@ SIGNATURES = {
     "bq_gemm_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "bq_gemm_w8a8_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _int, _i64, _i64, _i64, _i64,
                                      _vp, _sz, _vp]),
+    "bq_gate_up_silu_quant_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp,
+                                          _vp, _sz, _vp]),
     "bq_gemm_w8a8_grouped": (_int, [_vp, _vp, _i64, _i64, _int,
                                     ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                     ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,

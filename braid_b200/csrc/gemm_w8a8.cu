@@ -61,6 +61,7 @@ struct Segment {
   int n;               // weight rows (output columns) of this segment
   int tile_begin;      // tile kernel: index of the segment's first tile
   int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
+  int split_forced;    // stream kernel: non-zero = use this split instead of the shape rule
   int cluster_begin;   // stream kernel: index of the segment's first cluster
   long long total_kb;  // persistent stream kernel: row tiles x K blocks of this weight
   int ctas;            // persistent stream kernel: CTAs that share this weight
@@ -74,6 +75,18 @@ struct FuseParams {
   int dtype;              // BQ_DTYPE_* of the activation operands
   bq::qd::QParams q;      // operands, addressing, codes out (q.q) and scale out (q.scale)
   unsigned int* words;    // [0] amax bits [1] amax arrivals [2] codes arrivals [3] status [4] departures
+};
+
+// SiLU(gate)*up and the quantization of the product, done in the epilogue of ONE GEMM over a
+// weight whose row tiles interleave 64 gate rows with the 64 up rows of the same columns.
+struct PairSilu {
+  int on;
+  const float* sw_up;      // device: dequant scale of the up half (seg.sw is the gate half's)
+  uint8_t* hq;             // device: e4m3 codes of h, [M, ld_hq]
+  long long ld_hq;
+  float* sh;               // device: the scale of h
+  unsigned int* words;     // [0] amax bits [1] arrivals [2] departures ([3] is the sticky status)
+  unsigned int expected;   // CTAs that take part in the exchange (the active ones)
 };
 
 struct GemmParams {
@@ -91,6 +104,7 @@ struct GemmParams {
   unsigned int* status;
   int seq;             // launch counter (development builds only)
   FuseParams fuse;
+  PairSilu pair;
   unsigned int* flags;   // persistent stream kernel: one word per (weight, CTA), zero between launches
   float* partials;       // persistent stream kernel: [weight][CTA][mma_n][128] fp32
 };
@@ -261,6 +275,86 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
         if (e.col_ok) store_out4(e.y, (long long)m * e.ldy + e.row0 + n4, e.out_dtype, acc);
       }
     }
+  }
+}
+
+// Interleaved gate/up tile: columns 0..63 of the tile are gate rows, 64..127 the up rows of the
+// same 64 output columns.  Sums the K slices like reduce_store, rounds both halves to the
+// activation type T exactly as the plain GEMM would have stored them, forms
+// h = T(T(silu(gate)) * up) (the two roundings of the separate torch kernels,
+// braid/model/mlp.py:48), and parks h (64 values of T per row) at the start of the row's
+// staging slot in THIS CTA's buffer -- rows of this CTA's share are read by no peer.
+// Lane L < 16 ends up with columns 4L, 4L+1; lane L+16 with 4L+2, 4L+3.  Returns max |h|.
+template <int SPLIT, typename T>
+__device__ __forceinline__ float silu_pair_rows(const EpilogueArgs& e, float scale_up, float* part_rw) {
+  using namespace bq::qd;
+  constexpr int kRows = (SPLIT < 8) ? 8 / SPLIT : 1;
+  constexpr int kWarps = 8;
+  const int n4 = e.lane * 4;
+  const bool up_half = e.lane >= 16;
+  const float sc = up_half ? scale_up : e.scale;
+  const int hcol = (e.lane & 15) * 4 + (up_half ? 2 : 0);
+  float mx = 0.0f;
+  for (int m0 = e.m_begin + e.warp; m0 < e.m_end; m0 += kWarps * kRows) {
+    float4 v[kRows][SPLIT];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int m = m0 + i * kWarps;
+      if (m < e.m_end) {
+        const uint32_t off = e.part_addr + static_cast<uint32_t>(m * kRowTile + n4) * 4u;
+#pragma unroll
+        for (int r = 0; r < SPLIT; ++r) {
+          if constexpr (SPLIT == 1)
+            v[i][0] = *reinterpret_cast<const float4*>(e.part + m * kRowTile + n4);
+          else
+            v[i][r] = ld_cluster_f4(map_to_cta(off, e.peer0 + r));
+        }
+      }
+    }
+    __syncwarp();   // every lane has its slice of the rows before any lane overwrites them
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int m = m0 + i * kWarps;    // warp-uniform
+      if (m < e.m_end) {
+        float4 acc = v[i][0];
+#pragma unroll
+        for (int r = 1; r < SPLIT; ++r) {
+          acc.x += v[i][r].x; acc.y += v[i][r].y; acc.z += v[i][r].z; acc.w += v[i][r].w;
+        }
+        // the value the plain GEMM would have stored: one rounding to T
+        const float r0 = widen(narrow<T>(acc.x * sc)), r1 = widen(narrow<T>(acc.y * sc));
+        const float r2 = widen(narrow<T>(acc.z * sc)), r3 = widen(narrow<T>(acc.w * sc));
+        const float got0 = __shfl_xor_sync(0xffffffffu, up_half ? r0 : r2, 16);
+        const float got1 = __shfl_xor_sync(0xffffffffu, up_half ? r1 : r3, 16);
+        const float g0 = up_half ? got0 : r0, g1 = up_half ? got1 : r1;
+        const float u0 = up_half ? r2 : got0, u1 = up_half ? r3 : got1;
+        const T s0 = narrow<T>(__fdiv_rn(g0, 1.0f + expf(-g0)));
+        const T s1 = narrow<T>(__fdiv_rn(g1, 1.0f + expf(-g1)));
+        const T h0 = narrow<T>(widen(s0) * u0);
+        const T h1 = narrow<T>(widen(s1) * u1);
+        mx = nan_max(mx, fabsf(widen(h0)));
+        mx = nan_max(mx, fabsf(widen(h1)));
+        T* hrow = reinterpret_cast<T*>(part_rw + m * kRowTile);
+        hrow[hcol] = h0;
+        hrow[hcol + 1] = h1;
+      }
+    }
+  }
+  return mx;
+}
+
+// After the grid-wide scale is known: cast the parked h of this CTA's rows and write the codes.
+template <typename T>
+__device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const float* part, float sc,
+                                               uint8_t* hq, long long ld_hq, int col0) {
+  using namespace bq::qd;
+  const int hcol = (e.lane & 15) * 4 + (e.lane >= 16 ? 2 : 0);
+  for (int m = e.m_begin + e.warp; m < e.m_end; m += 8) {
+    const T* hrow = reinterpret_cast<const T*>(part + m * kRowTile);
+    const float2 f = make_float2(quant_one(widen(hrow[hcol]), sc), quant_one(widen(hrow[hcol + 1]), sc));
+    const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint16_t*>(hq + static_cast<long long>(m) * ld_hq + col0 + hcol) =
+        static_cast<uint16_t>(pair & 0xFFFFu);
   }
 }
 
@@ -576,10 +670,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   phase_stamp(4);
 
   // ---- reduce the K slices in rank order and write this CTA's share of rows --
+  float pair_max = 0.0f;
+  const int per = (p.M + split - 1) / split;
+  const int m_begin = krank * per;
+  const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
   if (ok) {
-    const int per = (p.M + split - 1) / split;
-    const int m_begin = krank * per;
-    const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
 #ifdef BQ_PHASES
     const bool col_ok = (row0 + lane * 4) < seg.n && g_dbg_mode != 3;
 #else
@@ -589,7 +684,22 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const int peer0 = group * split;
     const EpilogueArgs ea{part, part_addr, peer0, m_begin, m_end, warp, lane, row0, scale, col_ok,
                           seg.y, seg.ldy, p.out_dtype, seg.res, seg.ld_res};
-    if (seg.res == nullptr) {
+    if (p.pair.on) {
+      const float scale_up = sx_ready * __ldg(p.pair.sw_up);
+      float mx;
+#define BQ_PAIR_ROWS(TT)                                                          \
+      switch (split) {                                                             \
+        case 1: mx = silu_pair_rows<1, TT>(ea, scale_up, part); break;             \
+        case 2: mx = silu_pair_rows<2, TT>(ea, scale_up, part); break;             \
+        case 4: mx = silu_pair_rows<4, TT>(ea, scale_up, part); break;             \
+        default: mx = silu_pair_rows<8, TT>(ea, scale_up, part); break;            \
+      }
+      if (p.out_dtype == BQ_DTYPE_BF16) { BQ_PAIR_ROWS(__nv_bfloat16) }
+      else if (p.out_dtype == BQ_DTYPE_F16) { BQ_PAIR_ROWS(__half) }
+      else { BQ_PAIR_ROWS(float) }
+#undef BQ_PAIR_ROWS
+      pair_max = mx;
+    } else if (seg.res == nullptr) {
       switch (split) {
         case 1: reduce_store<1, false>(ea); break;
         case 2: reduce_store<2, false>(ea); break;
@@ -610,6 +720,64 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
   phase_stamp(6);
   chain_stamp(p.seq, 2);
+  if (p.pair.on) {
+    // ---- grid-wide max |h| -> scale -> codes of this CTA's rows (h is parked in `part`) ----
+    using namespace bq::qd;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      pair_max = nan_max(pair_max, __shfl_xor_sync(0xffffffffu, pair_max, off));
+    if (lane == 0) s_quant[warp] = pair_max;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float w = s_quant[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) w = nan_max(w, s_quant[i]);
+      unsigned int* const words = p.pair.words;
+      if (p.pair.expected > 1) {
+        // an aborted CTA still arrives (with 0), so the others are not left waiting
+        atomicMax(&words[0], __float_as_uint(w));
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&words[1]) : "memory");
+        unsigned int amax_bits = 0, arrived = 0;
+        const long long t0 = clock64();
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];"
+                       : "=r"(amax_bits), "=r"(arrived)
+                       : "l"(words)
+                       : "memory");
+          if (arrived >= p.pair.expected) break;
+          if (clock64() - t0 > kSpinLimitCycles) {
+            atomicExch(p.status, (unsigned int)kErrDeviceWait);
+            break;
+          }
+        }
+        w = __uint_as_float(amax_bits);
+      }
+      const float sc = scale_from_amax(w);
+      if (blockIdx.x == 0) p.pair.sh[0] = sc;
+      s_quant[0] = sc;
+    }
+    __syncthreads();
+    const float sc = s_quant[0];
+    if (ok) {
+      const EpilogueArgs ea{part, smem_u32(part), 0, m_begin, m_end, warp, lane, row0, 0.0f, true,
+                            nullptr, 0, p.out_dtype, nullptr, 0};
+      const int col0 = tile_in_seg * (kRowTile / 2);
+      if (p.out_dtype == BQ_DTYPE_BF16)
+        silu_pair_emit<__nv_bfloat16>(ea, part, sc, p.pair.hq, p.pair.ld_hq, col0);
+      else if (p.out_dtype == BQ_DTYPE_F16)
+        silu_pair_emit<__half>(ea, part, sc, p.pair.hq, p.pair.ld_hq, col0);
+      else
+        silu_pair_emit<float>(ea, part, sc, p.pair.hq, p.pair.ld_hq, col0);
+    }
+    if (threadIdx.x == 0 && p.pair.expected > 1) {
+      unsigned int* const words = p.pair.words;
+      const unsigned int old = atomicAdd(&words[2], 1u);
+      if (old == p.pair.expected - 1) {
+        words[0] = 0u; words[1] = 0u; words[2] = 0u;
+        __threadfence();
+      }
+    }
+  }
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
@@ -1374,7 +1542,8 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   const int stage_bytes = kATileBytes + b_tile;
   int cluster = 1, min_split = 8;
   for (int i = 0; i < p.n_seg; ++i) {
-    p.seg[i].split = split_for_weight(p.seg[i].n, p.k_blocks);
+    p.seg[i].split = p.seg[i].split_forced > 0 ? p.seg[i].split_forced
+                                               : split_for_weight(p.seg[i].n, p.k_blocks);
     if (p.seg[i].split > cluster) cluster = p.seg[i].split;
     if (p.seg[i].split < min_split) min_split = p.seg[i].split;
   }
@@ -1410,8 +1579,9 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   if (tile_bytes < staging) tile_bytes = staging;
   const int smem = tile_bytes + kBarrierBytes + 1024;
   if (smem > kMaxSmem) return kErrUnsupported;
-  if (p.fuse.mode != 0) {
-    // the fused quantizer waits on the whole grid: every CTA must be resident
+  if (p.pair.on) p.pair.expected = (unsigned)((p.seg[0].n / kRowTile) * p.seg[0].split);
+  if (p.fuse.mode != 0 || p.pair.on) {
+    // the in-kernel quantizer waits on the whole grid: every CTA must be resident
     const int cap = max_resident_ctas(cluster, smem);
     if (getenv("BQ_DEBUG"))
       fprintf(stderr, "[bq] fused launch: grid %lld cluster %d smem %d resident cap %d\n", grid,
@@ -1609,7 +1779,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
                 const void* const* wq, const float* const* sw, void* const* y, const int64_t* N,
                 const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
                 const FuseParams* fuse, const void* const* res = nullptr,
-                const int64_t* ld_res = nullptr) {
+                const int64_t* ld_res = nullptr, const PairSilu* pair = nullptr,
+                int split_forced = 0) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
@@ -1619,14 +1790,17 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
   const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
   for (int i = 0; i < n_seg; ++i) {   // argument checks first: no CUDA call before they pass
-    if (!wq[i] || !sw[i] || !y[i] || N[i] <= 0) return kErrBadArg;
-    if (N[i] % 16 || ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(wq[i], 16) ||
-        !aligned_to(y[i], out_align))
-      return kErrUnsupported;
+    if (!wq[i] || !sw[i] || N[i] <= 0) return kErrBadArg;
+    if (N[i] % 16 || !aligned_to(wq[i], 16)) return kErrUnsupported;
+    if (pair == nullptr) {   // the pair form writes codes of h, not y
+      if (!y[i]) return kErrBadArg;
+      if (ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(y[i], out_align)) return kErrUnsupported;
+    }
     if (N[i] > 0x7fffff00LL) return kErrTooLarge;
   }
   const bool stream_path = M <= g_opt_stream_max_m;
-  if (fuse && !stream_path) return kErrUnsupported;   // the fused form exists for the decode regime
+  if ((fuse || pair) && !stream_path) return kErrUnsupported;   // decode-regime forms only
+  if (pair && (fuse || res || n_seg != 1)) return kErrBadArg;
   if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
     if (!stream_path || ld_res == nullptr) return kErrUnsupported;
     for (int i = 0; i < n_seg; ++i)
@@ -1651,6 +1825,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.fuse = *fuse;
     p.fuse.words = static_cast<unsigned int*>(ws);
   }
+  if (pair) {
+    p.pair = *pair;
+    p.pair.on = 1;
+    p.pair.words = static_cast<unsigned int*>(ws);
+  }
 
   const bool pair_path = !stream_path && g_opt_pair != 0;
   const int w_box_rows = (stream_path || pair_path) ? kRowTile : kTileN;
@@ -1659,8 +1838,9 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
-    p.seg[i].y = y[i];
-    p.seg[i].ldy = ldy[i];
+    p.seg[i].y = pair ? nullptr : y[i];
+    p.seg[i].ldy = pair ? 0 : ldy[i];
+    p.seg[i].split_forced = split_forced;
     p.seg[i].res = res ? res[i] : nullptr;
     p.seg[i].ld_res = res ? ld_res[i] : 0;
     p.seg[i].n = (int)N[i];
@@ -1676,7 +1856,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    if (!fuse && !res && g_opt_decode_kernel != 1) {
+    if (!fuse && !res && !pair && g_opt_decode_kernel != 1) {
       const size_t need = persist_scratch_bytes(device_sms(), n_seg, mma_n);
       if (ws_bytes >= need) return launch_persist(tm_x, maps, p, ws, stream);
       if (g_opt_decode_kernel == 2) return kErrWorkspace;
@@ -1749,6 +1929,31 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
   const int64_t ldys[1] = {ldy};
   return bq_gemm_w8a8_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes,
                               stream);
+}
+
+extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_pair,
+                                          const float* sw_gate, const float* sw_up, int64_t M,
+                                          int64_t I, int64_t K, int act_dtype, void* hq_out,
+                                          float* sh_out, void* ws, size_t ws_bytes, void* stream) {
+  if (!wq_pair || !sw_gate || !sw_up || !hq_out || !sh_out || I <= 0) return kErrBadArg;
+  if (I % (kRowTile / 2) || !aligned_to(hq_out, 2)) return kErrUnsupported;
+  PairSilu pair;
+  memset(&pair, 0, sizeof(pair));
+  pair.sw_up = sw_up;
+  pair.hq = static_cast<uint8_t*>(hq_out);
+  pair.ld_hq = I;
+  pair.sh = sh_out;
+  const void* wqs[1] = {wq_pair};
+  const float* sws[1] = {sw_gate};
+  void* ys[1] = {nullptr};
+  const int64_t Ns[1] = {2 * I};
+  const int64_t ldys[1] = {0};
+  // K slices as the gate weight alone would get them: every dot product is then summed in the
+  // order of the separate gate and up GEMMs
+  const int k_blocks = (int)((K + kBK - 1) / kBK);
+  const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight((int)I, k_blocks) : 1;
+  return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
+                     nullptr, nullptr, nullptr, &pair, split);
 }
 
 extern "C" int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const float* sw,

@@ -827,22 +827,103 @@ def maybe_quantize(w: torch.Tensor, enabled: bool) -> torch.Tensor | FP8Weight:
 
 
 # ---------------------------------------------------------------------------
+# gate/up as ONE weight with interleaved row tiles (a layout made for the kernel)
+# ---------------------------------------------------------------------------
+# Row tile t of the paired weight holds gate rows [64t, 64t+64) followed by up rows [64t, 64t+64),
+# so one 128-row MMA tile yields gate AND up of the same 64 columns and the epilogue can form
+# silu(gate) * up, its amax and its FP8 codes without the two halves ever being written.  The
+# reference keeps `gate_proj` and `up_proj` as two tensors with two scales (braid/model/mlp.py:
+# 27-29); both scales are kept, the paired copy is built once per weight pair outside captures.
+_PAIR_MLP = True
+_PAIRED: dict[tuple[int, int], tuple] = {}
+
+
+def set_paired_mlp(enable: bool) -> None:
+    """Use (default) or not the interleaved gate/up copy and the 3-launch MLP.  Off saves the
+    extra copy of the two weights (2 * I * K bytes per layer); results are identical."""
+    global _PAIR_MLP
+    _PAIR_MLP = bool(enable)
+    if not enable:
+        _PAIRED.clear()
+
+
+def paired_gate_up(gate: FP8Weight, up: FP8Weight) -> torch.Tensor | None:
+    """The interleaved `[2I, K]` e4m3 copy of a gate/up pair, cached per pair of tensors.
+    `None` when the shapes do not pair (I not a multiple of 64) or when it would have to be built
+    during a stream capture."""
+    import weakref
+    key = (gate.data.data_ptr(), up.data.data_ptr())
+    hit = _PAIRED.get(key)
+    if hit is not None and hit[0]() is gate.data and hit[1]() is up.data:
+        return hit[2]
+    I, K = gate.data.shape
+    if (up.data.shape != (I, K) or I % 64 or not gate.data.is_contiguous()
+            or not up.data.is_contiguous() or torch.cuda.is_current_stream_capturing()):
+        return None
+    for k in [k for k, v in _PAIRED.items() if v[0]() is None or v[1]() is None]:
+        del _PAIRED[k]
+    g8 = gate.data.view(torch.uint8).view(I // 64, 64, K)
+    u8 = up.data.view(torch.uint8).view(I // 64, 64, K)
+    paired = torch.stack((g8, u8), dim=1).reshape(2 * I, K).view(FP8)
+    _PAIRED[key] = (weakref.ref(gate.data), weakref.ref(up.data), paired)
+    return paired
+
+
+def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
+                       act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor] | None:
+    """`quantize_act(F.silu(xq @ gate^T) * (xq @ up^T))` in ONE launch (decode sizes): the two
+    GEMMs run as one over the paired weight, the product and its quantization happen in the
+    epilogue (braid/model/mlp.py:46-49 up to the input of down_proj).  Codes and scale are
+    bit-identical to the separate GEMMs + `silu_mul_quant`.  `None` when not applicable."""
+    M, K = xq.shape
+    code = _DTYPE_CODE.get(act_dtype)
+    if not _PAIR_MLP or _quantizers_off() or code is None or M == 0 or M > 256:
+        return None
+    paired = paired_gate_up(gate, up)
+    if paired is None or gate.data.shape[1] != K:
+        return None
+    lib = _require_lib()
+    I = gate.data.shape[0]
+    hq = torch.empty((M, I), dtype=FP8, device=xq.device)
+    sh = torch.empty((1, 1), dtype=torch.float32, device=xq.device)
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    rc = lib.bq_gate_up_silu_quant_w8a8(xq.data_ptr(), sx.data_ptr(), paired.data_ptr(),
+                                        gate.scale.data_ptr(), up.scale.data_ptr(), M, I, K, code,
+                                        hq.data_ptr(), sh.data_ptr(), _take_slot(xq.device), 16,
+                                        _stream_ptr(xq.device))
+    if rc == _lib.BQ_ERR_UNSUPPORTED:
+        return None
+    _lib.check(rc, "gate_up_silu_quant")
+    return hq, sh
+
+
+# ---------------------------------------------------------------------------
 # fused sublayer tails (what the reference spells as separate bf16 kernels)
 # ---------------------------------------------------------------------------
 def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
                 down_proj: FP8Weight, residual: torch.Tensor | None = None) -> torch.Tensor:
-    """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 4 launches.
-
-    quantize(x) -> one grouped GEMM writing gate|up into one `[M, 2I]` buffer ->
-    SiLU*mul fused into the quantization of h (h never written) -> down GEMM.
-    Result bit-identical to the reference's nine-plus-kernel sequence built from
-    the same primitives.
+    """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 3 launches at decode
+    sizes: quantize(x) -> gate and up as one GEMM over the paired weight with SiLU*mul and the
+    quantization of h in its epilogue -> down GEMM (with `residual` added in its epilogue).
+    Larger M, unpaired shapes or `set_paired_mlp(False)`: 4 launches (quantize -> grouped GEMM
+    writing gate|up into one `[M, 2I]` buffer -> SiLU*mul inside the quantizer of h -> down).
+    Either way the result is bit-identical to the reference's nine-plus-kernel sequence built
+    from the same primitives.
     """
     *lead, K = x.shape
     pre = x if isinstance(x, QuantizedActivation) else None
     x2 = None if pre is not None else x.reshape(-1, K)
     M = pre.q.shape[0] if pre is not None else x2.shape[0]
     I = gate_proj.shape[0]
+    res2 = residual.reshape(-1, down_proj.shape[0]) if residual is not None else None
+    if _PAIR_MLP and M <= 256 and x.device.type == "cuda" and not _FUSE_LINEAR:
+        xq, sx = (pre.q, pre.scale) if pre is not None else quantize_act(x2)
+        paired = gate_up_silu_quant(xq, sx, gate_proj, up_proj, x.dtype)
+        if paired is not None:
+            y = fp8_matmul(paired[0], paired[1], down_proj, out_dtype=x.dtype, residual=res2)
+            return y.reshape(*lead, down_proj.shape[0])
+        pre = QuantizedActivation(xq, sx, x.shape, x.dtype)     # do not quantize twice
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     halves = (gu[:, :I], gu[:, I:])
     if pre is not None:
@@ -850,7 +931,6 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     elif linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
         xq, sx = quantize_act(x2)
         fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
-    res2 = residual.reshape(-1, down_proj.shape[0]) if residual is not None else None
     fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1]) if res2 is None else None
     if fused is not None:
         y = fused[0][0]

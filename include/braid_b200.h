@@ -240,6 +240,31 @@ int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const
                           void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The first half of the quantized MLP in ONE launch (decode regime, M <= 256):
+ *   gate = Xq.Wg^T, up = Xq.Wu^T (each rounded to the activation type as bq_gemm_w8a8 would),
+ *   h = T(T(silu(gate)) * up), then amax / scale / e4m3 codes of h
+ * -- neither gate, up nor h is written; only the codes and the scale are.  Bit-identical to
+ * bq_gemm_w8a8_grouped(gate, up) followed by bq_silu_mul_quant.
+ *
+ * The kernel needs gate and up of the same columns in one MMA tile, so it takes the two
+ * weights as ONE [2I, K] e4m3 tensor whose 128-row tiles interleave them: rows
+ * [128t, 128t+64) = gate rows [64t, 64t+64), rows [128t+64, 128t+128) = up rows [64t, 64t+64).
+ * Both per-tensor scales are kept.  I must be a multiple of 64.
+ *
+ * Replaces: braid/model/mlp.py:46-48 (`gate = fp8_matmul(..)`, `up = fp8_matmul(..)`,
+ * `h = F.silu(gate) * up`) and the `quantize_act` inside `linear(h, down_proj)` (:49).
+ *
+ *   wq_pair  device, [2I, K] e4m3 codes in the interleaved layout, 16-byte aligned
+ *   hq_out   device, M*I bytes, contiguous [M, I];  sh_out  device, one float
+ *   ws       16 bytes, zero before the first call, self-resetting (as for bq_quantize_act)
+ * Returns BQ_ERR_UNSUPPORTED when the launch cannot be resident at once or M > 256.
+ */
+int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_pair,
+                               const float* sw_gate, const float* sw_up, int64_t M, int64_t I,
+                               int64_t K, int act_dtype, void* hq_out, float* sh_out,
+                               void* ws, size_t ws_bytes, void* stream);
+
+/*
  * Several projections of ONE quantized activation in a single launch: segment
  * i computes Y_i[M,N_i] = (Xq . Wq_i^T) * sx * sw_i with its own weight scale,
  * so results are bit-identical to n_seg separate bq_gemm_w8a8 calls.  The
