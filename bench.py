@@ -3,8 +3,9 @@
 
 Default workload (`config.workload = "decode_step_projection_set"`): the full projection set of
 one decode step of a 32-layer Qwen3.5-9B-class hybrid (24 Gated-DeltaNet + 8 attention layers,
-MLP in every layer) at batch 128 — 128 activation quantizations and 128 grouped FP8 GEMM
-launches covering 200 weights (6.9 GB of e4m3), captured once in a CUDA graph and replayed.
+MLP in every layer) at batch 128 — 128 activation quantizations (32 of them done in the
+epilogue of the paired gate/up GEMM) and 128 FP8 GEMM launches covering 200 weights (6.9 GB of
+e4m3), captured once in a CUDA graph and replayed.
 One step = one replay.  metric = projection-set tokens per second = rows x steps / time.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--rows 128] [--impl b200|reference]
@@ -342,7 +343,19 @@ def main():
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
         import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # ... and at any level above NONE it still prints it when the communicator is created:
+        # point fd 1 at stderr until that has happened, so stdout carries the JSON line only
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist_mod.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
         dist = dist_mod
 
     from braid_b200 import quant as Q
@@ -380,6 +393,8 @@ def main():
     d2h = y_host.numel() * y_host.element_size()
 
     # ---- dominant kernel alone: the step's FP8 GEMM launches, same shapes and order ---------
+    # (gate|up in its plain grouped form: the paired form the step uses adds the SiLU*mul and
+    # quantization epilogue, which is not GEMM time)
     xq, sx = Q.quantize_act(static_x)
     coreq, _ = Q.quantize_act(ps.core)
     oq, _ = Q.quantize_act(ps.o)
@@ -408,7 +423,9 @@ def main():
     status = Q.device_status()
 
     # ---- the step without the 48 bf16 gate projections: this package's kernels only ----------
+    n2 = Q.launch_count()
     g_fp8, _ = capture(lambda: ps.step_b200(static_x, bf16_gates=False))
+    fp8_launches = (Q.launch_count() - n2) // 4
     ms_fp8, _ = timed_replays(g_fp8.replay, args.steps, args.warmup, dist=None)
     del g_fp8
 
@@ -465,8 +482,9 @@ def main():
                               "tflops": shapes.step_flops(args.rows) * args.layers / shapes.n_layers
                               / (ms_per_step * 1e-3) / 1e12},
             "fp8_kernels_only": {"ms_per_step": ms_fp8 / args.steps,
+                                 "launches_per_step": fp8_launches,
                                  "what": "the step without the 48 bf16 gate GEMMs (F.linear) the "
-                                         "reference keeps in bf16: 256 launches, all of this library"},
+                                         "reference keeps in bf16: every launch is this library's"},
             "cpu_baseline": cpu,
             "library_baseline": library,
             "column_parallel": colpar,
