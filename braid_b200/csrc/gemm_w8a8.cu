@@ -102,7 +102,6 @@ struct GemmParams {
   int m_tiles;         // tile kernel: ceil(M / 128)
   int total_tiles;     // tile kernel
   unsigned int* status;
-  int seq;             // launch counter (development builds only)
   FuseParams fuse;
   PairSilu pair;
   unsigned int* flags;   // persistent stream kernel: one word per (weight, CTA), zero between launches
@@ -112,37 +111,6 @@ struct GemmParams {
 struct alignas(64) WeightMaps {
   CUtensorMap w[BQ_MAX_SEGMENTS];
 };
-
-#ifdef BQ_PHASES
-// Development aid (never compiled into the shipped library): nanosecond stamps of
-// the phases of every CTA of the stream kernel.
-__device__ unsigned long long g_phase_ts[8 * 2048];
-__device__ unsigned long long g_chain_ts[64 * 512 * 4];   // [launch % 64][cta < 512][start, accum, end, smid]
-__device__ unsigned int g_chain_seq = 0;
-__device__ int g_dbg_mode = 0;   // 1: one MMA per k-block, 2: no MMA (timing experiments only)
-__device__ __forceinline__ void phase_stamp(int idx) {
-  if (threadIdx.x == 0 && blockIdx.x < 2048) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_phase_ts[blockIdx.x * 8 + idx] = t;
-  }
-}
-__device__ __forceinline__ void chain_stamp(int seq, int idx) {
-  if (threadIdx.x == 0 && blockIdx.x < 512) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_chain_ts[((seq & 63) * 512 + blockIdx.x) * 4 + idx] = t;
-    if (idx == 0) {
-      unsigned int smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      g_chain_ts[((seq & 63) * 512 + blockIdx.x) * 4 + 3] = smid;
-    }
-  }
-}
-#else
-__device__ __forceinline__ void phase_stamp(int) {}
-__device__ __forceinline__ void chain_stamp(int, int) {}
-#endif
 
 __device__ __forceinline__ int find_segment(const GemmParams& p, int tile) {
   int s = 0;
@@ -479,8 +447,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // 8 floats
   const bool fused = p.fuse.mode != 0;
 
-  phase_stamp(0);
-  chain_stamp(p.seq, 0);
   pdl_launch_dependents();   // the next kernel may start its own set-up right away
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A cluster of p.cluster CTAs works on p.cluster / split row tiles of one weight
@@ -528,7 +494,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  phase_stamp(1);
 
   if (!active) {
     // nothing to multiply; it still takes its share of the fused quantizer and
@@ -606,14 +571,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         tc_fence_after();
         const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
         const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
-#ifdef BQ_PHASES
-        if (g_dbg_mode == 2) { mbar_arrive(empty_bar(s)); continue; }
-        if (g_dbg_mode == 1) {
-          mma_f8(tmem_base, da, db, idesc, i != 0 ? 1u : 0u);
-          mma_commit(empty_bar(s));
-          continue;
-        }
-#endif
 #pragma unroll
         for (int j = 0; j < kBK / kUmmaK; ++j) {
           // +32 bytes along K inside the swizzle span = +2 in descriptor units
@@ -641,8 +598,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   const float sx_ready = fused ? 0.0f : __ldg(p.sx);
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
-  phase_stamp(2);
-  chain_stamp(p.seq, 1);
   if (!ok) *abort_flag = 1;
   __syncthreads();
   ok = (*abort_flag == 0);
@@ -665,9 +620,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     atomicExch(p.status, (unsigned int)kErrDeviceWait);
   }
   tc_fence_before();
-  phase_stamp(3);
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
-  phase_stamp(4);
 
   // ---- reduce the K slices in rank order and write this CTA's share of rows --
   float pair_max = 0.0f;
@@ -675,11 +628,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   const int m_begin = krank * per;
   const int m_end = (m_begin + per < p.M) ? (m_begin + per) : p.M;
   if (ok) {
-#ifdef BQ_PHASES
-    const bool col_ok = (row0 + lane * 4) < seg.n && g_dbg_mode != 3;
-#else
     const bool col_ok = (row0 + lane * 4) < seg.n;      // n is a multiple of 16
-#endif
     const uint32_t part_addr = smem_u32(part);
     const int peer0 = group * split;
     const EpilogueArgs ea{part, part_addr, peer0, m_begin, m_end, warp, lane, row0, scale, col_ok,
@@ -716,10 +665,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
   }
   // nobody leaves while a peer may still read its staging buffer
-  phase_stamp(5);
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
-  phase_stamp(6);
-  chain_stamp(p.seq, 2);
   if (p.pair.on) {
     // ---- grid-wide max |h| -> scale -> codes of this CTA's rows (h is parked in `part`) ----
     using namespace bq::qd;
@@ -1606,10 +1552,6 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cfg.numAttrs = g_opt_pdl ? 2 : 1;
   g_last_launch[0] = 0; g_last_launch[1] = grid; g_last_launch[2] = cluster;
   g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
-#ifdef BQ_PHASES
-  static int launch_seq = 0;
-  p.seq = launch_seq++;
-#endif
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
@@ -1972,19 +1914,6 @@ extern "C" int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float
                      nullptr, rs, ldrs);
 }
 
-#ifdef BQ_PHASES
-extern "C" int bq_debug_set_mode(int mode) {
-  return cudaMemcpyToSymbol(g_dbg_mode, &mode, sizeof(int)) == cudaSuccess ? 0 : 3;
-}
-extern "C" int bq_debug_read_chain(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_chain_ts, sizeof(unsigned long long) * 64 * 512 * 4) ==
-                 cudaSuccess ? 0 : 3;
-}
-extern "C" int bq_debug_read_phases(unsigned long long* out, int n_ctas) {
-  return cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(unsigned long long) * 8 * n_ctas) ==
-                 cudaSuccess ? 0 : 3;
-}
-#endif
 
 extern "C" int bq_last_gemm_launch(int64_t out[6]) {
   if (!out) return kErrBadArg;
