@@ -220,6 +220,12 @@ def main(args):
         print(json.dumps(quant_row(only, args.rows, 4096, dev, peaks, reps=3)), flush=True)
         print(json.dumps({"device_status": Q.device_status()}), flush=True)
         return
+    if only == "mlp_block":
+        # the whole quantized MLP of one layer at --rows (paired gate/up kernel + down): what the
+        # ncu capture of the paired epilogue runs
+        print(json.dumps(mlp_block_row(args.rows, dev, peaks, reps=3)), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
     if only == "norms":
         for kind in ("rms_norm", "rms_norm_dense", "rms_norm_torch", "gated_rms_norm",
                      "gated_rms_norm_torch"):
