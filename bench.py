@@ -280,18 +280,30 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         mlp = ColumnParallelMLP.random_init(4096, 12288, torch.device("cuda"), dist.group.WORLD, seed=1)
         x = torch.randn(rows, 4096, device="cuda").to(torch.bfloat16)
         fn = lambda: mlp.forward(x)  # noqa: E731
-        ms, _ = timed_replays(fn, steps, warmup, dist=dist)
+        # one CUDA graph per rank holding the kernels AND the two NCCL all-gathers, replayed like
+        # the decode step; eager launches if the collective cannot be captured here
+        how = "graph replay"
+        try:
+            graph, _ = capture(fn)
+            call = graph.replay
+        except Exception:  # noqa: BLE001
+            torch.cuda.synchronize()
+            how, call = "eager launches", fn
+        ms, _ = timed_replays(call, steps, warmup, dist=dist)
         flops = 2 * rows * 3 * 4096 * 12288
         entry = {"ms_per_call": ms / steps, "tflops": flops / (ms / steps * 1e-3) / 1e12,
-                 "all_gather_bytes": mlp.gather_bytes(rows)}
+                 "all_gather_bytes": mlp.gather_bytes(rows), "timing": how}
+        if how == "graph replay":
+            del graph
         del mlp
         # the same MLP, unsharded, on one GPU of the same box (every rank runs it; rank 0 reports)
         g = torch.Generator(device="cuda").manual_seed(1)
         mk = lambda n, k: Q.quantize_weight(  # noqa: E731
             (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
         wg, wu, wd = mk(12288, 4096), mk(12288, 4096), mk(4096, 12288)
-        one = lambda: Q.mlp_forward(x, wg, wu, wd)  # noqa: E731
-        ms1, _ = timed_replays(one, steps, warmup, dist=dist)
+        g1, _ = capture(lambda: Q.mlp_forward(x, wg, wu, wd))
+        ms1, _ = timed_replays(g1.replay, steps, warmup, dist=dist)
+        del g1
         entry["single_gpu_ms_per_call"] = ms1 / steps
         entry["speedup_vs_single_gpu"] = ms1 / ms
         out[f"M{rows}"] = entry
