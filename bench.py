@@ -295,7 +295,32 @@ def column_parallel_block(dist, rows_list, steps, warmup):
                  "all_gather_bytes": mlp.gather_bytes(rows), "timing": how}
         if how == "graph replay":
             del graph
+        y_nccl = fn().clone()
         del mlp
+        # the same sharded MLP with the all-gathers folded into the GEMM epilogues (peer-mapped
+        # buffers over CUDA IPC, per-rank arrival counters, no collective): decode sizes only
+        if rows <= 256:
+            try:
+                from braid_b200.parallel import FusedColumnParallelMLP
+                fmlp = FusedColumnParallelMLP.random_init(4096, 12288, torch.device("cuda"),
+                                                          dist.group.WORLD, seed=1)
+                fmlp.connect()
+                y_fused = fmlp.forward(x).clone()
+                torch.cuda.synchronize()
+                dist.barrier()
+                gf, _ = capture(lambda: fmlp.forward(x))
+                msf, _ = timed_replays(gf.replay, steps, warmup, dist=dist)
+                entry["fused"] = {"ms_per_call": msf / steps,
+                                  "equals_nccl_form": bool(torch.equal(y_fused, y_nccl)),
+                                  "wait_status": int(fmlp.buffers.status.item()),
+                                  "launches_per_call": 5,
+                                  "what": "GEMM epilogues store into every rank's gathered buffer "
+                                          "through peer pointers; one-thread wait kernels; no NCCL"}
+                del gf
+                dist.barrier()
+                del fmlp
+            except Exception as e:  # noqa: BLE001
+                entry["fused"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
         # the same MLP, unsharded, on one GPU of the same box (every rank runs it; rank 0 reports)
         g = torch.Generator(device="cuda").manual_seed(1)
         mk = lambda n, k: Q.quantize_weight(  # noqa: E731
@@ -306,6 +331,9 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         del g1
         entry["single_gpu_ms_per_call"] = ms1 / steps
         entry["speedup_vs_single_gpu"] = ms1 / ms
+        if "fused" in entry and "ms_per_call" in entry["fused"]:
+            entry["fused"]["speedup_vs_single_gpu"] = (ms1 / steps) / entry["fused"]["ms_per_call"]
+            entry["fused"]["speedup_vs_nccl_form"] = (ms / steps) / entry["fused"]["ms_per_call"]
         out[f"M{rows}"] = entry
         del wg, wu, wd
         torch.cuda.empty_cache()

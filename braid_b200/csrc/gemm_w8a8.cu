@@ -89,6 +89,19 @@ struct PairSilu {
   unsigned int expected;   // CTAs that take part in the exchange (the active ones)
 };
 
+// Column-parallel form: the output tile (or, in the paired form, h) is stored straight into the
+// gathered buffer of every rank of the node -- plain stores through peer-mapped pointers, this
+// rank's own buffer included -- and every CTA then adds 1 to a counter on each rank with a
+// system-scope release.  No collective call, no multicast.  The pointers already carry this
+// rank's column offset.
+constexpr int kMaxPeers = 8;
+struct PushParams {
+  int n;                          // destinations (0 = not a push launch)
+  void* dst[kMaxPeers];
+  long long ld;                   // row stride of every destination, elements
+  unsigned int* flag[kMaxPeers];  // one arrival counter per destination rank
+};
+
 struct GemmParams {
   Segment seg[BQ_MAX_SEGMENTS];
   int n_seg;
@@ -104,6 +117,7 @@ struct GemmParams {
   unsigned int* status;
   FuseParams fuse;
   PairSilu pair;
+  PushParams push;
   unsigned int* flags;   // persistent stream kernel: one word per (weight, CTA), zero between launches
   float* partials;       // persistent stream kernel: [weight][CTA][mma_n][128] fp32
 };
@@ -154,6 +168,7 @@ struct EpilogueArgs {
   int out_dtype;
   const void* res;
   long long ld_res;
+  const PushParams* push;
 };
 
 // Four residual values of the output type, as raw bits (16 bytes cover the widest case).
@@ -240,7 +255,14 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
         if constexpr (RES) {
           if (e.col_ok) acc = add_res4(acc, rraw[i], e.out_dtype);
         }
-        if (e.col_ok) store_out4(e.y, (long long)m * e.ldy + e.row0 + n4, e.out_dtype, acc);
+        if (e.col_ok) {
+          if (e.push->n == 0) {
+            store_out4(e.y, (long long)m * e.ldy + e.row0 + n4, e.out_dtype, acc);
+          } else {
+            for (int d = 0; d < e.push->n; ++d)
+              store_out4(e.push->dst[d], (long long)m * e.push->ld + e.row0 + n4, e.out_dtype, acc);
+          }
+        }
       }
     }
   }
@@ -632,7 +654,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const uint32_t part_addr = smem_u32(part);
     const int peer0 = group * split;
     const EpilogueArgs ea{part, part_addr, peer0, m_begin, m_end, warp, lane, row0, scale, col_ok,
-                          seg.y, seg.ldy, p.out_dtype, seg.res, seg.ld_res};
+                          seg.y, seg.ldy, p.out_dtype, seg.res, seg.ld_res, &p.push};
     if (p.pair.on) {
       const float scale_up = sx_ready * __ldg(p.pair.sw_up);
       float mx;
@@ -666,7 +688,28 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   }
   // nobody leaves while a peer may still read its staging buffer
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
-  if (p.pair.on) {
+  if (p.pair.on && p.push.n > 0) {
+    // ---- column-parallel form: h itself goes to every rank's gathered buffer; the amax needs
+    // all ranks' shards and is taken by the quantizer that follows the exchange ----
+    __syncthreads();   // parked rows are complete
+    if (ok) {
+      const int col0 = tile_in_seg * (kRowTile / 2);
+      const int hcol = (lane & 15) * 4 + (lane >= 16 ? 2 : 0);
+      for (int m = m_begin + warp; m < m_end; m += 8) {
+        const long long at = static_cast<long long>(m) * p.push.ld + col0 + hcol;
+        if (p.out_dtype == BQ_DTYPE_F32) {
+          const float2 v = *reinterpret_cast<const float2*>(part + m * kRowTile + hcol);
+          for (int d = 0; d < p.push.n; ++d)
+            *reinterpret_cast<float2*>(static_cast<float*>(p.push.dst[d]) + at) = v;
+        } else {
+          const uint32_t v = *reinterpret_cast<const uint32_t*>(
+              reinterpret_cast<const uint16_t*>(part + m * kRowTile) + hcol);
+          for (int d = 0; d < p.push.n; ++d)
+            *reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(p.push.dst[d]) + at) = v;
+        }
+      }
+    }
+  } else if (p.pair.on) {
     // ---- grid-wide max |h| -> scale -> codes of this CTA's rows (h is parked in `part`) ----
     using namespace bq::qd;
 #pragma unroll
@@ -706,7 +749,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const float sc = s_quant[0];
     if (ok) {
       const EpilogueArgs ea{part, smem_u32(part), 0, m_begin, m_end, warp, lane, row0, 0.0f, true,
-                            nullptr, 0, p.out_dtype, nullptr, 0};
+                            nullptr, 0, p.out_dtype, nullptr, 0, &p.push};
       const int col0 = tile_in_seg * (kRowTile / 2);
       if (p.out_dtype == BQ_DTYPE_BF16)
         silu_pair_emit<__nv_bfloat16>(ea, part, sc, p.pair.hq, p.pair.ld_hq, col0);
@@ -724,7 +767,36 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       }
     }
   }
+  if (p.push.n > 0) {
+    // every store of this CTA is ordered before its arrival on every rank
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int d = 0; d < p.push.n; ++d)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push.flag[d]) : "memory");
+    }
+  }
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// Waits (bounded) until `flag` has counted `count` more arrivals than at the end of the
+// previous wait, i.e. until every CTA of every rank's push launch has stored its share into
+// this rank's gathered buffer.  One thread; the arrival total is kept in `seen`.
+__global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, unsigned int count,
+                                 unsigned int* status) {
+  const unsigned int target = *seen + count;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - target) >= 0) break;
+    if (clock64() - t0 > kSpinLimitCycles) {
+      atomicExch(status, (unsigned int)kErrDeviceWait);
+      break;
+    }
+  }
+  *seen = target;
+  __threadfence();
 }
 
 // ---------------------------------------------------------------------------
@@ -1526,7 +1598,7 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   const int smem = tile_bytes + kBarrierBytes + 1024;
   if (smem > kMaxSmem) return kErrUnsupported;
   if (p.pair.on) p.pair.expected = (unsigned)((p.seg[0].n / kRowTile) * p.seg[0].split);
-  if (p.fuse.mode != 0 || p.pair.on) {
+  if (p.fuse.mode != 0 || (p.pair.on && p.push.n == 0)) {
     // the in-kernel quantizer waits on the whole grid: every CTA must be resident
     const int cap = max_resident_ctas(cluster, smem);
     if (getenv("BQ_DEBUG"))
@@ -1722,7 +1794,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
                 const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
                 const FuseParams* fuse, const void* const* res = nullptr,
                 const int64_t* ld_res = nullptr, const PairSilu* pair = nullptr,
-                int split_forced = 0) {
+                int split_forced = 0, const PushParams* push = nullptr) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
@@ -1734,7 +1806,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   for (int i = 0; i < n_seg; ++i) {   // argument checks first: no CUDA call before they pass
     if (!wq[i] || !sw[i] || N[i] <= 0) return kErrBadArg;
     if (N[i] % 16 || !aligned_to(wq[i], 16)) return kErrUnsupported;
-    if (pair == nullptr) {   // the pair form writes codes of h, not y
+    if (pair == nullptr && push == nullptr) {   // the pair and push forms do not write y
       if (!y[i]) return kErrBadArg;
       if (ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(y[i], out_align)) return kErrUnsupported;
     }
@@ -1743,6 +1815,10 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   const bool stream_path = M <= g_opt_stream_max_m;
   if ((fuse || pair) && !stream_path) return kErrUnsupported;   // decode-regime forms only
   if (pair && (fuse || res || n_seg != 1)) return kErrBadArg;
+  if (push) {
+    if (!stream_path) return kErrUnsupported;
+    if (fuse || res || n_seg != 1) return kErrBadArg;
+  }
   if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
     if (!stream_path || ld_res == nullptr) return kErrUnsupported;
     for (int i = 0; i < n_seg; ++i)
@@ -1772,6 +1848,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.pair.on = 1;
     p.pair.words = static_cast<unsigned int*>(ws);
   }
+  if (push) p.push = *push;
 
   const bool pair_path = !stream_path && g_opt_pair != 0;
   const int w_box_rows = (stream_path || pair_path) ? kRowTile : kTileN;
@@ -1780,8 +1857,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
-    p.seg[i].y = pair ? nullptr : y[i];
-    p.seg[i].ldy = pair ? 0 : ldy[i];
+    p.seg[i].y = (pair || push) ? nullptr : y[i];
+    p.seg[i].ldy = (pair || push) ? 0 : ldy[i];
     p.seg[i].split_forced = split_forced;
     p.seg[i].res = res ? res[i] : nullptr;
     p.seg[i].ld_res = res ? ld_res[i] : 0;
@@ -1798,7 +1875,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    if (!fuse && !res && !pair && g_opt_decode_kernel != 1) {
+    if (!fuse && !res && !pair && !push && g_opt_decode_kernel != 1) {
       const size_t need = persist_scratch_bytes(device_sms(), n_seg, mma_n);
       if (ws_bytes >= need) return launch_persist(tm_x, maps, p, ws, stream);
       if (g_opt_decode_kernel == 2) return kErrWorkspace;
@@ -1896,6 +1973,87 @@ extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const
   const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight((int)I, k_blocks) : 1;
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
                      nullptr, nullptr, nullptr, &pair, split);
+}
+
+namespace {
+int fill_push(PushParams* pp, int n_peers, void* const* dst, int64_t ld, void* const* flags,
+              int64_t width, size_t align) {
+  if (n_peers < 1 || n_peers > kMaxPeers || !dst || !flags) return kErrBadArg;
+  if (ld < width || ld % 4) return kErrUnsupported;
+  memset(pp, 0, sizeof(*pp));
+  pp->n = n_peers;
+  pp->ld = ld;
+  for (int i = 0; i < n_peers; ++i) {
+    if (!dst[i] || !flags[i]) return kErrBadArg;
+    if (!aligned_to(dst[i], align) || !aligned_to(flags[i], 4)) return kErrUnsupported;
+    pp->dst[i] = dst[i];
+    pp->flag[i] = static_cast<unsigned int*>(flags[i]);
+  }
+  return kOk;
+}
+}  // namespace
+
+extern "C" int bq_push_signal_count(int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0 || K > 0x7fffff00LL) return 0;
+  const int k_blocks = (int)((K + kBK - 1) / kBK);
+  return (int)((rows + kRowTile - 1) / kRowTile) * split_for_weight(rows, k_blocks);
+}
+
+extern "C" int bq_push_signal_count_paired(int64_t I, int64_t K) {
+  if (I <= 0 || K <= 0 || K > 0x7fffff00LL) return 0;
+  const int k_blocks = (int)((K + kBK - 1) / kBK);
+  return (int)((2 * I + kRowTile - 1) / kRowTile) * split_for_weight(I, k_blocks);
+}
+
+extern "C" int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const float* sw,
+                                 int out_dtype, int64_t M, int64_t N, int64_t K, int n_peers,
+                                 void* const* y_dst, int64_t ldy, void* const* flags, void* ws,
+                                 size_t ws_bytes, void* stream) {
+  PushParams push;
+  if (int rc = fill_push(&push, n_peers, y_dst, ldy, flags, N, out_dtype == BQ_DTYPE_F32 ? 16 : 8))
+    return rc;
+  const void* wqs[1] = {wq};
+  const float* sws[1] = {sw};
+  void* ys[1] = {nullptr};
+  const int64_t Ns[1] = {N};
+  const int64_t ldys[1] = {0};
+  return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes, stream,
+                     nullptr, nullptr, nullptr, nullptr, 0, &push);
+}
+
+extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
+                                         const float* sw_gate, const float* sw_up, int64_t M,
+                                         int64_t I, int64_t K, int act_dtype, int n_peers,
+                                         void* const* h_dst, int64_t ld_h, void* const* flags,
+                                         void* ws, size_t ws_bytes, void* stream) {
+  if (!wq_pair || !sw_gate || !sw_up || I <= 0) return kErrBadArg;
+  if (I % (kRowTile / 2)) return kErrUnsupported;
+  PushParams push;
+  if (int rc = fill_push(&push, n_peers, h_dst, ld_h, flags, I, act_dtype == BQ_DTYPE_F32 ? 8 : 4))
+    return rc;
+  PairSilu pair;
+  memset(&pair, 0, sizeof(pair));
+  pair.sw_up = sw_up;
+  const void* wqs[1] = {wq_pair};
+  const float* sws[1] = {sw_gate};
+  void* ys[1] = {nullptr};
+  const int64_t Ns[1] = {2 * I};
+  const int64_t ldys[1] = {0};
+  const int k_blocks = (int)((K + kBK - 1) / kBK);
+  const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight(I, k_blocks) : 1;
+  return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
+                     nullptr, nullptr, nullptr, &pair, split, &push);
+}
+
+extern "C" int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word,
+                            void* stream) {
+  if (!flag || !seen || !status_word || count == 0) return kErrBadArg;
+  if (!aligned_to(flag, 4) || !aligned_to(seen, 4) || !aligned_to(status_word, 4)) return kErrUnsupported;
+  wait_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned int*>(flag), static_cast<unsigned int*>(seen), count,
+      static_cast<unsigned int*>(status_word));
+  if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
+  return kOk;
 }
 
 extern "C" int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const float* sw,

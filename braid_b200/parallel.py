@@ -12,8 +12,10 @@ the benchmark configuration defines:
     scale on all ranks and identical to the single-GPU value), computes its slice of the down
     projection, and the bf16 output slices are all-gathered into `[M, H]`.
 
-Weight shards keep the per-tensor scale of the WHOLE weight, so results equal the single-GPU
-ones bit for bit.  `ops` is the module providing `quantize_act`, `fp8_matmul_grouped` and
+Weight shards keep the per-tensor scale of the WHOLE weight, so scales and FP8 codes equal the
+single-GPU ones; a GEMM output can differ from the single-GPU one in its last bit because the K
+slicing of the weight-streaming kernel follows the shape of the shard it is given (with the
+order-independent stand-in used on CPU the results are bit-identical).  `ops` is the module providing `quantize_act`, `fp8_matmul_grouped` and
 `FP8Weight` (default: `braid_b200.quant`); the CPU tests drive the sharding and gather logic with
 a stand-in over gloo.
 """
@@ -99,5 +101,140 @@ class ColumnParallelMLP:
         (y_local,) = ops.fp8_matmul_grouped(hq, sh, (self.down,), out_dtype=x.dtype)
         y = gather_columns(y_local, self.group, [hi - lo for lo, hi in self.h_ranges])
         return y.reshape(*lead, self.H)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------------------------
+# The same MLP without a collective call: the GEMM epilogues store into every rank's gathered
+# buffer through peer-mapped pointers and signal per-rank arrival counters.
+# ---------------------------------------------------------------------------------------------
+class PeerBuffers:
+    """One rank's gathered buffers and counters, plus where the other ranks' copies are.
+
+    `h` `[rows_max, I]` and `y` `[rows_max, H]` receive every rank's column slice; `sync` holds
+    the two arrival counters (h, y) that the other ranks increment.  `seen` and `status` are
+    private to the rank.  `addresses(r)` gives rank r's (h, y, sync) device addresses as they are
+    valid on THIS rank."""
+
+    def __init__(self, rows_max: int, inter: int, hidden: int, dtype: torch.dtype, device):
+        self.h = torch.zeros((rows_max, inter), dtype=dtype, device=device)
+        self.y = torch.zeros((rows_max, hidden), dtype=dtype, device=device)
+        self.sync = torch.zeros(8, dtype=torch.int32, device=device)
+        self.seen = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.peers: list[tuple[int, int, int]] = []     # per rank: (h, y, sync) addresses
+        self._keep: list = []                            # imported peer tensors stay alive
+
+    def local_addresses(self) -> tuple[int, int, int]:
+        return self.h.data_ptr(), self.y.data_ptr(), self.sync.data_ptr()
+
+    def connect_ipc(self, group) -> None:
+        """Exchange CUDA IPC handles of (h, y, sync) with every rank of `group` (one process per
+        GPU on one node) and map the peers' buffers into this process."""
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        mine = [(t.untyped_storage()._share_cuda_(), t.storage_offset() * t.element_size())
+                for t in (self.h, self.y, self.sync)]
+        everyone: list = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.peers = []
+        for r in range(world):
+            if r == rank:
+                self.peers.append(self.local_addresses())
+                continue
+            addrs = []
+            for handle, byte_offset in everyone[r]:
+                st = torch.UntypedStorage._new_shared_cuda(*handle)
+                view = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st)
+                # a copy between the two devices makes torch enable peer access for this pair
+                probe = torch.empty(1, dtype=torch.uint8, device=self.h.device)
+                probe.copy_(view[:1])
+                self._keep.append(view)
+                addrs.append(view.data_ptr() + byte_offset)
+            self.peers.append(tuple(addrs))
+        torch.cuda.synchronize(self.h.device)
+        dist.barrier(group=group)
+
+    def connect_local(self, all_buffers: list["PeerBuffers"]) -> None:
+        """Several ranks emulated in ONE process on one GPU (tests): plain addresses."""
+        self.peers = [b.local_addresses() for b in all_buffers]
+
+
+class FusedColumnParallelMLP(ColumnParallelMLP):
+    """`ColumnParallelMLP` with both all-gathers folded into the producing GEMMs (decode sizes).
+
+    gate/up shard: one paired GEMM whose epilogue forms this rank's slice of SiLU(gate)*up and
+    stores it into every rank's `h` buffer; down shard: one GEMM whose epilogue stores its slice
+    into every rank's `y` buffer.  Each exchange is followed by a one-thread wait kernel on the
+    rank's own arrival counter (bounded: a wait that runs out raises `status`).  Five launches
+    per rank and no collective.  Buffers are reused from call to call: a rank cannot start
+    writing exchange n+1 into a peer before that peer has finished reading exchange n, because
+    its own exchange n completes only after every peer has launched past that read."""
+
+    def __init__(self, gate, up, down, group=None, ops=None, rows_max: int = 256,
+                 dtype: torch.dtype = torch.bfloat16, world: int | None = None, rank: int | None = None):
+        if world is None:
+            super().__init__(gate, up, down, group, ops)
+        else:                                   # emulated ranks (tests): no process group
+            self._init_shards(gate, up, down, ops, world, rank)
+        widths = {hi - lo for lo, hi in self.i_ranges} | {hi - lo for lo, hi in self.h_ranges}
+        if any(w % 64 for w in widths):
+            raise ValueError("shards must be multiples of 64 rows for the paired form")
+        dev = self.gate.data.device
+        self.rows_max, self.dtype = rows_max, dtype
+        self.buffers = PeerBuffers(rows_max, self.I, self.H, dtype, dev)
+        K_in = self.gate.data.shape[1]
+        self.count_h = sum(self.ops.push_signal_count(hi - lo, K_in, paired=True) for lo, hi in self.i_ranges)
+        self.count_y = sum(self.ops.push_signal_count(hi - lo, self.I) for lo, hi in self.h_ranges)
+        self.ops.paired_gate_up(self.gate, self.up)      # built here, outside any capture
+
+    def _init_shards(self, gate, up, down, ops, world, rank):
+        if ops is None:
+            from . import quant as ops
+        self.ops, self.group, self.world, self.rank = ops, None, world, rank
+        I, H = gate.shape
+        self.I, self.H = I, H
+        self.i_ranges = [shard_rows(I, world, r) for r in range(world)]
+        self.h_ranges = [shard_rows(H, world, r) for r in range(world)]
+        (ilo, ihi), (hlo, hhi) = self.i_ranges[rank], self.h_ranges[rank]
+        W = ops.FP8Weight
+        self.gate = W(gate.data[ilo:ihi].contiguous(), gate.scale, (ihi - ilo, H))
+        self.up = W(up.data[ilo:ihi].contiguous(), up.scale, (ihi - ilo, H))
+        self.down = W(down.data[hlo:hhi].contiguous(), down.scale, (hhi - hlo, I))
+
+    def connect(self) -> None:
+        self.buffers.connect_ipc(self.group)
+
+    # -- the four phases (a test interleaves them over emulated ranks; forward() runs them in order)
+    def push_h(self, x2: torch.Tensor) -> None:
+        ops, es = self.ops, torch.empty(0, dtype=self.dtype).element_size()
+        xq, sx = ops.quantize_act(x2)
+        col = self.i_ranges[self.rank][0]
+        ops.gate_up_silu_push(xq, sx, self.gate, self.up, self.dtype,
+                              [h + col * es for h, _, _ in self.buffers.peers], self.I,
+                              [s for _, _, s in self.buffers.peers])
+
+    def wait_h_push_y(self, M: int) -> None:
+        ops, b, es = self.ops, self.buffers, torch.empty(0, dtype=self.dtype).element_size()
+        ops.wait_flag(b.sync[0:1], b.seen[0:1], self.count_h, b.status)
+        hq, sh = ops.quantize_act(b.h[:M])
+        col = self.h_ranges[self.rank][0]
+        ops.gemm_push(hq, sh, self.down, self.dtype, [y + col * es for _, y, _ in b.peers], self.H,
+                      [s + 4 for _, _, s in b.peers])
+
+    def wait_y(self, M: int) -> torch.Tensor:
+        b = self.buffers
+        self.ops.wait_flag(b.sync[1:2], b.seen[1:2], self.count_y, b.status)
+        return b.y[:M]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        *lead, K = x.shape
+        x2 = x.reshape(-1, K)
+        M = x2.shape[0]
+        if M > self.rows_max or M > 256 or x.dtype != self.dtype or not self.buffers.peers:
+            return super().forward(x)                    # prefill sizes: the NCCL form
+        self.push_h(x2)
+        self.wait_h_push_y(M)
+        return self.wait_y(M).reshape(*lead, self.H)
 
     __call__ = forward

@@ -899,6 +899,65 @@ def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: 
 
 
 # ---------------------------------------------------------------------------
+# column-parallel forms: the GEMM epilogue stores into every rank's gathered buffer
+# ---------------------------------------------------------------------------
+def _ptr_array(ptrs: Sequence[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def push_signal_count(rows: int, K: int, paired: bool = False) -> int:
+    """Arrivals one rank's push launch adds to every rank's counter (its active CTAs)."""
+    lib = _require_lib()
+    return int(lib.bq_push_signal_count_paired(rows, K) if paired else lib.bq_push_signal_count(rows, K))
+
+
+def gemm_push(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight, out_dtype: torch.dtype,
+              dst_ptrs: Sequence[int], ld: int, flag_ptrs: Sequence[int]) -> None:
+    """`fp8_matmul` of this rank's weight shard whose epilogue stores the `[M, N_shard]` result
+    into every rank's gathered buffer (`dst_ptrs`: device addresses of this rank's first column
+    in each buffer, row stride `ld`) and then signals every rank's arrival counter."""
+    _check_gemm_inputs(xq, sx)
+    lib = _require_lib()
+    M, K = xq.shape
+    rc = lib.bq_gemm_w8a8_push(xq.data_ptr(), w.data.data_ptr(), sx.data_ptr(), w.scale.data_ptr(),
+                               _DTYPE_CODE[out_dtype], M, w.data.shape[0], K, len(dst_ptrs),
+                               _ptr_array(dst_ptrs), ld, _ptr_array(flag_ptrs),
+                               _take_slot(xq.device), 16, _stream_ptr(xq.device))
+    _lib.check(rc, "gemm_push")
+
+
+def gate_up_silu_push(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
+                      act_dtype: torch.dtype, dst_ptrs: Sequence[int], ld: int,
+                      flag_ptrs: Sequence[int]) -> None:
+    """This rank's slice of `F.silu(xq @ gate^T) * (xq @ up^T)` in one launch over the paired
+    shard, stored into every rank's gathered `h` buffer, followed by the signals."""
+    _check_gemm_inputs(xq, sx)
+    lib = _require_lib()
+    paired = paired_gate_up(gate, up)
+    if paired is None:
+        raise ValueError("gate/up shard cannot be paired (rows must be a multiple of 64; build "
+                         "the pair outside stream capture)")
+    M, K = xq.shape
+    rc = lib.bq_gate_up_silu_push_w8a8(xq.data_ptr(), sx.data_ptr(), paired.data_ptr(),
+                                       gate.scale.data_ptr(), up.scale.data_ptr(), M,
+                                       gate.data.shape[0], K, _DTYPE_CODE[act_dtype], len(dst_ptrs),
+                                       _ptr_array(dst_ptrs), ld, _ptr_array(flag_ptrs),
+                                       _take_slot(xq.device), 16, _stream_ptr(xq.device))
+    _lib.check(rc, "gate_up_silu_push")
+
+
+def wait_flag(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.Tensor) -> None:
+    """Stream-ordered bounded wait until the one-word counter `flag` has advanced by `count`
+    beyond `seen` (then `seen += count`).  A wait that runs out sets `status` non-zero."""
+    global _launches
+    lib = _require_lib()
+    _launches += 1
+    rc = lib.bq_wait_flag(flag.data_ptr(), seen.data_ptr(), count, status.data_ptr(),
+                          _stream_ptr(flag.device))
+    _lib.check(rc, "wait_flag")
+
+
+# ---------------------------------------------------------------------------
 # fused sublayer tails (what the reference spells as separate bf16 kernels)
 # ---------------------------------------------------------------------------
 def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,

@@ -265,6 +265,46 @@ int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_p
                                void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * Column-parallel forms for one NVLink/NVSwitch node (no counterpart in the reference, which is
+ * single-GPU; the benchmark configuration defines an N-split MLP with gathered outputs).  The
+ * GEMM of a rank's weight shard stores its output tile straight into the gathered buffer of
+ * EVERY rank -- `dst[i]` are device pointers valid in this process (this rank's own buffer and
+ * the peers' buffers mapped through CUDA IPC), already offset to this rank's first column --
+ * and then every CTA adds 1 to the arrival counter `flags[i]` of each rank with a system-scope
+ * release.  A rank's buffer is complete when its counter has advanced by the sum over ranks of
+ * bq_push_signal_count(shard rows, K); bq_wait_flag waits for exactly that (bounded) in stream
+ * order.  Plain stores and counters only: no collective call, no multicast.  Decode regime
+ * (M <= 256), up to 8 destinations.
+ */
+int bq_push_signal_count(int64_t rows, int64_t K);
+
+/* y shard = Xq . Wq^T * sx * sw pushed to every rank; rows = N of this rank's shard. */
+int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const float* sw,
+                      int out_dtype, int64_t M, int64_t N, int64_t K, int n_peers,
+                      void* const* y_dst, int64_t ldy, void* const* flags,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * h shard = T(T(silu(gate)) * up) of this rank's interleaved gate/up shard (layout as for
+ * bq_gate_up_silu_quant_w8a8, I = columns of this rank) pushed to every rank.  The amax of h
+ * spans all ranks' shards, so quantization is left to bq_quantize_act on the gathered buffer.
+ * Signals bq_push_signal_count_paired(I, K) arrivals per rank.
+ */
+int bq_push_signal_count_paired(int64_t I, int64_t K);
+int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
+                              const float* sw_gate, const float* sw_up, int64_t M, int64_t I,
+                              int64_t K, int act_dtype, int n_peers, void* const* h_dst,
+                              int64_t ld_h, void* const* flags,
+                              void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * One-thread kernel: waits until *flag has advanced by `count` beyond *seen (bounded; a wait
+ * that runs out sets *status_word to BQ_ERR_DEVICE_WAIT and returns), then adds `count` to
+ * *seen.  `flag` is this rank's arrival counter, `seen` a device word owned by this rank.
+ */
+int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word, void* stream);
+
+/*
  * Several projections of ONE quantized activation in a single launch: segment
  * i computes Y_i[M,N_i] = (Xq . Wq_i^T) * sx * sw_i with its own weight scale,
  * so results are bit-identical to n_seg separate bq_gemm_w8a8 calls.  The

@@ -1,0 +1,90 @@
+"""The column-parallel MLP whose GEMM epilogues store into every rank's gathered buffer
+(`FusedColumnParallelMLP`), with the ranks EMULATED on one GPU: every rank's buffers live in this
+process, and the launches are enqueued so that no kernel ever waits for one enqueued after it
+(all pushes of an exchange precede its first wait).  The multi-process form over CUDA IPC runs in
+`bench.py --gpus N` (column_parallel.fused)."""
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from _util import randn_cpu
+
+pytestmark = pytest.mark.gpu
+
+H, I = 4096, 12288
+
+
+def _weights(Q):
+    mk = lambda n, k, s: Q.quantize_weight(randn_cpu((n, k), seed=s, scale=0.02).cuda())  # noqa: E731
+    return mk(I, H, 1), mk(I, H, 2), mk(H, I, 3)
+
+
+def _emulated(Q, world, weights, rows_max=256):
+    from braid_b200.parallel import FusedColumnParallelMLP
+    ranks = [FusedColumnParallelMLP(*weights, ops=Q, rows_max=rows_max, world=world, rank=r)
+             for r in range(world)]
+    for r in ranks:
+        r.buffers.connect_local([q.buffers for q in ranks])
+    return ranks
+
+
+def _sharded_reference(Q, ranks, x):
+    """The unfused spelling of the same sharded computation, shard by shard on one GPU."""
+    xq, sx = Q.quantize_act(x)
+    parts = []
+    for r in ranks:
+        g, u = Q.fp8_matmul_grouped(xq, sx, (r.gate, r.up), out_dtype=x.dtype)
+        parts.append(F.silu(g) * u)
+    h = torch.cat(parts, dim=1)
+    hq, sh = Q.quantize_act(h)
+    return h, torch.cat([Q.fp8_matmul(hq, sh, r.down, out_dtype=x.dtype) for r in ranks], dim=1)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_fused_exchange_equals_the_gathered_spelling(Q, world, M):
+    weights = _weights(Q)
+    ranks = _emulated(Q, world, weights)
+    for call in range(3):                                   # buffers and counters are reused
+        x = randn_cpu((M, H), seed=10 * M + call).cuda()
+        for r in ranks:
+            r.push_h(x)
+        for r in ranks:
+            r.wait_h_push_y(M)
+        outs = [r.wait_y(M).clone() for r in ranks]
+        h_ref, y_ref = _sharded_reference(Q, ranks, x)
+        for r, y in zip(ranks, outs):
+            assert torch.equal(r.buffers.h[:M], h_ref), f"rank {r.rank}: gathered h differs (call {call})"
+            assert torch.equal(y, y_ref), f"rank {r.rank}: gathered y differs (call {call})"
+            assert int(r.buffers.status.item()) == 0
+        # against the unsharded MLP: same codes and scales, GEMM sums within the bf16 tolerance
+        y_one = Q.mlp_forward(x, *weights)
+        err = (outs[0].float() - y_one.float()).abs().max() / y_one.float().abs().max()
+        assert float(err) < 1e-2
+    assert Q.device_status() == 0
+
+
+def test_a_wait_that_nothing_satisfies_runs_out_and_reports(Q):
+    """A counter no rank increments: the wait kernel gives up after its cycle limit (well under
+    a second), raises the status word, and the context stays usable."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    Q.wait_flag(flag, seen, 5, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5                          # BQ_ERR_DEVICE_WAIT
+    assert int(seen.item()) == 5                            # the wait still advances its baseline
+    x = randn_cpu((8, 4096), seed=1).cuda()
+    q, s = Q.quantize_act(x)                                # the device still works
+    assert torch.isfinite(s).all()
+
+
+def test_push_argument_checks(Q):
+    from braid_b200 import _lib
+    lib = _lib.load()
+    assert lib.bq_push_signal_count(4096, 12288) == 32 * 4      # 32 row tiles x 4 K slices
+    assert lib.bq_push_signal_count_paired(1536, 4096) > 0
+    assert lib.bq_push_signal_count(0, 4096) == 0
+    assert lib.bq_wait_flag(None, None, 1, None, None) == _lib.BQ_ERR_BAD_ARG
