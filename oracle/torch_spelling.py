@@ -5,7 +5,7 @@ for the quantizers, exactly as the reference gates its own fused kernel
 (`_quant_arms`, tests/test_quant.py:371-384): torch's CUDA kernels decide what
 `amax / 448.0`, `x / scale`, `F.silu`, `torch.sigmoid` and the bf16 roundings
 evaluate to.  Lines follow braid/model/quant.py:108-115 and :228-229,
-braid/model/mlp.py:48 and braid/model/attention.py:215.
+braid/model/mlp.py:48, braid/model/attention.py:215 and braid/model/norm.py:31-71.
 """
 from __future__ import annotations
 
@@ -32,6 +32,20 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return o * torch.sigmoid(gate)
+
+
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    """braid/model/norm.py:31-45: fp32 norm with the effective gamma, one cast back."""
+    return F.rms_norm(x.float(), (x.shape[-1],), gamma, eps).type_as(x)
+
+
+def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    """braid/model/norm.py:48-71: normalise, round to the activation type, gamma, silu(gate) in fp32."""
+    input_dtype = x.dtype
+    xf = F.rms_norm(x.float(), (x.shape[-1],), None, eps)
+    h = gamma * xf.to(input_dtype)
+    h = h * F.silu(gate.float())
+    return h.to(input_dtype)
 
 
 def scaled_mm(xq, sx, wq, sw, out_dtype=torch.bfloat16):

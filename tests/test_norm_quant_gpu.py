@@ -38,7 +38,7 @@ def test_rms_norm_quant_is_bit_identical(Q, dt, shape):
     for seed in range(3):
         x = randn_cpu(shape, seed=seed * 101 + shape[0], dtype=dt, scale=(0.05, 1.0, 30.0)[seed]).cuda()
         gamma = _gamma(shape[1], seed, spread=(0.02, 0.3, 1.0)[seed])
-        ref = Q.torch_rms_norm(x, gamma, EPS)
+        ref = TS.rms_norm(x, gamma, EPS)
         qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
         assert qa.shape == x.shape and qa.dtype is dt
         bad = int((u8(qa.dense) != u8(ref)).sum())
@@ -54,7 +54,7 @@ def test_rms_norm_quant_many_rows_of_real_width(Q):
         x = randn_cpu((2048, 4096), seed=40 + seed, scale=scale).cuda()
         x[::7] *= 16.0          # rows of very different energy
         gamma = _gamma(4096, seed)
-        ref = Q.torch_rms_norm(x, gamma, EPS)
+        ref = TS.rms_norm(x, gamma, EPS)
         qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
         rows_bad = int((qa.dense != ref).any(dim=1).sum())
         assert rows_bad == 0, f"{rows_bad} of 2048 rows differ at scale {scale}"
@@ -66,16 +66,16 @@ def test_rms_norm_quant_strided_rows_leading_dims_and_fallback(Q):
     wide = randn_cpu((16, 8192), seed=2).cuda()
     x = wide[:, :4096]                                  # row stride 8192
     qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
-    ref = Q.torch_rms_norm(x, gamma, EPS)
+    ref = TS.rms_norm(x, gamma, EPS)
     assert torch.equal(qa.dense, ref)
     _same(qa, ref, "strided")
     x3 = randn_cpu((4, 3, 4096), seed=3).cuda()         # [B, T, H] as the layer sees it
     qa = Q.rms_norm_quant(x3, gamma, EPS, keep_dense=True)
     assert qa.shape == x3.shape and qa.dense.shape == x3.shape and qa.q.shape == (12, 4096)
-    _same(qa, Q.torch_rms_norm(x3, gamma, EPS), "3-d")
+    _same(qa, TS.rms_norm(x3, gamma, EPS), "3-d")
     big = randn_cpu((4096, 4096), seed=4).cuda()        # more rows than fit at once: two steps
     qa = Q.rms_norm_quant(big, gamma, EPS, keep_dense=True)
-    ref = Q.torch_rms_norm(big, gamma, EPS)
+    ref = TS.rms_norm(big, gamma, EPS)
     assert torch.equal(qa.dense, ref)
     _same(qa, ref, "4096 rows")
 
@@ -88,14 +88,14 @@ def test_rms_norm_quant_degenerate_values(Q):
     x = randn_cpu((4, 4096), seed=6).cuda()
     x[2, 100] = float("nan")
     qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
-    ref = Q.torch_rms_norm(x, gamma, EPS)
+    ref = TS.rms_norm(x, gamma, EPS)
     assert torch.isnan(qa.scale).all()
     assert torch.equal(torch.isnan(qa.dense), torch.isnan(ref))
     qr, sr = TS.quantize_act(ref)
     assert int((u8(qa.q) != u8(qr)).sum()) == 0
     huge = torch.full((2, 4096), 60000.0, dtype=torch.bfloat16, device="cuda")
     qa = Q.rms_norm_quant(huge, gamma, EPS, keep_dense=True)
-    ref = Q.torch_rms_norm(huge, gamma, EPS)
+    ref = TS.rms_norm(huge, gamma, EPS)
     assert torch.equal(qa.dense, ref)
     _same(qa, ref, "huge")
 
@@ -110,7 +110,7 @@ def test_gated_rms_norm_quant_is_bit_identical(Q, ydt, rows, heads):
         z = randn_cpu((rows, heads * D), seed=seed * 19 + rows + 1, scale=(1.0, 3.0, 8.0)[seed]).cuda()
         gamma = _gamma(D, seed, spread=(0.02, 0.3, 1.0)[seed])
         core = y.to(torch.bfloat16).reshape(-1, D)            # braid/model/gdn.py:383
-        ref = Q.torch_rms_norm_gated(core, z.reshape(-1, D), gamma, EPS).reshape(rows, heads * D)
+        ref = TS.rms_norm_gated(core, z.reshape(-1, D), gamma, EPS).reshape(rows, heads * D)
         qa = Q.gated_rms_norm_quant(y, z, gamma, EPS, D)
         assert qa.shape == (rows, heads * D) and qa.dtype is torch.bfloat16
         _same(qa, ref, f"{ydt} rows {rows} heads {heads} seed {seed}")
@@ -122,11 +122,11 @@ def test_gated_rms_norm_quant_many_rows_and_nan(Q):
     y[::5] *= 40.0
     z = randn_cpu((1024, heads * D), seed=4, scale=2.0).cuda()
     gamma = _gamma(D, 9)
-    ref = Q.torch_rms_norm_gated(y.to(torch.bfloat16).reshape(-1, D), z.reshape(-1, D), gamma,
+    ref = TS.rms_norm_gated(y.to(torch.bfloat16).reshape(-1, D), z.reshape(-1, D), gamma,
                                  EPS).reshape(1024, heads * D)
     _same(Q.gated_rms_norm_quant(y, z, gamma, EPS, D), ref, "1024 rows")
     z[7, 300] = float("nan")
-    ref = Q.torch_rms_norm_gated(y.to(torch.bfloat16).reshape(-1, D), z.reshape(-1, D), gamma,
+    ref = TS.rms_norm_gated(y.to(torch.bfloat16).reshape(-1, D), z.reshape(-1, D), gamma,
                                  EPS).reshape(1024, heads * D)
     qa = Q.gated_rms_norm_quant(y, z, gamma, EPS, D)
     assert torch.isnan(qa.scale).all()
@@ -143,7 +143,7 @@ def test_consumers_take_the_quantized_activation(Q):
     mk = lambda n, k, s: Q.quantize_weight((randn_cpu((n, k), seed=s, scale=0.02)).cuda())  # noqa: E731
     w_qkv, w_z, w_out = mk(8192, H, 13), mk(4096, H, 14), mk(H, 4096, 15)
     w_a = randn_cpu((32, H), seed=16, scale=0.02).cuda()
-    h = Q.torch_rms_norm(x, gamma, EPS)
+    h = TS.rms_norm(x, gamma, EPS)
     want = Q.project(h, w_qkv, w_z, w_a)
     got = Q.project(Q.rms_norm_quant(x, gamma, EPS, keep_dense=True), w_qkv, w_z, w_a)
     for a, b in zip(got, want):
@@ -158,7 +158,7 @@ def test_consumers_take_the_quantized_activation(Q):
     y = randn_cpu((16, 32, 128), seed=20, dtype=torch.float32).cuda()
     z = randn_cpu((16, 1, 4096), seed=21).cuda()
     g128 = _gamma(128, 22)
-    core = Q.torch_rms_norm_gated(y.to(torch.bfloat16).reshape(-1, 128), z.reshape(-1, 128), g128, EPS)
+    core = TS.rms_norm_gated(y.to(torch.bfloat16).reshape(-1, 128), z.reshape(-1, 128), g128, EPS)
     want = Q.linear(core.reshape(16, 1, 4096), w_out)
     got = Q.linear(Q.gated_rms_norm_quant(y, z, g128, EPS, 128), w_out)
     assert got.shape == want.shape and torch.equal(got, want)
