@@ -45,6 +45,7 @@ SIGNATURES = {
                                      _vp, _sz, _vp]),
     "bq_gate_up_silu_quant_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp,
                                           _vp, _sz, _vp]),
+    "bq_enable_peer_access": (_int, [_int]),
     "bq_push_signal_count": (_int, [_i64, _i64]),
     "bq_push_signal_count_paired": (_int, [_i64, _i64]),
     "bq_gemm_w8a8_push": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _int,

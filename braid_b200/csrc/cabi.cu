@@ -48,3 +48,22 @@ extern "C" int bq_read_device_status(void* ws, void* stream, int* status_out) {
   *status_out = static_cast<int>(word);
   return BQ_OK;
 }
+
+extern "C" int bq_enable_peer_access(int peer_device) {
+  int dev = -1, can = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return BQ_ERR_LAUNCH; }
+  if (peer_device < 0) return BQ_ERR_BAD_ARG;
+  if (peer_device == dev) return BQ_OK;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return BQ_ERR_LAUNCH;
+  }
+  if (!can) return BQ_ERR_UNSUPPORTED;
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return BQ_ERR_LAUNCH;
+  }
+  (void)cudaGetLastError();   // "already enabled" is not an error here
+  return BQ_OK;
+}

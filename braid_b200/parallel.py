@@ -146,9 +146,13 @@ class PeerBuffers:
             for handle, byte_offset in everyone[r]:
                 st = torch.UntypedStorage._new_shared_cuda(*handle)
                 view = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st)
-                # a copy between the two devices makes torch enable peer access for this pair
-                probe = torch.empty(1, dtype=torch.uint8, device=self.h.device)
-                probe.copy_(view[:1])
+                if view.device.index == self.h.device.index:
+                    raise RuntimeError("a peer's buffer maps onto this rank's own device: the ranks "
+                                       "of the group must each own a different GPU")
+                # The mapping belongs to the peer device's context in this process; kernels of
+                # THIS rank run on its own device and need peer access to it switched on.
+                from . import quant as _q
+                _q.enable_peer_access(self.h.device, view.device.index)
                 self._keep.append(view)
                 addrs.append(view.data_ptr() + byte_offset)
             self.peers.append(tuple(addrs))

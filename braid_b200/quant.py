@@ -905,6 +905,13 @@ def _ptr_array(ptrs: Sequence[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
 
+def enable_peer_access(local_device: torch.device, peer_index: int) -> None:
+    """Allow kernels on `local_device` to touch memory of GPU `peer_index` mapped into this process."""
+    lib = _require_lib()
+    with torch.cuda.device(local_device):
+        _lib.check(lib.bq_enable_peer_access(int(peer_index)), "enable_peer_access")
+
+
 def push_signal_count(rows: int, K: int, paired: bool = False) -> int:
     """Arrivals one rank's push launch adds to every rank's counter (its active CTAs)."""
     lib = _require_lib()

@@ -278,6 +278,14 @@ int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_p
  */
 int bq_push_signal_count(int64_t rows, int64_t K);
 
+/*
+ * Lets kernels launched on the CURRENT device dereference memory of `peer_device` that this
+ * process has mapped (cudaDeviceEnablePeerAccess; already-enabled is success).  A peer buffer
+ * opened through CUDA IPC is mapped for the peer device's context: without this call a kernel
+ * on the current device faults on it.  BQ_ERR_UNSUPPORTED when the two devices have no peer path.
+ */
+int bq_enable_peer_access(int peer_device);
+
 /* y shard = Xq . Wq^T * sx * sw pushed to every rank; rows = N of this rank's shard. */
 int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const float* sw,
                       int out_dtype, int64_t M, int64_t N, int64_t K, int n_peers,
