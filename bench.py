@@ -317,7 +317,7 @@ def column_parallel_block(dist, rows_list, steps, warmup):
                                   "what": "GEMM epilogues store into every rank's gathered buffer "
                                           "through peer pointers; one-thread wait kernels; no NCCL"}
                 del gf
-                dist.barrier()
+                fmlp.close()
                 del fmlp
             except Exception as e:  # noqa: BLE001
                 entry["fused"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}

@@ -1,6 +1,7 @@
 // Entry points of the C ABI that are not kernels: version, status text, the
 // tuning switches and the read-out of the sticky device status word.
 #include <cuda_runtime.h>
+#include <string.h>
 #include <stdint.h>
 
 #include "../../include/braid_b200.h"
@@ -65,5 +66,60 @@ extern "C" int bq_enable_peer_access(int peer_device) {
     return BQ_ERR_LAUNCH;
   }
   (void)cudaGetLastError();   // "already enabled" is not an error here
+  return BQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Buffers that other processes of the node map into their own device's address space
+// ---------------------------------------------------------------------------------------------
+// The importing side must open the handle with ITS OWN device current: the mapping then belongs
+// to that device's context and its kernels may dereference it (peer access is switched on by the
+// open).  A mapping opened under the exporting device's context of the importing process is not
+// reachable from kernels of another device, whatever peer access says.
+extern "C" int bq_peer_alloc(size_t bytes, void** ptr_out, void* handle_out) {
+  if (bytes == 0 || ptr_out == nullptr || handle_out == nullptr) return BQ_ERR_BAD_ARG;
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) { (void)cudaGetLastError(); return BQ_ERR_LAUNCH; }
+  cudaIpcMemHandle_t h;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+      cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    (void)cudaFree(p);
+    return BQ_ERR_LAUNCH;
+  }
+  memcpy(handle_out, &h, sizeof(h));
+  *ptr_out = p;
+  return BQ_OK;
+}
+
+extern "C" int bq_peer_free(void* ptr) {
+  if (ptr == nullptr) return BQ_ERR_BAD_ARG;
+  if (cudaFree(ptr) != cudaSuccess) { (void)cudaGetLastError(); return BQ_ERR_LAUNCH; }
+  return BQ_OK;
+}
+
+extern "C" int bq_peer_open(const void* handle, void** ptr_out) {
+  if (handle == nullptr || ptr_out == nullptr) return BQ_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || p == nullptr) {
+    (void)cudaGetLastError();
+    return BQ_ERR_UNSUPPORTED;
+  }
+  // a copy through the runtime reports a bad mapping as an error code instead of a kernel fault
+  unsigned int probe = 0;
+  if (cudaMemcpy(&probe, p, sizeof(probe), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    (void)cudaGetLastError();
+    (void)cudaIpcCloseMemHandle(p);
+    return BQ_ERR_UNSUPPORTED;
+  }
+  *ptr_out = p;
+  return BQ_OK;
+}
+
+extern "C" int bq_peer_close(void* ptr) {
+  if (ptr == nullptr) return BQ_ERR_BAD_ARG;
+  if (cudaIpcCloseMemHandle(ptr) != cudaSuccess) { (void)cudaGetLastError(); return BQ_ERR_LAUNCH; }
   return BQ_OK;
 }

@@ -109,59 +109,95 @@ class ColumnParallelMLP:
 # The same MLP without a collective call: the GEMM epilogues store into every rank's gathered
 # buffer through peer-mapped pointers and signal per-rank arrival counters.
 # ---------------------------------------------------------------------------------------------
+class _DeviceBlock:
+    """Raw device memory handed to torch through the CUDA array interface (no copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
 class PeerBuffers:
     """One rank's gathered buffers and counters, plus where the other ranks' copies are.
 
     `h` `[rows_max, I]` and `y` `[rows_max, H]` receive every rank's column slice; `sync` holds
-    the two arrival counters (h, y) that the other ranks increment.  `seen` and `status` are
-    private to the rank.  `addresses(r)` gives rank r's (h, y, sync) device addresses as they are
-    valid on THIS rank."""
+    the two arrival counters (h, y) that the other ranks increment.  The three live in ONE device
+    allocation made by the library (`bq_peer_alloc`), because it has to be exported to the other
+    processes as a whole; `seen` and `status` are private to the rank.  `peers[r]` is rank r's
+    (h, y, sync) device addresses as they are valid on THIS rank."""
 
-    def __init__(self, rows_max: int, inter: int, hidden: int, dtype: torch.dtype, device):
-        self.h = torch.zeros((rows_max, inter), dtype=dtype, device=device)
-        self.y = torch.zeros((rows_max, hidden), dtype=dtype, device=device)
-        self.sync = torch.zeros(8, dtype=torch.int32, device=device)
-        self.seen = torch.zeros(2, dtype=torch.int32, device=device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.peers: list[tuple[int, int, int]] = []     # per rank: (h, y, sync) addresses
-        self._keep: list = []                            # imported peer tensors stay alive
+    def __init__(self, rows_max: int, inter: int, hidden: int, dtype: torch.dtype, device, ops=None):
+        import ctypes
+        from . import _lib
+        self.device = torch.device(device)
+        es = torch.empty(0, dtype=dtype).element_size()
+        self.off_h = 0
+        self.off_y = _align(rows_max * inter * es)
+        self.off_sync = self.off_y + _align(rows_max * hidden * es)
+        self.nbytes = self.off_sync + 256
+        self._lib = _lib.load()
+        ptr = ctypes.c_void_p()
+        self.handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.bq_peer_alloc(self.nbytes, ctypes.byref(ptr), self.handle), "peer_alloc")
+        self.base = int(ptr.value)
+        raw = torch.as_tensor(_DeviceBlock(self.base, self.nbytes), device=self.device)
+        self._raw = raw
+        self.h = raw[self.off_h:self.off_h + rows_max * inter * es].view(dtype).view(rows_max, inter)
+        self.y = raw[self.off_y:self.off_y + rows_max * hidden * es].view(dtype).view(rows_max, hidden)
+        self.sync = raw[self.off_sync:self.off_sync + 256].view(torch.int32)
+        self.seen = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.peers: list[tuple[int, int, int]] = []
+        self._opened: list[int] = []
 
-    def local_addresses(self) -> tuple[int, int, int]:
-        return self.h.data_ptr(), self.y.data_ptr(), self.sync.data_ptr()
+    def _addresses(self, base: int) -> tuple[int, int, int]:
+        return base + self.off_h, base + self.off_y, base + self.off_sync
 
     def connect_ipc(self, group) -> None:
-        """Exchange CUDA IPC handles of (h, y, sync) with every rank of `group` (one process per
-        GPU on one node) and map the peers' buffers into this process."""
+        """Exchange the 64-byte handles with every rank of `group` (one process per GPU on one
+        node) and map each peer's allocation for THIS rank's device."""
+        import ctypes
+        from . import _lib
         world, rank = dist.get_world_size(group), dist.get_rank(group)
-        mine = [(t.untyped_storage()._share_cuda_(), t.storage_offset() * t.element_size())
-                for t in (self.h, self.y, self.sync)]
         everyone: list = [None] * world
-        dist.all_gather_object(everyone, mine, group=group)
+        dist.all_gather_object(everyone, bytes(self.handle.raw), group=group)
         self.peers = []
-        for r in range(world):
-            if r == rank:
-                self.peers.append(self.local_addresses())
-                continue
-            addrs = []
-            for handle, byte_offset in everyone[r]:
-                st = torch.UntypedStorage._new_shared_cuda(*handle)
-                view = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st)
-                if view.device.index == self.h.device.index:
-                    raise RuntimeError("a peer's buffer maps onto this rank's own device: the ranks "
-                                       "of the group must each own a different GPU")
-                # The mapping belongs to the peer device's context in this process; kernels of
-                # THIS rank run on its own device and need peer access to it switched on.
-                from . import quant as _q
-                _q.enable_peer_access(self.h.device, view.device.index)
-                self._keep.append(view)
-                addrs.append(view.data_ptr() + byte_offset)
-            self.peers.append(tuple(addrs))
-        torch.cuda.synchronize(self.h.device)
+        with torch.cuda.device(self.device):
+            for r in range(world):
+                if r == rank:
+                    self.peers.append(self._addresses(self.base))
+                    continue
+                p = ctypes.c_void_p()
+                buf = ctypes.create_string_buffer(everyone[r], 64)
+                _lib.check(self._lib.bq_peer_open(buf, ctypes.byref(p)), "peer_open")
+                self._opened.append(int(p.value))
+                self.peers.append(self._addresses(int(p.value)))
+        torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
 
     def connect_local(self, all_buffers: list["PeerBuffers"]) -> None:
         """Several ranks emulated in ONE process on one GPU (tests): plain addresses."""
-        self.peers = [b.local_addresses() for b in all_buffers]
+        self.peers = [b._addresses(b.base) for b in all_buffers]
+
+    def close(self, group=None) -> None:
+        """Unmap the peers' buffers, then (after everyone has) free this rank's own."""
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self._lib.bq_peer_close(p)
+            self._opened = []
+            if group is not None:
+                dist.barrier(group=group)
+            if self.base:
+                self.h = self.y = self.sync = self._raw = None
+                self._lib.bq_peer_free(self.base)
+                self.base = 0
+        self.peers = []
 
 
 class FusedColumnParallelMLP(ColumnParallelMLP):
@@ -208,6 +244,9 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
 
     def connect(self) -> None:
         self.buffers.connect_ipc(self.group)
+
+    def close(self) -> None:
+        self.buffers.close(self.group)
 
     # -- the four phases (a test interleaves them over emulated ranks; forward() runs them in order)
     def push_h(self, x2: torch.Tensor) -> None:

@@ -286,6 +286,19 @@ int bq_push_signal_count(int64_t rows, int64_t K);
  */
 int bq_enable_peer_access(int peer_device);
 
+/*
+ * Set-up calls of the column-parallel form (never on the hot path).  bq_peer_alloc makes a
+ * zeroed device buffer on the current device and a 64-byte handle other PROCESSES of the node
+ * can open; bq_peer_open maps such a buffer for the CURRENT device of the calling process (peer
+ * access included) and verifies the mapping with a copy through the runtime, so a bad mapping is
+ * an error code, never a kernel fault.  A handle may be opened once per process and device.
+ */
+#define BQ_PEER_HANDLE_BYTES 64
+int bq_peer_alloc(size_t bytes, void** ptr_out, void* handle_out /* BQ_PEER_HANDLE_BYTES */);
+int bq_peer_free(void* ptr);
+int bq_peer_open(const void* handle /* BQ_PEER_HANDLE_BYTES */, void** ptr_out);
+int bq_peer_close(void* ptr);
+
 /* y shard = Xq . Wq^T * sx * sw pushed to every rank; rows = N of this rank's shard. */
 int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const float* sw,
                       int out_dtype, int64_t M, int64_t N, int64_t K, int n_peers,

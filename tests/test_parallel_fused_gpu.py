@@ -64,6 +64,8 @@ def test_fused_exchange_equals_the_gathered_spelling(Q, world, M):
         err = (outs[0].float() - y_one.float()).abs().max() / y_one.float().abs().max()
         assert float(err) < 1e-2
     assert Q.device_status() == 0
+    for r in ranks:
+        r.buffers.close()
 
 
 def test_a_wait_that_nothing_satisfies_runs_out_and_reports(Q):
