@@ -73,6 +73,8 @@ def _worker(rank, world, port, hidden, inter, rows, ret):
         gate, up, down = mk(inter, hidden), mk(inter, hidden), mk(hidden, inter)
         x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
         mlp = ColumnParallelMLP(gate, up, down, group=None, ops=ops)
+        if rows >= 40:                      # exercise the chunked, overlapped form on CPU sizes
+            mlp.pipeline_rows, mlp.pipeline_from = 16, 32
         y = mlp(x.view(1, rows, hidden))
         # single-process reference with the same stand-in
         xq, sx = ops.quantize_act(x)
@@ -86,7 +88,7 @@ def _worker(rank, world, port, hidden, inter, rows, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,hidden,inter,rows", [(2, 64, 96, 5), (2, 48, 160, 16)])
+@pytest.mark.parametrize("world,hidden,inter,rows", [(2, 64, 96, 5), (2, 48, 160, 16), (2, 64, 96, 50)])
 def test_column_parallel_equals_unsharded(world, hidden, inter, rows):
     port = 29500 + (os.getpid() % 2000)
     mgr = mp.Manager()
