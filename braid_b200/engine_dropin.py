@@ -177,9 +177,10 @@ class ArmResult:
 
 
 def build_engine(ckpt, quant: str = "all", use_kernels: bool = False,
-                 state_dtype: torch.dtype = torch.float16):
+                 state_dtype: torch.dtype = torch.float16, dtype: torch.dtype = torch.bfloat16):
+    """`dtype` must be the dtype the checkpoint's projection weights were created in."""
     engine_mod = importlib.import_module("braid.model.engine")
-    return engine_mod.Engine.from_checkpoint(ckpt, device=ckpt["norm"].device, dtype=torch.bfloat16,
+    return engine_mod.Engine.from_checkpoint(ckpt, device=ckpt["norm"].device, dtype=dtype,
                                              use_kernels=use_kernels, quant=quant,
                                              state_dtype=state_dtype)
 

@@ -177,3 +177,50 @@ def test_activate_is_reversible(Q, ref_engine_env):
     assert all(a is not b for a, b in zip(state(), stock))
     E.deactivate()
     assert state() == stock
+
+
+@pytest.mark.parametrize("case", ["fp32_engine", "4b_widths"])
+def test_other_engine_shapes_capture_and_replay_identically(Q, case):
+    """The same gate on (a) an fp32 engine (fp32 activations through every fused kernel: the
+    reference keeps fp32 engines for its identity gates) and (b) the 4B member's widths
+    (hidden 2560, MLP 9216), both with every group quantized and all fusions on."""
+    import importlib
+    from braid_b200 import engine_dropin as E
+    sys.path.insert(0, str(REF))
+    sys.path.insert(0, str(ROOT / "baseline"))
+    _purge()
+    eng = cache = dec = ckpt = None
+    try:
+        import ref_kernels
+        use_kernels = ref_kernels.available()
+        if use_kernels:
+            ref_kernels.attach()
+        graph_mod = importlib.import_module("braid.model.graph")
+        dtype = torch.float32 if case == "fp32_engine" else torch.bfloat16
+        cfg = E.text_config(4, VOCAB) if case == "fp32_engine" else \
+            E.text_config(4, VOCAB, hidden_size=2560, intermediate_size=9216)
+        ckpt = E.random_checkpoint(cfg, torch.device("cuda", 0), dtype=dtype, seed=4)
+        E.activate()
+        eng = E.build_engine(ckpt, quant="all", use_kernels=use_kernels, dtype=dtype,
+                             state_dtype=torch.float32)
+        n0 = Q.launch_count()
+        cache = _prefilled(E, eng, B)
+        snapshot = cache.snapshot()
+        tokens = torch.arange(100, 100 + B, device="cuda")[:, None]
+        slots = torch.arange(B, device="cuda")
+        eager = eng.decode_step(tokens, cache.select(slots.tolist())).clone()
+        assert eager.dtype is dtype and Q.launch_count() > n0
+        cache.restore(snapshot)
+        dec = graph_mod.GraphedDecoder(eng, cache, buckets=(B,))
+        cache.restore(snapshot)
+        replay = dec.step(tokens, slots)
+        assert torch.isfinite(eager.float()).all() and torch.equal(eager, replay)
+        assert Q.device_status() == 0
+    finally:
+        E.deactivate()
+        del eng, cache, dec, ckpt
+        _purge()
+        sys.path.remove(str(REF))
+        sys.path.remove(str(ROOT / "baseline"))
+        gc.collect()
+        torch.cuda.empty_cache()
