@@ -10,6 +10,7 @@ replays timed with CUDA events; never a sync per call.
 from __future__ import annotations
 
 import json
+import os
 import statistics
 from pathlib import Path
 
@@ -212,7 +213,7 @@ def main(args):
     torch.cuda.set_device(dev)
     Q.warm_fused(True)
     peaks = bench.measured_peaks()
-    out_dir = Path("gpurun_out")
+    out_dir = Path(os.environ.get("BQ_SWEEP_OUT", "gpurun_out"))   # where sweep.json is written
     out_dir.mkdir(exist_ok=True)
     rows = []
     only = getattr(args, "only", None)
