@@ -50,8 +50,6 @@ SIGNATURES = {
     "bq_peer_free": (_int, [_vp]),
     "bq_peer_open": (_int, [_vp, ctypes.POINTER(_vp)]),
     "bq_peer_close": (_int, [_vp]),
-    "bq_push_signal_count": (_int, [_i64, _i64]),
-    "bq_push_signal_count_paired": (_int, [_i64, _i64]),
     "bq_gemm_w8a8_push": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _int,
                                  ctypes.POINTER(_vp), _i64, ctypes.POINTER(_vp), _vp, _sz, _vp]),
     "bq_gate_up_silu_push_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int,

@@ -91,15 +91,18 @@ struct PairSilu {
 
 // Column-parallel form: the output tile (or, in the paired form, h) is stored straight into the
 // gathered buffer of every rank of the node -- plain stores through peer-mapped pointers, this
-// rank's own buffer included -- and every CTA then adds 1 to a counter on each rank with a
-// system-scope release.  No collective call, no multicast.  The pointers already carry this
-// rank's column offset.
+// rank's own buffer included.  The CTAs of the launch count themselves on a local word; the last
+// one to finish adds 1 to a counter on each rank with a system-scope release (one arrival per
+// rank and exchange).  No collective call, no multicast.  The pointers already carry this rank's
+// column offset.
 constexpr int kMaxPeers = 8;
 struct PushParams {
   int n;                          // destinations (0 = not a push launch)
   void* dst[kMaxPeers];
   long long ld;                   // row stride of every destination, elements
   unsigned int* flag[kMaxPeers];  // one arrival counter per destination rank
+  unsigned int* done;             // local: CTAs of this launch that have stored their share
+  unsigned int expected;          // CTAs that store (the active ones)
 };
 
 struct GemmParams {
@@ -768,12 +771,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
   }
   if (p.push.n > 0) {
-    // every store of this CTA is ordered before its arrival on every rank
-    __threadfence_system();
+    // The stores of all threads of this CTA are ordered before thread 0's fence by the barrier
+    // (fences are cumulative); the fence orders them before this CTA's count; the last CTA sees
+    // every count, fences again and only then signals the ranks: every store of the launch
+    // happens before every arrival.
     __syncthreads();
     if (threadIdx.x == 0) {
-      for (int d = 0; d < p.push.n; ++d)
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push.flag[d]) : "memory");
+      __threadfence_system();
+      const unsigned int old = atomicAdd(p.push.done, 1u);
+      if (old == p.push.expected - 1u) {
+        *p.push.done = 0u;                       // ready for the next launch on this scratch
+        __threadfence_system();
+        for (int d = 0; d < p.push.n; ++d)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push.flag[d]) : "memory");
+      }
     }
   }
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
@@ -1598,6 +1609,8 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   const int smem = tile_bytes + kBarrierBytes + 1024;
   if (smem > kMaxSmem) return kErrUnsupported;
   if (p.pair.on) p.pair.expected = (unsigned)((p.seg[0].n / kRowTile) * p.seg[0].split);
+  if (p.push.n > 0)
+    p.push.expected = (unsigned)(((p.seg[0].n + kRowTile - 1) / kRowTile) * p.seg[0].split);
   if (p.fuse.mode != 0 || (p.pair.on && p.push.n == 0)) {
     // the in-kernel quantizer waits on the whole grid: every CTA must be resident
     const int cap = max_resident_ctas(cluster, smem);
@@ -1848,7 +1861,10 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.pair.on = 1;
     p.pair.words = static_cast<unsigned int*>(ws);
   }
-  if (push) p.push = *push;
+  if (push) {
+    p.push = *push;
+    p.push.done = static_cast<unsigned int*>(ws);   // first scratch word: zero between launches
+  }
 
   const bool pair_path = !stream_path && g_opt_pair != 0;
   const int w_box_rows = (stream_path || pair_path) ? kRowTile : kTileN;
@@ -1992,18 +2008,6 @@ int fill_push(PushParams* pp, int n_peers, void* const* dst, int64_t ld, void* c
   return kOk;
 }
 }  // namespace
-
-extern "C" int bq_push_signal_count(int64_t rows, int64_t K) {
-  if (rows <= 0 || K <= 0 || K > 0x7fffff00LL) return 0;
-  const int k_blocks = (int)((K + kBK - 1) / kBK);
-  return (int)((rows + kRowTile - 1) / kRowTile) * split_for_weight(rows, k_blocks);
-}
-
-extern "C" int bq_push_signal_count_paired(int64_t I, int64_t K) {
-  if (I <= 0 || K <= 0 || K > 0x7fffff00LL) return 0;
-  const int k_blocks = (int)((K + kBK - 1) / kBK);
-  return (int)((2 * I + kRowTile - 1) / kRowTile) * split_for_weight(I, k_blocks);
-}
 
 extern "C" int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const float* sw,
                                  int out_dtype, int64_t M, int64_t N, int64_t K, int n_peers,

@@ -253,7 +253,7 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
 
     gate/up shard: one paired GEMM whose epilogue forms this rank's slice of SiLU(gate)*up and
     stores it into every rank's `h` buffer; down shard: one GEMM whose epilogue stores its slice
-    into every rank's `y` buffer.  Each exchange is followed by a one-thread wait kernel on the
+    into every rank's `y` buffer; the last CTA of a launch signals every rank once.  Each exchange is followed by a one-thread wait kernel on the
     rank's own arrival counter (bounded: a wait that runs out raises `status`).  Five launches
     per rank and no collective.  Buffers are reused from call to call: a rank cannot start
     writing exchange n+1 into a peer before that peer has finished reading exchange n, because
@@ -271,9 +271,8 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         dev = self.gate.data.device
         self.rows_max, self.dtype = rows_max, dtype
         self.buffers = PeerBuffers(rows_max, self.I, self.H, dtype, dev)
-        K_in = self.gate.data.shape[1]
-        self.count_h = sum(self.ops.push_signal_count(hi - lo, K_in, paired=True) for lo, hi in self.i_ranges)
-        self.count_y = sum(self.ops.push_signal_count(hi - lo, self.I) for lo, hi in self.h_ranges)
+        # every rank's launch signals each rank once per exchange
+        self.count_h = self.count_y = self.world
         self.ops.paired_gate_up(self.gate, self.up)      # built here, outside any capture
 
     def _init_shards(self, gate, up, down, ops, world, rank):

@@ -912,12 +912,6 @@ def enable_peer_access(local_device: torch.device, peer_index: int) -> None:
         _lib.check(lib.bq_enable_peer_access(int(peer_index)), "enable_peer_access")
 
 
-def push_signal_count(rows: int, K: int, paired: bool = False) -> int:
-    """Arrivals one rank's push launch adds to every rank's counter (its active CTAs)."""
-    lib = _require_lib()
-    return int(lib.bq_push_signal_count_paired(rows, K) if paired else lib.bq_push_signal_count(rows, K))
-
-
 def gemm_push(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight, out_dtype: torch.dtype,
               dst_ptrs: Sequence[int], ld: int, flag_ptrs: Sequence[int]) -> None:
     """`fp8_matmul` of this rank's weight shard whose epilogue stores the `[M, N_shard]` result

@@ -270,13 +270,13 @@ int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_p
  * GEMM of a rank's weight shard stores its output tile straight into the gathered buffer of
  * EVERY rank -- `dst[i]` are device pointers valid in this process (this rank's own buffer and
  * the peers' buffers mapped through CUDA IPC), already offset to this rank's first column --
- * and then every CTA adds 1 to the arrival counter `flags[i]` of each rank with a system-scope
- * release.  A rank's buffer is complete when its counter has advanced by the sum over ranks of
- * bq_push_signal_count(shard rows, K); bq_wait_flag waits for exactly that (bounded) in stream
- * order.  Plain stores and counters only: no collective call, no multicast.  Decode regime
- * (M <= 256), up to 8 destinations.
+ * and the last CTA of the launch to finish then adds 1 to the arrival counter `flags[i]` of each
+ * rank with a system-scope release (the CTAs count themselves on the first word of `ws`, which
+ * must be zero before the first call and is returned to zero).  A rank's buffer is complete when
+ * its counter has advanced by the number of ranks; bq_wait_flag waits for exactly that (bounded)
+ * in stream order.  Plain stores and counters only: no collective call, no multicast.  Decode
+ * regime (M <= 256), up to 8 destinations.
  */
-int bq_push_signal_count(int64_t rows, int64_t K);
 
 /*
  * Lets kernels launched on the CURRENT device dereference memory of `peer_device` that this
@@ -309,9 +309,7 @@ int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const flo
  * h shard = T(T(silu(gate)) * up) of this rank's interleaved gate/up shard (layout as for
  * bq_gate_up_silu_quant_w8a8, I = columns of this rank) pushed to every rank.  The amax of h
  * spans all ranks' shards, so quantization is left to bq_quantize_act on the gathered buffer.
- * Signals bq_push_signal_count_paired(I, K) arrivals per rank.
  */
-int bq_push_signal_count_paired(int64_t I, int64_t K);
 int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
                               const float* sw_gate, const float* sw_up, int64_t M, int64_t I,
                               int64_t K, int act_dtype, int n_peers, void* const* h_dst,

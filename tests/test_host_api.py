@@ -222,18 +222,12 @@ def test_random_checkpoint_runs_through_the_reference_engine_on_cpu():
             del sys.modules[name]
 
 
-def test_push_signal_counts_follow_the_shape_rule():
-    """Host-only arithmetic of the column-parallel form: arrivals per launch = row tiles x K slices
-    of the shard, the paired form counting its 2*I interleaved rows with the K split of one [I, K]
-    weight.  Sums over ranks are what `bq_wait_flag` waits for."""
+def test_push_entry_points_check_their_arguments():
+    """Host-only: the column-parallel entry points refuse missing pointers before any CUDA call."""
     from braid_b200 import _lib
     lib = _lib.load()
-    assert lib.bq_push_signal_count(4096, 12288) == 32 * 4
-    assert lib.bq_push_signal_count(2048, 12288) == 16 * 4
-    assert lib.bq_push_signal_count(512, 12288) == 4 * 4
-    assert lib.bq_push_signal_count(0, 4096) == 0 and lib.bq_push_signal_count(4096, 0) == 0
-    one = lib.bq_push_signal_count(6144, 4096)            # a 2-rank gate shard on its own
-    assert lib.bq_push_signal_count_paired(6144, 4096) == 2 * one
     assert lib.bq_wait_flag(None, None, 1, None, None) == _lib.BQ_ERR_BAD_ARG
     assert lib.bq_gemm_w8a8_push(None, None, None, None, 1, 8, 4096, 4096, 0, None, 4096, None,
                                  None, 0, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_peer_open(None, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_peer_alloc(0, None, None) == _lib.BQ_ERR_BAD_ARG

@@ -81,12 +81,3 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_reports(Q):
     x = randn_cpu((8, 4096), seed=1).cuda()
     q, s = Q.quantize_act(x)                                # the device still works
     assert torch.isfinite(s).all()
-
-
-def test_push_argument_checks(Q):
-    from braid_b200 import _lib
-    lib = _lib.load()
-    assert lib.bq_push_signal_count(4096, 12288) == 32 * 4      # 32 row tiles x 4 K slices
-    assert lib.bq_push_signal_count_paired(1536, 4096) > 0
-    assert lib.bq_push_signal_count(0, 4096) == 0
-    assert lib.bq_wait_flag(None, None, 1, None, None) == _lib.BQ_ERR_BAD_ARG
