@@ -313,9 +313,9 @@ def column_parallel_block(dist, rows_list, steps, warmup):
                 entry["fused"] = {"ms_per_call": msf / steps,
                                   "equals_nccl_form": bool(torch.equal(y_fused, y_nccl)),
                                   "wait_status": int(fmlp.buffers.status.item()),
-                                  "launches_per_call": 5,
+                                  "launches_per_call": 4,
                                   "what": "GEMM epilogues store into every rank's gathered buffer "
-                                          "through peer pointers; one-thread wait kernels; no NCCL"}
+                                          "through peer pointers; arrival waits in the consumer / a one-thread kernel; no NCCL"}
                 del gf
                 fmlp.close()
                 del fmlp

@@ -66,13 +66,43 @@ __device__ __forceinline__ float grid_amax(float m, QuantWs* ws) {
   return s_amax;
 }
 
+// Column-parallel form: every CTA waits (bounded, thread 0 polls with a system-scope acquire)
+// until the arrival counter has advanced by `count` beyond *seen -- i.e. until every rank's push
+// launch has stored its share of the buffer this kernel is about to read.  *seen is advanced by
+// grid_wait_done() once every CTA has read it.
+__device__ __forceinline__ void grid_wait_arrivals(const unsigned int* flag, const unsigned int* seen,
+                                                   unsigned int count, QuantWs* ws) {
+  if (threadIdx.x == 0) {
+    unsigned int base;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(base) : "l"(seen) : "memory");
+    const unsigned int target = base + count;
+    const long long t0 = clock64();
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (static_cast<int>(v - target) >= 0) break;
+      if (clock64() - t0 > bq::kSpinLimitCycles) {
+        atomicExch(&ws->status, (unsigned int)bq::kErrDeviceWait);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
 // Called by thread 0 of every CTA of a multi-CTA grid after it has the global
 // amax: the last CTA to check out returns the scratch to zero, so the next
 // launch (and a graph replay) starts clean.
-__device__ __forceinline__ void grid_depart(QuantWs* ws) {
-  if (gridDim.x == 1 || threadIdx.x != 0) return;
+__device__ __forceinline__ void grid_depart(QuantWs* ws, unsigned int* wait_seen = nullptr,
+                                            unsigned int wait_count = 0u) {
+  if (threadIdx.x != 0) return;
+  if (gridDim.x == 1) {
+    if (wait_seen != nullptr) *wait_seen += wait_count;
+    return;
+  }
   const unsigned int old = atomicAdd(&ws->depart, 1u);
   if (old == gridDim.x - 1) {
+    if (wait_seen != nullptr) *wait_seen += wait_count;   // every CTA has read the old value
     ws->amax_bits = 0u;
     ws->arrive = 0u;
     ws->depart = 0u;

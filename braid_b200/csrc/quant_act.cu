@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
   Pack8<T> held[MAXH];
   Pack8<T> other[MODE == kPlain ? 1 : MAXH];
   bq::pdl_wait_prior_grids();   // the activation is the previous kernel's output
+  if (p.wait_flag != nullptr)
+    grid_wait_arrivals(p.wait_flag, p.wait_seen, p.wait_count, static_cast<QuantWs*>(p.ws));
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) {
     const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
   }
-  grid_depart(static_cast<QuantWs*>(p.ws));
+  grid_depart(static_cast<QuantWs*>(p.ws), p.wait_flag != nullptr ? p.wait_seen : nullptr, p.wait_count);
 }
 
 // Streaming variant for activations that do not fit in the register file of
@@ -100,6 +102,8 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
   bq::pdl_wait_prior_grids();
+  if (p.wait_flag != nullptr)
+    grid_wait_arrivals(p.wait_flag, p.wait_seen, p.wait_count, static_cast<QuantWs*>(p.ws));
   float m = 0.0f;
   for (unsigned int g0 = tid; g0 < p.n_groups; g0 += nthreads * kUnroll) {
     Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
@@ -148,7 +152,7 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     for (unsigned int i = 0; i < p.tail; ++i)
       dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(src[i]), sc), __NV_SATFINITE, __NV_E4M3);
   }
-  grid_depart(static_cast<QuantWs*>(p.ws));
+  grid_depart(static_cast<QuantWs*>(p.ws), p.wait_flag != nullptr ? p.wait_seen : nullptr, p.wait_count);
 }
 
 struct DeviceInfo {
@@ -274,6 +278,30 @@ extern "C" int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out,
   p.n_groups = static_cast<unsigned int>(n / kGroup);
   p.tail = static_cast<unsigned int>(n % kGroup);
   p.groups_per_row = 1;
+  return dispatch_dtype<kPlain>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_quantize_act_after(const void* x, int dtype, int64_t n, void* q_out,
+                                     float* scale_out, const void* flag, void* seen,
+                                     unsigned int count, void* ws, size_t ws_bytes, void* stream) {
+  if (x == nullptr || q_out == nullptr || scale_out == nullptr || n <= 0) return bq::kErrBadArg;
+  if (flag == nullptr || seen == nullptr || count == 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  if (!aligned_to(x, 16) || !aligned_to(q_out, 8) || !aligned_to(flag, 4) || !aligned_to(seen, 4))
+    return bq::kErrUnsupported;
+  if (n / kGroup >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = x;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = scale_out;
+  p.ws = ws;
+  p.n_groups = static_cast<unsigned int>(n / kGroup);
+  p.tail = static_cast<unsigned int>(n % kGroup);
+  p.groups_per_row = 1;
+  p.wait_flag = static_cast<const unsigned int*>(flag);
+  p.wait_seen = static_cast<unsigned int*>(seen);
+  p.wait_count = count;
   return dispatch_dtype<kPlain>(dtype, p, static_cast<cudaStream_t>(stream));
 }
 

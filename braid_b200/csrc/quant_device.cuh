@@ -37,6 +37,11 @@ struct QParams {
   unsigned int chunk;         // sigmoid gate: head width of the strided gate view
   long long chunk_stride;     // sigmoid gate: distance between heads
   int held;                   // groups each thread keeps (hold kernel)
+  // column-parallel form: the input is a gathered buffer other ranks store into; wait until the
+  // arrival counter has advanced by wait_count beyond *wait_seen before loading (nullptr = no wait)
+  const unsigned int* wait_flag;
+  unsigned int* wait_seen;
+  unsigned int wait_count;
 };
 
 template <typename T> struct alignas(16) Pack8 { T v[8]; };

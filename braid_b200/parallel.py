@@ -253,11 +253,12 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
 
     gate/up shard: one paired GEMM whose epilogue forms this rank's slice of SiLU(gate)*up and
     stores it into every rank's `h` buffer; down shard: one GEMM whose epilogue stores its slice
-    into every rank's `y` buffer; the last CTA of a launch signals every rank once.  Each exchange is followed by a one-thread wait kernel on the
-    rank's own arrival counter (bounded: a wait that runs out raises `status`).  Five launches
-    per rank and no collective.  Buffers are reused from call to call: a rank cannot start
-    writing exchange n+1 into a peer before that peer has finished reading exchange n, because
-    its own exchange n completes only after every peer has launched past that read."""
+    into every rank's `y` buffer.  The last CTA of a launch signals every rank once.  The wait
+    for `h` sits inside the quantizer that consumes it; the wait for `y` is a one-thread kernel.
+    Both are bounded (a wait that runs out raises a status word).  Four launches per rank and
+    no collective.  Buffers are reused from call to call: a rank cannot start writing exchange
+    n+1 into a peer before that peer has finished reading exchange n, because its own exchange
+    n completes only after every peer has launched past that read."""
 
     def __init__(self, gate, up, down, group=None, ops=None, rows_max: int = 256,
                  dtype: torch.dtype = torch.bfloat16, world: int | None = None, rank: int | None = None):
@@ -306,8 +307,8 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
 
     def wait_h_push_y(self, M: int) -> None:
         ops, b, es = self.ops, self.buffers, torch.empty(0, dtype=self.dtype).element_size()
-        ops.wait_flag(b.sync[0:1], b.seen[0:1], self.count_h, b.status)
-        hq, sh = ops.quantize_act(b.h[:M])
+        # the wait for every rank's h shard is inside the quantizer's kernel
+        hq, sh = ops.quantize_act_after(b.h[:M], b.sync[0:1], b.seen[0:1], self.count_h)
         col = self.h_ranges[self.rank][0]
         ops.gemm_push(hq, sh, self.down, self.dtype, [y + col * es for _, y, _ in b.peers], self.H,
                       [s + 4 for _, _, s in b.peers])

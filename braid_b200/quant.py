@@ -343,6 +343,25 @@ def quantize_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return q, scale
 
 
+def quantize_act_after(x: torch.Tensor, flag: torch.Tensor, seen: torch.Tensor,
+                       count: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """`quantize_act` of a gathered buffer that other ranks store into: the kernel itself waits
+    (bounded) until the one-word counter `flag` has advanced by `count` beyond `seen`, then
+    quantizes, and advances `seen`.  A wait that runs out shows in `device_status()`."""
+    _check_cuda(x, "quantize_act_after")
+    lib = _require_lib()
+    code = _DTYPE_CODE.get(x.dtype)
+    if code is None or not x.is_contiguous() or x.data_ptr() % 16 or x.numel() == 0:
+        raise ValueError("the gathered buffer must be a contiguous, 16-byte aligned fp32/bf16/fp16 tensor")
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    scale = torch.empty((1, 1), dtype=torch.float32, device=x.device)
+    rc = lib.bq_quantize_act_after(x.data_ptr(), code, x.numel(), q.data_ptr(), scale.data_ptr(),
+                                   flag.data_ptr(), seen.data_ptr(), count,
+                                   _take_slot(x.device), 16, _stream_ptr(x.device))
+    _lib.check(rc, "quantize_act_after")
+    return q, scale
+
+
 def silu_mul_quant(gate: torch.Tensor, up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """`quantize_act(F.silu(gate) * up)` in one launch, without materialising the product.
 

@@ -324,6 +324,16 @@ int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pa
 int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word, void* stream);
 
 /*
+ * bq_quantize_act on a gathered buffer, with the wait of bq_wait_flag folded into the kernel:
+ * every CTA waits (bounded; a wait that runs out raises the status word of `ws`) until *flag has
+ * advanced by `count` beyond *seen before it loads, and *seen is advanced once all have.  One
+ * launch fewer per exchange and the dependent-launch chain stays intact.
+ */
+int bq_quantize_act_after(const void* x, int dtype, int64_t n, void* q_out, float* scale_out,
+                          const void* flag, void* seen, unsigned int count,
+                          void* ws, size_t ws_bytes, void* stream);
+
+/*
  * Several projections of ONE quantized activation in a single launch: segment
  * i computes Y_i[M,N_i] = (Xq . Wq_i^T) * sx * sw_i with its own weight scale,
  * so results are bit-identical to n_seg separate bq_gemm_w8a8 calls.  The
