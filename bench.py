@@ -16,7 +16,8 @@ collective on the data path (`"scaling": "weak"`); rank 0 also times the column-
 (N-split weights + NCCL all-gather) and reports it under `column_parallel`.
 
 `--impl reference` times the reference's CPU spelling of the same path (oracle/cpu_spelling.py)
-on the host cores, on a bounded sample: one layer of each kind, scaled by the layer counts.
+on all host cores; every step is the same bounded sample: one layer of each kind in full, scaled
+by the layer counts.  It also times torch's own CPU `_scaled_mm` on a slice and extrapolates.
 """
 from __future__ import annotations
 
@@ -169,74 +170,117 @@ def capture(fn, warm: int = 3):
 
 
 # ------------------------------------------------------------------------------------------
-def cpu_baseline(rows: int, reps: int = 1):
-    """The reference's CPU spelling on a bounded sample: one GDN, one attention and one MLP layer
-    of projections, timed in full and scaled by the stack's 24 / 8 / 32 layer counts."""
+def workload_config(rows: int, layers: int, world: int) -> dict:
+    """The `config` both arms print: what one step is."""
     from braid_b200.projection_set import StackShapes
-    from oracle import cpu_spelling as C
     s = StackShapes()
-    g = torch.Generator().manual_seed(0)
+    n_att = sum(1 for i in range(layers) if s.is_attention(i))
+    return {"workload": "decode_step_projection_set", "rows": rows, "layers": layers,
+            "hidden": s.hidden, "intermediate": s.intermediate, "gdn_layers": layers - n_att,
+            "attn_layers": n_att, "fp8_weight_bytes": s.fp8_weight_bytes() * layers // s.n_layers,
+            "parallelism": f"dp{world}",
+            "l2": "inputs larger than L2 (6.9 GB of weights streamed per step)",
+            "timing": "b200 arm: CUDA-graph replay, CUDA events, max over ranks; reference arm: "
+                      "host wall clock around the sampled step",
+            "ab_gates": "bf16 F.linear, as the reference keeps them"}
 
-    def weight(n, k):
-        w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
-        return C.quantize(w)
 
-    x = torch.randn(rows, s.hidden, generator=g).to(torch.bfloat16)
-    core = torch.randn(rows, s.gdn_inner, generator=g).to(torch.bfloat16)
-    H, I = s.hidden, s.intermediate
-    gdn = [weight(s.gdn_qkv, H), weight(s.gdn_z, H), weight(H, s.gdn_inner)]
-    att = [weight(s.attn_q, H), weight(s.attn_kv, H), weight(s.attn_kv, H), weight(H, H)]
-    mlp = [weight(I, H), weight(I, H), weight(H, I)]
+class CpuSample:
+    """The reference's CPU spelling on a bounded sample of one step: one GDN, one attention and
+    one MLP layer of projections, each timed in full and scaled by the stack's layer counts."""
 
-    def run_gdn():
-        C.project(x, gdn[0], gdn[1])
-        C.linear(core, *gdn[2])
+    def __init__(self, rows: int, layers: int = 32):
+        from braid_b200.projection_set import StackShapes
+        from oracle import cpu_spelling as C
+        torch.set_num_threads(os.cpu_count() or 1)    # torchrun sets OMP_NUM_THREADS=1
+        self.C, self.rows, s = C, rows, StackShapes()
+        self.s = s
+        g = torch.Generator().manual_seed(0)
 
-    def run_att():
-        qg, _, _ = C.project(x, att[0], att[1], att[2])
+        def weight(n, k):
+            return C.quantize((torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16))
+
+        H, I = s.hidden, s.intermediate
+        self.x = torch.randn(rows, H, generator=g).to(torch.bfloat16)
+        self.core = torch.randn(rows, s.gdn_inner, generator=g).to(torch.bfloat16)
+        self.gdn = [weight(s.gdn_qkv, H), weight(s.gdn_z, H), weight(H, s.gdn_inner)]
+        self.att = [weight(s.attn_q, H), weight(s.attn_kv, H), weight(s.attn_kv, H), weight(H, H)]
+        self.mlp = [weight(I, H), weight(I, H), weight(H, I)]
+        self.n_att = sum(1 for i in range(layers) if s.is_attention(i))
+        self.n_gdn, self.n_mlp = layers - self.n_att, layers
+
+    def step(self) -> tuple[float, float]:
+        """One sampled step: (seconds the sample took, seconds the whole step would take)."""
+        C, s, rows = self.C, self.s, self.rows
+        t0 = time.perf_counter()
+        C.project(self.x, self.gdn[0], self.gdn[1])
+        C.linear(self.core, *self.gdn[2])
+        t1 = time.perf_counter()
+        qg, _, _ = C.project(self.x, self.att[0], self.att[1], self.att[2])
         gate = qg.view(rows, s.attn_heads, 2 * s.attn_head_dim)[..., s.attn_head_dim:]
-        C.linear(core * torch.sigmoid(gate.reshape(rows, H)), *att[3])
+        C.linear(self.core * torch.sigmoid(gate.reshape(rows, s.hidden)), *self.att[3])
+        t2 = time.perf_counter()
+        C.mlp(self.x, self.mlp[0], self.mlp[1], self.mlp[2])
+        t3 = time.perf_counter()
+        return t3 - t0, self.n_gdn * (t1 - t0) + self.n_att * (t2 - t1) + self.n_mlp * (t3 - t2)
 
-    def run_mlp():
-        C.mlp(x, mlp[0], mlp[1], mlp[2])
+    def scaled_mm_extrapolated(self, slice_rows: int = 64) -> dict:
+        """torch's own CPU `_scaled_mm` (the literal call of braid/model/quant.py:240-241; a scalar
+        loop on CPU) on the first `slice_rows` rows of the gate weight, extrapolated by bytes to
+        the FP8 weights of one step."""
+        C = self.C
+        xq, sx = C.quantize(self.x)
+        wq, sw = self.mlp[0]
+        sec = C.scaled_mm_slice_seconds(xq, sx, wq, sw, rows=slice_rows)
+        total = self.s.fp8_weight_bytes() * self.n_mlp // self.s.n_layers
+        step_s = sec / (slice_rows * wq.shape[1]) * total
+        return {"slice_rows": slice_rows, "slice_seconds": sec, "step_seconds_extrapolated": step_s,
+                "value": self.rows / step_s, "unit": "tok/s",
+                "what": "torch._scaled_mm on CPU, one N-slice timed, scaled by weight bytes"}
 
-    def best(fn):
-        fn()
-        ts = []
-        for _ in range(max(1, reps)):
-            t0 = time.perf_counter()
-            fn()
-            ts.append(time.perf_counter() - t0)
-        return min(ts)
+    def describe(self, sample_s: float, step_s: float) -> str:
+        return (f"1 GDN + 1 attention + 1 MLP layer of projections at {self.rows} rows timed in full "
+                f"with the reference's CPU spelling (torch quantizer + fp32 dequant-matmul on "
+                f"{torch.get_num_threads()} threads) = {sample_s * 1e3:.0f} ms per sampled step, scaled "
+                f"by {self.n_gdn}/{self.n_att}/{self.n_mlp} layers to {step_s * 1e3:.0f} ms per step")
 
-    n_att = s.n_layers // s.attn_every
-    n_gdn = s.n_layers - n_att
-    t_step = n_gdn * best(run_gdn) + n_att * best(run_att) + s.n_layers * best(run_mlp)
-    return {"value": rows / t_step, "unit": "tok/s", "cores": torch.get_num_threads(),
-            "kind": "port",
-            "sample": (f"1 GDN + 1 attention + 1 MLP layer of projections at {rows} rows timed in "
-                       f"full with the reference's CPU spelling (torch quantizer + fp32 dequant-"
-                       f"matmul on {torch.get_num_threads()} threads), scaled by {n_gdn}/{n_att}/"
-                       f"{s.n_layers} layers; est. {t_step * 1e3:.0f} ms per step"),
-            "host_cpus": os.cpu_count()}
+
+def cpu_baseline(rows: int, layers: int = 32, steps: int = 3, warmup: int = 1, sample=None,
+                 with_scaled_mm: bool = False):
+    sample = sample or CpuSample(rows, layers)
+    for _ in range(warmup):
+        sample.step()
+    got = [sample.step() for _ in range(max(1, steps))]
+    sample_s = statistics.mean(t[0] for t in got)
+    step_s = statistics.mean(t[1] for t in got)
+    out = {"value": rows / step_s, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+           "sample": sample.describe(sample_s, step_s), "host_cpus": os.cpu_count(),
+           "timed_steps": len(got), "sample_seconds_per_step": sample_s,
+           "step_seconds_extrapolated": step_s}
+    if with_scaled_mm:
+        try:
+            out["reference_scaled_mm"] = sample.scaled_mm_extrapolated()
+        except Exception as e:  # noqa: BLE001
+            out["reference_scaled_mm"] = {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
+    return out
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    for _ in range(args.warmup and 1):
-        cpu_baseline(args.rows, reps=1)
-    vals = [cpu_baseline(args.rows, reps=1) for _ in range(min(args.steps, 3))]
-    best = max(vals, key=lambda d: d["value"])
+    best = cpu_baseline(args.rows, args.layers, steps=args.steps, warmup=args.warmup,
+                        with_scaled_mm=True)
     line = {
         "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "tok/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": args.rows / best["value"] * 1e3, "higher_is_better": True,
+        "ms_per_step": best["step_seconds_extrapolated"] * 1e3,
+        "sample_ms_per_step": best["sample_seconds_per_step"] * 1e3,
+        "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f8e4m3xf8e4m3->f32",
         "data": "synthetic",
-        "config": {"workload": "decode_step_projection_set", "rows": args.rows, "layers": 32,
-                   "hidden": 4096, "intermediate": 12288, "device": "host CPU"},
+        "config": workload_config(args.rows, args.layers, world),
         "cpu_baseline": best,
         "e2e": {"value": best["value"], "unit": "tok/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -268,6 +312,75 @@ def run_engine_compare(args):
                                      use_kernels=use_kernels)
     res = {"metric": "engine_decode_tokens_per_s", "unit": "tok/s", "n_gpus": 1, **res}
     print(json.dumps(res), flush=True)
+
+
+def reference_fused_quantizer():
+    """The reference's shipped fused quantizer (braid/kernels/csrc/quant_act.cu:140-176), from the
+    extension baseline/ref_kernels.py builds for sm_100a out of the reference checkout.  Returns
+    the callable `x -> (q, scale)` or a one-line reason why it is not there."""
+    try:
+        sys.path.insert(0, str(ROOT / "baseline"))
+        import ref_kernels
+        if not ref_kernels.prebuilt_path().exists():
+            return "no prebuilt reference extension under baseline/_ref/_prebuilt"
+        import importlib.util
+        name = ref_kernels.NAME
+        if name in sys.modules:
+            mod = sys.modules[name]
+        else:
+            spec = importlib.util.spec_from_file_location(name, ref_kernels.prebuilt_path())
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            sys.modules[name] = mod
+        fn = mod.quantize_act
+
+        def quantizer(x):
+            q, scale = fn(x)
+            return q, scale
+        return quantizer
+    except Exception as e:  # noqa: BLE001
+        return f"{type(e).__name__}: {str(e)[:140]}"
+
+
+def projection_tables(dev, peaks):
+    """BASELINE's per-projection half of the metric, in the same run: decode-regime GB/s as a
+    fraction of the HBM copy peak over the config-2 / config-3 launch shapes at M = 1, 16, 128,
+    and prefill-regime TFLOP/s at config 4's packed row count, each beside the library GEMM
+    (`torch._scaled_mm`) on the same shapes (method: braid_b200/sweep.py)."""
+    from braid_b200 import sweep
+    rows = []
+    for name in ("mlp.gate_up", "mlp.down", "gdn.in_proj_qkv_z", "gdn.out_proj", "attn.qkv",
+                 "attn.k_proj"):
+        ns, k = sweep.PROJECTIONS[name]
+        for m in (1, 16, 128):
+            r = sweep.gemm_row(name, ns, k, m, dev, peaks, reps=9)
+            rows.append({"proj": name, "M": m, "us": r["us"], "gbs": r["gbs"], "frac_hbm": r["frac_hbm"],
+                         "vs_scaled_mm": r.get("speedup_vs_lib")})
+    fr = sorted(r["frac_hbm"] for r in rows)
+    ratio = sorted(r["vs_scaled_mm"] for r in rows if r["vs_scaled_mm"])
+    per_projection = {
+        "rows": rows, "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+        "frac_hbm": {"min": fr[0], "median": statistics.median(fr), "max": fr[-1]},
+        "frac_hbm_M128": {r["proj"]: r["frac_hbm"] for r in rows if r["M"] == 128},
+        "vs_scaled_mm": {"min": ratio[0], "median": statistics.median(ratio), "max": ratio[-1]} if ratio else None,
+        "note": "attn.o_proj has out_proj's shape; frac = algorithmic bytes (N*K + M*K + 2*M*N) / time / peak"}
+    g = torch.Generator().manual_seed(4)
+    m4 = int(torch.randint(64, 1025, (16,), generator=g).sum().item())
+    peak8 = sweep.fp8_library_peak(dev, seconds=1.0)
+    prows = []
+    for name in ("mlp.gate_up", "mlp.down", "gdn.in_proj_qkv_z", "gdn.out_proj"):
+        ns, k = sweep.PROJECTIONS[name]
+        r = sweep.gemm_row(name, ns, k, m4, dev, peaks, inner=4, reps=7)
+        prows.append({"proj": name, "M": m4, "us": r["us"], "tflops": r["tflops"],
+                      "frac_fp8_measured_burst": r["tflops"] / peak8["fp8_tflops_burst"],
+                      "frac_fp8_nominal_4500": r["tflops"] / 4500.0,
+                      "vs_scaled_mm": r.get("speedup_vs_lib"), "kernel": r["launch"]["kernel"]})
+    prefill = {"workload": "config 4: 16 packed sequences, lengths ~U[64,1024] (seed 4)", "M": m4,
+               "rows": prows, "fp8_peak_measured": peak8,
+               "fp8_peak_how": "torch._scaled_mm 8192^3, best of 10 (burst) / back to back 1 s (sustained)",
+               "min_vs_scaled_mm": min((r["vs_scaled_mm"] or 0.0) for r in prows),
+               "min_frac_fp8_measured_burst": min(r["frac_fp8_measured_burst"] for r in prows)}
+    return per_projection, prefill
 
 
 def column_parallel_block(dist, rows_list, steps, warmup):
@@ -352,6 +465,8 @@ def main():
     ap.add_argument("--only", default=None, help="with --sweep: one projection name, at --rows")
     ap.add_argument("--no-library-arm", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-tables", action="store_true",
+                    help="skip the per-projection decode table and the prefill (config 4) record")
     ap.add_argument("--engine", action="store_true",
                     help="the reference's whole graphed decode step (installed under baseline/_ref) "
                          "stock vs on these kernels; one GPU, its own JSON line")
@@ -447,15 +562,12 @@ def main():
     peaks = measured_peaks()
     gemm_bytes = ps.gemm_algorithmic_bytes()
     achieved = gemm_bytes / (ms_gemm / args.steps * 1e-3) / 1e9
-    # dram read+write per launch measured by ncu on the three launch shapes of a 2-layer case
-    # (profiles/gemm_stream_kernel_decode_M128.md): 1.01-1.04 x the algorithmic bytes, scaled here
-    # to the average launch of the full step (traffic grows in proportion to the weights)
-    traffic_ratio = 1.02
+    traffic = ps.gemm_measured_traffic_bytes()
     roofline = {"bound": "hbm", "kernel": "gemm_stream_kernel", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"],
-                "traffic": traffic_ratio * gemm_bytes / max(1, gemm_launches),
-                "traffic_source": "ncu dram__bytes_read+write on a 2-layer capture, scaled by weight bytes",
+                "traffic": traffic["bytes"] / max(1, gemm_launches),
+                "traffic_source": traffic["source"],
                 "launches_per_step": gemm_launches,
                 "algorithmic_bytes_per_launch": gemm_bytes / max(1, gemm_launches),
                 "avg_launch_us": ms_gemm / args.steps / max(1, gemm_launches) * 1e3}
@@ -469,19 +581,38 @@ def main():
     ms_fp8, _ = timed_replays(g_fp8.replay, args.steps, args.warmup, dist=None)
     del g_fp8
 
-    # ---- the same step built from the library GEMM + torch-spelling quantizer ---------------
-    library = None
+    # ---- the same step built from the library GEMM, with each of the reference's quantizers ----
+    library, library_fused = None, None
     if not args.no_library_arm and rank == 0:
+        def library_arm(quantizer, what):
+            try:
+                g_lib, _ = capture(lambda: ps.step_library(static_x, quantizer))
+                ms_lib, _ = timed_replays(g_lib.replay, args.steps, args.warmup, dist=None)
+                del g_lib
+                return {"value": args.rows / (ms_lib / args.steps * 1e-3), "unit": "tok/s",
+                        "ms_per_step": ms_lib / args.steps, "what": what}
+            except Exception as e:  # noqa: BLE001 - reported in the JSON line
+                torch.cuda.synchronize()
+                return {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+
+        library = library_arm(None, "same step from torch._scaled_mm + the reference's torch-spelling "
+                                    "quantizer (nine kernels), one CUDA graph, same weights, one GPU")
+        ref_quant = reference_fused_quantizer()
+        if callable(ref_quant):
+            library_fused = library_arm(ref_quant, "same step from torch._scaled_mm + the reference's own "
+                                                   "fused two-launch quantizer (its CUDA source built for "
+                                                   "sm_100a), one CUDA graph, same weights, one GPU")
+        else:
+            library_fused = {"unavailable": ref_quant}
+
+    # ---- the other half of the metric: per-projection decode GB/s and prefill TFLOP/s ------------
+    per_projection, prefill = None, None
+    if rank == 0 and world == 1 and not args.no_tables:
         try:
-            g_lib, _ = capture(lambda: ps.step_library(static_x))
-            ms_lib, _ = timed_replays(g_lib.replay, args.steps, args.warmup, dist=None)
-            library = {"value": args.rows / (ms_lib / args.steps * 1e-3), "unit": "tok/s",
-                       "ms_per_step": ms_lib / args.steps,
-                       "what": "same step from torch._scaled_mm + torch-spelling quantizer, "
-                               "one CUDA graph, same weights, one GPU"}
-            del g_lib
-        except Exception as e:  # noqa: BLE001 - reported in the JSON line
-            library = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+            per_projection, prefill = projection_tables(dev, peaks)
+        except Exception as e:  # noqa: BLE001
+            torch.cuda.synchronize()
+            per_projection = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
 
     colpar = None
     if dist is not None:
@@ -493,7 +624,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
-            cpu = cpu_baseline(args.rows)
+            cpu = cpu_baseline(args.rows, args.layers, steps=3, warmup=1)
         except Exception as e:  # noqa: BLE001
             cpu = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
 
@@ -503,13 +634,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f8e4m3xf8e4m3->f32", "data": "synthetic",
-            "config": {"workload": "decode_step_projection_set", "rows": args.rows,
-                       "layers": args.layers, "hidden": shapes.hidden,
-                       "intermediate": shapes.intermediate, "gdn_layers": 24, "attn_layers": 8,
-                       "fp8_weight_bytes": ps.fp8_weight_bytes(), "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (6.9 GB of weights streamed per step)",
-                       "timing": "CUDA-graph replay, CUDA events, max over ranks",
-                       "ab_gates": "bf16 F.linear, as the reference keeps them"},
+            "config": workload_config(args.rows, args.layers, world),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
@@ -527,6 +652,9 @@ def main():
                                          "reference keeps in bf16: every launch is this library's"},
             "cpu_baseline": cpu,
             "library_baseline": library,
+            "library_baseline_fused_quantizer": library_fused,
+            "per_projection": per_projection,
+            "prefill": prefill,
             "column_parallel": colpar,
             "device_status": status,
             "fused_state": Q.fused_state(),

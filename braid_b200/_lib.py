@@ -7,9 +7,12 @@ Loading fails loudly; there is no other implementation to fall back to.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libbraid_b200.so"
+# BRAID_B200_LIB selects another build of the same library (the development build with phase
+# stamps, `python -m braid_b200.build --phases`); unset, the in-tree product library is loaded.
+LIB_PATH = Path(os.environ.get("BRAID_B200_LIB") or Path(__file__).resolve().parent / "libbraid_b200.so")
 
 BQ_OK = 0
 BQ_ERR_BAD_ARG = 1
@@ -32,6 +35,8 @@ SIGNATURES = {
     "bq_quantize_act": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_quantize_act_static": (_int, [_vp, _int, _i64, _vp, _vp, _vp]),
     "bq_silu_mul_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "bq_silu_mul_scale": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),
+    "bq_silu_mul_cast": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "bq_sigmoid_gate_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64,
                                      _vp, _vp, _vp, _sz, _vp]),
     "bq_rmsnorm_quant": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp,
@@ -39,7 +44,6 @@ SIGNATURES = {
     "bq_gated_rmsnorm_quant": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,
                                       _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
-    "bq_gemm_scratch_bytes": (_sz, [_i64, _int]),
     "bq_gemm_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "bq_gemm_w8a8_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _int, _i64, _i64, _i64, _i64,
                                      _vp, _sz, _vp]),
@@ -60,11 +64,6 @@ SIGNATURES = {
                                     ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                     ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
                                     _vp, _sz, _vp]),
-    "bq_linear_w8a8_grouped": (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _i64,
-                                      _vp, _vp, _int,
-                                      ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
-                                      ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
-                                      _vp, _sz, _vp]),
     "bq_read_device_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "bq_set_option": (_int, [ctypes.c_char_p, _i64]),
     "bq_last_gemm_launch": (_int, [ctypes.POINTER(_i64)]),

@@ -9,6 +9,11 @@ square root, no flush-to-zero.
 
 Run `python -m braid_b200.build` to (re)build; `python -m braid_b200.build -v`
 adds `-Xptxas -v` (registers, spills, shared memory per kernel).
+`python -m braid_b200.build --phases` builds a second, development-only library
+(`libbraid_b200_phases.so`, compiled with `-DBQ_PHASES`) whose decode-regime kernels stamp
+the time of each of their phases; `BRAID_B200_LIB=<path>` makes the package load it
+(`python bench.py --sweep --only phases` prints the table).  The shipped library contains
+none of that code.
 """
 from __future__ import annotations
 
@@ -41,10 +46,15 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+PHASES_LIB = PKG / "libbraid_b200_phases.so"
+
+
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (),
+          out: Path | None = None) -> Path:
     """Compile the CUDA sources for sm_100a into one shared library."""
-    if not force and not is_stale():
+    if out is None and not defines and not force and not is_stale():
         return LIB
+    LIB = out if out is not None else globals()["LIB"]
     cmd = [
         nvcc_path(), "-std=c++17", "-O3", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
@@ -54,6 +64,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         "-I", str(PKG.parent / "include"),
         "-o", str(LIB),
     ]
+    cmd += [f"-D{d}" for d in defines]
     if verbose or os.environ.get("BRAID_B200_VERBOSE") == "1":
         cmd += ["-Xptxas", "-v"]
     cmd += [str(CSRC / s) for s in SOURCES]
@@ -66,5 +77,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    out = build(force=True, verbose="-v" in sys.argv[1:])
-    print(out)
+    if "--phases" in sys.argv[1:]:
+        print(build(force=True, verbose="-v" in sys.argv[1:], defines=("BQ_PHASES",), out=PHASES_LIB))
+    else:
+        print(build(force=True, verbose="-v" in sys.argv[1:]))

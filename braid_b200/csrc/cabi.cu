@@ -123,3 +123,48 @@ extern "C" int bq_peer_close(void* ptr) {
   if (cudaIpcCloseMemHandle(ptr) != cudaSuccess) { (void)cudaGetLastError(); return BQ_ERR_LAUNCH; }
   return BQ_OK;
 }
+
+#ifdef BQ_PHASES
+// ---------------------------------------------------------------------------------------------
+// Development build only: the ring the decode-regime kernels stamp their phases into
+// ---------------------------------------------------------------------------------------------
+static __device__ unsigned long long g_phase_ring[(size_t)bq::kPhaseLaunches * bq::kPhaseCtas * bq::kPhaseWords];
+static int g_phase_seq = 0;
+static int g_phase_on = 0;
+
+unsigned long long* bq::phase_ring_for_launch(int* seq_out) {
+  static unsigned long long* ring = nullptr;
+  if (!g_phase_on) return nullptr;
+  if (ring == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_phase_ring) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    ring = static_cast<unsigned long long*>(ptr);
+  }
+  *seq_out = g_phase_seq++;
+  return ring;
+}
+
+// on = 1 starts numbering launches from 0 again and clears the ring
+extern "C" int bq_debug_phases(int on) {
+  g_phase_on = on;
+  g_phase_seq = 0;
+  if (on) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_phase_ring) != cudaSuccess) return BQ_ERR_LAUNCH;
+    if (cudaMemset(ptr, 0, sizeof(unsigned long long) * bq::kPhaseLaunches * bq::kPhaseCtas * bq::kPhaseWords) != cudaSuccess)
+      return BQ_ERR_LAUNCH;
+  }
+  return BQ_OK;
+}
+
+// copies the whole ring to `out` (kPhaseLaunches * kPhaseCtas * kPhaseWords u64) and returns the
+// number of launches numbered so far through *launches_out
+extern "C" int bq_debug_read_phases(unsigned long long* out, int* launches_out) {
+  if (out == nullptr || launches_out == nullptr) return BQ_ERR_BAD_ARG;
+  if (cudaDeviceSynchronize() != cudaSuccess) return BQ_ERR_LAUNCH;
+  if (cudaMemcpyFromSymbol(out, g_phase_ring, sizeof(unsigned long long) * bq::kPhaseLaunches * bq::kPhaseCtas * bq::kPhaseWords) != cudaSuccess)
+    return BQ_ERR_LAUNCH;
+  *launches_out = g_phase_seq;
+  return BQ_OK;
+}
+#endif

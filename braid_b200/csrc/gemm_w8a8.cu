@@ -63,18 +63,6 @@ struct Segment {
   int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
   int split_forced;    // stream kernel: non-zero = use this split instead of the shape rule
   int cluster_begin;   // stream kernel: index of the segment's first cluster
-  long long total_kb;  // persistent stream kernel: row tiles x K blocks of this weight
-  int ctas;            // persistent stream kernel: CTAs that share this weight
-  int cta_begin;       // persistent stream kernel: first of those CTAs (they wrap around the grid)
-};
-
-// The activation quantizer fused into the stream kernel (mode 0 = not fused: the
-// kernel then reads ready-made codes and a ready-made scale).
-struct FuseParams {
-  int mode;               // 0 off, 1 plain, 2 SiLU(a)*b, 3 a*sigmoid(b)
-  int dtype;              // BQ_DTYPE_* of the activation operands
-  bq::qd::QParams q;      // operands, addressing, codes out (q.q) and scale out (q.scale)
-  unsigned int* words;    // [0] amax bits [1] amax arrivals [2] codes arrivals [3] status [4] departures
 };
 
 // SiLU(gate)*up and the quantization of the product, done in the epilogue of ONE GEMM over a
@@ -118,11 +106,10 @@ struct GemmParams {
   int m_tiles;         // tile kernel: ceil(M / 128)
   int total_tiles;     // tile kernel
   unsigned int* status;
-  FuseParams fuse;
+  unsigned long long* phase_ring;   // development builds (BQ_PHASES) only, else nullptr
+  int phase_seq;
   PairSilu pair;
   PushParams push;
-  unsigned int* flags;   // persistent stream kernel: one word per (weight, CTA), zero between launches
-  float* partials;       // persistent stream kernel: [weight][CTA][mma_n][128] fp32
 };
 
 struct alignas(64) WeightMaps {
@@ -351,99 +338,6 @@ __device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const floa
   }
 }
 
-constexpr int kQuantThreads = 192;   // warps 2..7 of the stream kernel
-
-__device__ __forceinline__ void quant_bar() {   // the six quantizer warps only
-  asm volatile("bar.sync 1, 192;" ::: "memory");
-}
-
-// Fused activation quantizer, run by warps 2..7 of EVERY CTA of the grid while the
-// producer warp is already streaming weights.  Two passes over the activation (the
-// second is served by L2): |x| max -> grid-wide exchange -> scale -> cast -> codes
-// to global memory -> arrival on the "codes are complete" counter the producers
-// poll before they issue the first activation-tile load.  Returns the global amax.
-template <typename T, int MODE>
-__device__ __forceinline__ float fused_quantize_t(const FuseParams& f, int qtid, float* s_red,
-                                                  unsigned int* status) {
-  using namespace bq::qd;
-  const unsigned int nq = gridDim.x * kQuantThreads;
-  const unsigned int q0 = blockIdx.x * kQuantThreads + qtid;
-  float m = 0.0f;
-  for (unsigned int g = q0; g < f.q.n_groups; g += nq) m = absmax8(produce<T, MODE>(f.q, g), m);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
-  if ((qtid & 31) == 0) s_red[qtid >> 5] = m;
-  quant_bar();
-  if (qtid == 0) {
-    float w = s_red[0];
-#pragma unroll
-    for (int i = 1; i < kQuantThreads / 32; ++i) w = nan_max(w, s_red[i]);
-    if (gridDim.x > 1) {
-      atomicMax(&f.words[0], __float_as_uint(w));
-      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&f.words[1]) : "memory");
-      unsigned int amax_bits = 0, arrived = 0;
-      const long long t0 = clock64();
-      for (;;) {
-        asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];"
-                     : "=r"(amax_bits), "=r"(arrived)
-                     : "l"(f.words)
-                     : "memory");
-        if (arrived >= gridDim.x) break;
-        if (clock64() - t0 > kSpinLimitCycles) {
-          atomicExch(status, (unsigned int)kErrDeviceWait);
-          break;
-        }
-      }
-      w = __uint_as_float(amax_bits);
-    }
-    s_red[6] = w;
-  }
-  quant_bar();
-  const float amax = s_red[6];
-  const float sc = scale_from_amax(amax);
-  for (unsigned int g = q0; g < f.q.n_groups; g += nq)
-    emit8(produce<T, MODE>(f.q, g), sc, f.q.q + static_cast<size_t>(g) * kGroup);
-  // codes were written through the generic proxy and will be read by TMA (async
-  // proxy) of other CTAs: device-scope fence, proxy fence, then the arrival
-  __threadfence();
-  asm volatile("fence.proxy.async;" ::: "memory");
-  quant_bar();
-  if (qtid == 0) {
-    if (blockIdx.x == 0) f.q.scale[0] = sc;
-    if (gridDim.x > 1)   // a single CTA hands over through shared memory and leaves the words alone
-      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&f.words[2]) : "memory");
-  }
-  return amax;
-}
-
-template <typename T>
-__device__ __forceinline__ float fused_quantize_m(const FuseParams& f, int qtid, float* s_red,
-                                                  unsigned int* status) {
-  switch (f.mode) {
-    case 1: return fused_quantize_t<T, bq::qd::kPlain>(f, qtid, s_red, status);
-    case 2: return fused_quantize_t<T, bq::qd::kSiluMul>(f, qtid, s_red, status);
-    default: return fused_quantize_t<T, bq::qd::kSigmoidGate>(f, qtid, s_red, status);
-  }
-}
-
-__device__ __noinline__ float fused_quantize(const FuseParams& f, int qtid, float* s_red,
-                                             unsigned int* status) {
-  switch (f.dtype) {
-    case BQ_DTYPE_F32: return fused_quantize_m<float>(f, qtid, s_red, status);
-    case BQ_DTYPE_F16: return fused_quantize_m<__half>(f, qtid, s_red, status);
-    default: return fused_quantize_m<__nv_bfloat16>(f, qtid, s_red, status);
-  }
-}
-
-// A CTA is done with the fused quantizer's counters: the last one out zeroes them.
-__device__ __forceinline__ void fused_depart(unsigned int* words) {
-  const unsigned int old = atomicAdd(&words[4], 1u);   // words[3] is the sticky status word
-  if (old == gridDim.x - 1) {
-    words[0] = 0u; words[1] = 0u; words[2] = 0u; words[4] = 0u;
-    __threadfence();
-  }
-}
-
 // ---------------------------------------------------------------------------
 // Weight-streaming kernel (swap-AB, cluster split-K)
 // ---------------------------------------------------------------------------
@@ -451,7 +345,10 @@ __device__ __forceinline__ void fused_depart(unsigned int* words) {
 //   [stages x 16 KiB weight tiles][stages x (mma_n*128) activation tiles] ... [barrier block]
 // The tile area is reused after the main loop as the fp32 staging buffer
 // part[m][128] that the cluster reduction reads.
-__global__ void __launch_bounds__(256, 2)
+#ifndef BQ_STREAM_MIN_CTAS
+#define BQ_STREAM_MIN_CTAS 2
+#endif
+__global__ void __launch_bounds__(256, BQ_STREAM_MIN_CTAS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p,
                    const int smem_tile_bytes) {
@@ -470,8 +367,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
   float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // 8 floats
-  const bool fused = p.fuse.mode != 0;
 
+  if (threadIdx.x == 0) { BQ_STAMP(p, 0); BQ_STAMP_META(p, 0); }
   pdl_launch_dependents();   // the next kernel may start its own set-up right away
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A cluster of p.cluster CTAs works on p.cluster / split row tiles of one weight
@@ -508,7 +405,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
-    s_quant[7] = 0.0f;
     fence_mbar_init();
   }
   if (warp == 1 && active) {
@@ -519,15 +415,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) BQ_STAMP(p, 1);
 
   if (!active) {
-    // nothing to multiply; it still takes its share of the fused quantizer and
-    // matches the two cluster barriers of the working CTAs
-    if (fused && warp >= 2) {
-      pdl_wait_prior_grids();
-      fused_quantize(p.fuse, threadIdx.x - 64, s_quant, p.status);
-      if (threadIdx.x == 64 && gridDim.x > 1) fused_depart(p.fuse.words);
-    }
+    // nothing to multiply: it only matches the two cluster barriers of the working CTAs
     if (p.cluster > 1) { cluster_sync_all(); cluster_sync_all(); }
     return;
   }
@@ -546,29 +437,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         tma_load_2d(a_base + i * kATileBytes, &tm_w.w[sg], full_bar(i), (kb_begin + i) * kBK, row0,
                     pol_w);
       }
-      if (fused) {
-        // the activation codes are being produced by the quantizer warps of the
-        // whole grid: wait (bounded) until every CTA has reported its share
-        if (gridDim.x > 1) {
-          const long long t0 = clock64();
-          for (;;) {
-            unsigned int done;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(&p.fuse.words[2]) : "memory");
-            if (done >= gridDim.x) break;
-            if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
-          }
-          fused_depart(p.fuse.words);
-        } else {
-          // single CTA: its own quantizer warps signal through shared memory
-          const long long t0 = clock64();
-          while (*reinterpret_cast<volatile float*>(s_quant + 7) == 0.0f) {
-            if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
-          }
-        }
-        asm volatile("fence.proxy.async;" ::: "memory");
-      } else {
-        pdl_wait_prior_grids();
-      }
+      pdl_wait_prior_grids();
+      BQ_STAMP(p, 2);
       for (int i = 0; i < prefill; ++i)
         tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
       for (int i = prefill; i < kb_count; ++i) {
@@ -594,6 +464,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
           break;
         }
         tc_fence_after();
+        if (i == 0) BQ_STAMP(p, 3);
         const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
         const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
 #pragma unroll
@@ -610,23 +481,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   // ---- epilogue: TMEM -> fp32 staging in shared memory ----------------------
   pdl_wait_prior_grids();   // scales are read and outputs written only after this
-  if (fused && warp >= 2) {
-    fused_quantize(p.fuse, threadIdx.x - 64, s_quant, p.status);
-    if (threadIdx.x == 64 && gridDim.x == 1) {
-      __threadfence_block();
-      *reinterpret_cast<volatile float*>(s_quant + 7) = 1.0f;   // single-CTA hand-off to the producer
-    }
-  }
   // the epilogue warps get here at once and have the scale ready long before
   // the accumulator is
   const float sw = __ldg(seg.sw);
-  const float sx_ready = fused ? 0.0f : __ldg(p.sx);
+  const float sx_ready = __ldg(p.sx);
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
+  if (threadIdx.x == 0) BQ_STAMP(p, 4);
   if (!ok) *abort_flag = 1;
   __syncthreads();
   ok = (*abort_flag == 0);
-  const float scale = (fused ? bq::qd::scale_from_amax(s_quant[6]) : sx_ready) * sw;
+  const float scale = sx_ready * sw;
   float* const part = reinterpret_cast<float*>(base_ptr);   // [mma_n][128]
   if (ok) {
     // 8 warps: warp w reads TMEM lanes 32*(w%4).. (the only ones it may touch)
@@ -646,6 +511,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   }
   tc_fence_before();
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
+  if (threadIdx.x == 0) BQ_STAMP(p, 5);
 
   // ---- reduce the K slices in rank order and write this CTA's share of rows --
   float pair_max = 0.0f;
@@ -689,6 +555,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       }
     }
   }
+  if (threadIdx.x == 0) BQ_STAMP(p, 6);
   // nobody leaves while a peer may still read its staging buffer
   if (p.cluster > 1) cluster_sync_all(); else __syncthreads();
   if (p.pair.on && p.push.n > 0) {
@@ -788,6 +655,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
   }
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if (threadIdx.x == 0) BQ_STAMP(p, 7);
 }
 
 // Waits (bounded) until `flag` has counted `count` more arrivals than at the end of the
@@ -808,308 +676,6 @@ __global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, u
   }
   *seen = target;
   __threadfence();
-}
-
-// ---------------------------------------------------------------------------
-// Persistent weight-streaming kernel (decode regime, every SM streams all the time)
-// ---------------------------------------------------------------------------
-// One CTA per SM.  The K blocks of each weight, taken row tile by row tile, form
-// one long sequence that is cut into equal contiguous ranges, one per CTA -- so
-// every SM streams the same number of bytes whatever the shapes are.  A range
-// that starts or ends inside a row tile leaves a partial sum: the CTA that holds
-// the beginning of the tile (lowest K) owns it and adds the partial sums of the
-// CTAs that continue the tile, in ascending-K order, from a scratch buffer (L2).
-// The cut points depend on the weight's own shape and the SM count only, never
-// on what else is in the launch, so results do not depend on grouping.
-// Warp roles: 0 = TMA producer (runs ahead across tiles and weights), 1 = MMA
-// issuer, 2..5 = epilogue (tensor memory -> partial/scratch or -> output), with
-// the accumulators rotated through tensor memory so that the epilogue of one tile
-// overlaps the stream of the next.
-constexpr int kPsThreads = 192;
-constexpr int kPsEpiThreads = 128;
-constexpr int kPsChunk = 16;                       // batch rows the epilogue transposes at a time
-
-__device__ __forceinline__ void epi_bar() {       // the four epilogue warps only
-  asm volatile("bar.sync 2, 128;" ::: "memory");
-}
-
-struct PsRange {
-  long long r, r1;      // K-block range of this CTA inside the weight's sequence
-  int j;                // index of this CTA among the CTAs of the weight
-};
-
-__device__ __forceinline__ bool ps_range(const Segment& sg, int cta, int grid, PsRange& out) {
-  int j = cta - sg.cta_begin;
-  if (j < 0) j += grid;
-  if (j >= sg.ctas) return false;
-  out.j = j;
-  out.r = (long long)j * sg.total_kb / sg.ctas;
-  out.r1 = (long long)(j + 1) * sg.total_kb / sg.ctas;
-  return out.r < out.r1;
-}
-
-// Walks the K blocks this CTA streams, weight after weight, in the order every role uses.
-struct PsCursor {
-  int w;
-  long long r, r1;
-  __device__ __forceinline__ void init() { w = -1; r = 0; r1 = 0; }
-  // Moves to the next K block; returns false when the CTA has no more work.
-  __device__ __forceinline__ bool next(const GemmParams& p, int cta, int grid, int& tile, int& kb) {
-    while (r >= r1) {
-      if (++w >= p.n_seg) return false;
-      PsRange rg;
-      if (ps_range(p.seg[w], cta, grid, rg)) { r = rg.r; r1 = rg.r1; }
-    }
-    tile = (int)(r / p.k_blocks);
-    kb = (int)(r - (long long)tile * p.k_blocks);
-    ++r;
-    return true;
-  }
-};
-
-__global__ void __launch_bounds__(kPsThreads, 1)
-gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_x,
-                    const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p,
-                    const int smem_tile_bytes) {
-  extern __shared__ uint8_t smem_dyn[];
-  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-  const int b_tile_bytes = p.mma_n * kBK;
-  const uint32_t a_base = base;
-  const uint32_t b_base = base + p.stages * kATileBytes;
-  // after the pipeline: a [16][128] fp32 transpose buffer for the epilogue, then the barriers
-  float* const xpose = reinterpret_cast<float*>(base_ptr + smem_tile_bytes);
-  const uint32_t bar_base = base + smem_tile_bytes + kPsChunk * kRowTile * 4;
-  uint8_t* const bar_ptr = base_ptr + smem_tile_bytes + kPsChunk * kRowTile * 4;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
-  auto acc_full = [&](int b) { return bar_base + 8u * (2 * p.stages + b); };
-  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * p.stages + 4 + b); };
-  volatile uint32_t* const tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * p.stages + 8));
-  volatile uint32_t* const abort_flag = tmem_slot + 1;
-
-  pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int cta = blockIdx.x, grid = gridDim.x;
-  const int kb_per_tile = p.k_blocks;
-  // accumulators rotate through tensor memory: 512 columns / columns per accumulator
-  uint32_t acc_cols = 32;
-  while (acc_cols < static_cast<uint32_t>(p.mma_n)) acc_cols <<= 1;
-  const int n_acc = (512 / acc_cols) > 4 ? 4 : (512 / acc_cols);
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tm_x);
-    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tm_w.w[i]);
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 4; ++b) {
-      mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);      // one arrival per epilogue warp
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (elect_one()) {
-      const uint64_t pol_w = policy_evict_first();
-      const uint64_t pol_x = policy_evict_last();
-      bool ok = true;
-      PsCursor cw, cx;          // weight-tile loads run ahead of activation-tile loads
-      cw.init();
-      cx.init();
-      int tile, kb, it = 0;
-      // weights do not depend on earlier kernels: fill the pipeline with them first,
-      // then wait for the kernel that produces the activation codes
-      int prefill = 0;
-      while (prefill < p.stages && cw.next(p, cta, grid, tile, kb)) {
-        mbar_expect_tx(full_bar(prefill), kATileBytes + b_tile_bytes);
-        tma_load_2d(a_base + prefill * kATileBytes, &tm_w.w[cw.w], full_bar(prefill), kb * kBK,
-                    tile * kRowTile, pol_w);
-        ++prefill;
-      }
-      pdl_wait_prior_grids();
-      for (int i = 0; i < prefill; ++i) {
-        cx.next(p, cta, grid, tile, kb);
-        tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), kb * kBK, 0, pol_x);
-      }
-      it = prefill;
-      while (ok && cw.next(p, cta, grid, tile, kb)) {
-        const int s = it % p.stages, use = it / p.stages;
-        if (!mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
-        mbar_expect_tx(full_bar(s), kATileBytes + b_tile_bytes);
-        tma_load_2d(a_base + s * kATileBytes, &tm_w.w[cw.w], full_bar(s), kb * kBK, tile * kRowTile,
-                    pol_w);
-        tma_load_2d(b_base + s * b_tile_bytes, &tm_x, full_bar(s), kb * kBK, 0, pol_x);
-        ++it;
-      }
-      if (!ok) *abort_flag = 1;
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (elect_one()) {
-      const uint32_t idesc = idesc_e4m3(kRowTile, p.mma_n);
-      int it = 0, seg_iter = 0;
-      bool ok = true;
-      for (int w = 0; w < p.n_seg && ok; ++w) {
-        PsRange rg;
-        if (!ps_range(p.seg[w], cta, grid, rg)) continue;
-        long long r = rg.r;
-        while (r < rg.r1 && ok) {
-          const int tile = (int)(r / kb_per_tile);
-          const long long tile_end = (long long)(tile + 1) * kb_per_tile;
-          const long long seg_end = rg.r1 < tile_end ? rg.r1 : tile_end;
-          const int b = seg_iter % n_acc, use_b = seg_iter / n_acc;
-          if (use_b > 0 && !mbar_wait(acc_empty(b), (use_b - 1) & 1)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t tmem_d = tmem_base + b * acc_cols;
-          bool first = true;
-          for (; r < seg_end; ++r, ++it) {
-            const int s = it % p.stages, use = it / p.stages;
-            if (!mbar_wait(full_bar(s), use & 1)) { ok = false; break; }
-            tc_fence_after();
-            const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
-            const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
-#pragma unroll
-            for (int j = 0; j < kBK / kUmmaK; ++j) {
-              mma_f8(tmem_d, da + 2u * j, db + 2u * j, idesc, (first && j == 0) ? 0u : 1u);
-            }
-            first = false;
-            mma_commit(empty_bar(s));
-          }
-          if (ok) mma_commit(acc_full(b));
-          ++seg_iter;
-        }
-      }
-      if (!ok) *abort_flag = 1;
-    }
-    __syncwarp();
-  } else {
-    // ---- epilogue warps 2..5 --------------------------------------------------------------
-    const int quad = warp & 3;                       // TMEM lanes [32*quad, +32)
-    const int et = threadIdx.x - 64;                 // 0..127 among the epilogue threads
-    const int n_local = quad * 32 + lane;            // weight row inside the tile
-    const size_t part_stride = (size_t)kRowTile * p.mma_n;   // floats per partial tile
-    pdl_wait_prior_grids();                          // outputs / scratch are written only after this
-    const float sx = __ldg(p.sx);
-    int seg_iter = 0;
-    bool ok = true;
-    for (int w = 0; w < p.n_seg && ok; ++w) {
-      const Segment sg = p.seg[w];
-      PsRange rg;
-      if (!ps_range(sg, cta, grid, rg)) continue;
-      const float scale = sx * __ldg(sg.sw);
-      long long r = rg.r;
-      while (r < rg.r1 && ok) {
-        const int tile = (int)(r / kb_per_tile);
-        const long long tile_start = (long long)tile * kb_per_tile;
-        const long long tile_end = tile_start + kb_per_tile;
-        const long long seg_end = rg.r1 < tile_end ? rg.r1 : tile_end;
-        const bool owner = (r == tile_start);        // holds the lowest-K part of the tile
-        const int b = seg_iter % n_acc, use_b = seg_iter / n_acc;
-        // a wait that runs out is recorded, but the warps go on together: leaving the loop
-        // one by one would strand the others at the named barrier
-        if (!mbar_wait(acc_full(b), use_b & 1)) *abort_flag = 1;
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * acc_cols;
-        const int row0 = tile * kRowTile;
-        if (!owner) {
-          // continuation of a tile another CTA owns: publish the partial sum
-          float* dst = p.partials + ((size_t)w * grid + rg.j) * part_stride;
-          for (int c = 0; c < p.mma_n; c += 16) {
-            uint32_t v[16];
-            tmem_ld16(taddr + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (c + i < p.M) dst[(size_t)(c + i) * kRowTile + n_local] = __uint_as_float(v[i]);
-          }
-          __threadfence();
-          epi_bar();
-          if (et == 0) {
-            unsigned int* flag = p.flags + (size_t)w * grid + rg.j;
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
-          }
-        } else {
-          // the CTAs that continue this tile, in ascending K
-          int first_c = rg.j + 1, n_c = 0;
-          if (seg_end < tile_end) {
-            for (int jc = rg.j + 1; jc < sg.ctas; ++jc) {
-              const long long rs = (long long)jc * sg.total_kb / sg.ctas;
-              if (rs >= tile_end) break;
-              ++n_c;
-            }
-            if (et < n_c) {        // one epilogue thread per continuation waits for its flag
-              const unsigned int* flag = p.flags + (size_t)w * grid + first_c + et;
-              const long long t0 = clock64();
-              for (;;) {
-                unsigned int f;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
-                if (f != 0) break;
-                if (clock64() - t0 > kSpinLimitCycles) { *abort_flag = 1; break; }
-              }
-            }
-            epi_bar();
-          }
-          for (int c = 0; c < p.mma_n; c += kPsChunk) {
-            uint32_t v[16];
-            tmem_ld16(taddr + c, v);
-            tmem_ld_wait();
-            float acc[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = __uint_as_float(v[i]);
-            for (int k = 0; k < n_c; ++k) {      // ascending K: fixed order
-              const float* src = p.partials + ((size_t)w * grid + first_c + k) * part_stride;
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (c + i < p.M) acc[i] += __ldcg(src + (size_t)(c + i) * kRowTile + n_local);
-            }
-            // transpose 16 batch rows x 128 weight rows through shared memory so that
-            // each output row is written as one 256-byte run
-#pragma unroll
-            for (int i = 0; i < 16; ++i) xpose[i * kRowTile + n_local] = acc[i] * scale;
-            epi_bar();
-            {
-              const int n4 = lane * 4;
-              const bool col_ok = (row0 + n4) < sg.n;
-#pragma unroll
-              for (int i = 0; i < kPsChunk / 4; ++i) {
-                const int ml = quad + 4 * i;          // rows quad, quad+4, ...
-                const int m = c + ml;
-                const float4 o = *reinterpret_cast<const float4*>(xpose + ml * kRowTile + n4);
-                if (m < p.M && col_ok)
-                  store_out4(sg.y, (long long)m * sg.ldy + row0 + n4, p.out_dtype, o);
-              }
-            }
-            epi_bar();
-          }
-          if (n_c > 0 && et < n_c) p.flags[(size_t)w * grid + first_c + et] = 0u;   // consumed
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(b));
-        r = seg_end;
-        ++seg_iter;
-      }
-    }
-    if (!ok) *abort_flag = 1;
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, (unsigned int)kErrDeviceWait);
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
 // ---------------------------------------------------------------------------
@@ -1471,7 +1037,6 @@ long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
 long long g_opt_pair = 1;       // prefill regime on CTA pairs (cta_group::2)
-long long g_opt_decode_kernel = 1;   // 1 = cluster kernel (default), 0 = persistent when the scratch allows it, 2 = persistent only
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -1485,17 +1050,14 @@ int configure_once() {
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     cudaError_t e3 = cudaFuncSetAttribute(gemm_pair_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    cudaError_t e4 = cudaFuncSetAttribute(gemm_persist_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess && e4 == cudaSuccess)
-             ? kOk : kErrLaunch;
+    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? kOk : kErrLaunch;
     if (rc != kOk) (void)cudaGetLastError();
   }
   return rc;
 }
 
 // Largest grid of the stream kernel that is resident at once with this cluster
-// size and shared-memory footprint (the fused quantizer has grid-wide waits).
+// size and shared-memory footprint (the paired gate/up epilogue has a grid-wide wait).
 int max_resident_ctas(int cluster, int smem) {
   struct Entry { int cluster, smem, cap; };
   static Entry cache[64];
@@ -1611,11 +1173,11 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   if (p.pair.on) p.pair.expected = (unsigned)((p.seg[0].n / kRowTile) * p.seg[0].split);
   if (p.push.n > 0)
     p.push.expected = (unsigned)(((p.seg[0].n + kRowTile - 1) / kRowTile) * p.seg[0].split);
-  if (p.fuse.mode != 0 || (p.pair.on && p.push.n == 0)) {
-    // the in-kernel quantizer waits on the whole grid: every CTA must be resident
+  if (p.pair.on && p.push.n == 0) {
+    // the epilogue's amax exchange waits on the whole grid: every CTA must be resident
     const int cap = max_resident_ctas(cluster, smem);
     if (getenv("BQ_DEBUG"))
-      fprintf(stderr, "[bq] fused launch: grid %lld cluster %d smem %d resident cap %d\n", grid,
+      fprintf(stderr, "[bq] paired launch: grid %lld cluster %d smem %d resident cap %d\n", grid,
               cluster, smem, cap);
     if (cap <= 0 || grid > cap) return kErrUnsupported;
   }
@@ -1637,6 +1199,9 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cfg.numAttrs = g_opt_pdl ? 2 : 1;
   g_last_launch[0] = 0; g_last_launch[1] = grid; g_last_launch[2] = cluster;
   g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
+#ifdef BQ_PHASES
+  p.phase_ring = bq::phase_ring_for_launch(&p.phase_seq);
+#endif
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
@@ -1661,70 +1226,6 @@ int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, 
   cfg.attrs = attr;
   cfg.numAttrs = g_opt_pdl ? 1 : 0;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tile_kernel, tm_x, maps, p);
-  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
-  return kOk;
-}
-
-// Scratch layout of the persistent stream kernel, after the 64 bytes every GEMM scratch starts
-// with (status word): one flag word per (weight, CTA), then the partial tiles.
-constexpr size_t kPsFlagsOffset = 64;
-constexpr size_t kPsPartialsOffset = 64 + 8192;     // room for 8 weights x 256 CTAs of flags
-
-size_t persist_scratch_bytes(int sms, int n_seg, int mma_n) {
-  return kPsPartialsOffset + (size_t)n_seg * sms * kRowTile * mma_n * sizeof(float);
-}
-
-int launch_persist(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, void* ws,
-                   cudaStream_t stream) {
-  const int sms = device_sms();
-  if (sms <= 0 || sms > 256) return kErrLaunch;
-  p.mma_n = ((p.M + 15) / 16) * 16;
-  const int stage_bytes = kATileBytes + p.mma_n * kBK;
-  const int grid = sms;
-  // K blocks a CTA takes from one weight: at least 4 (64 KB of weights), and few enough
-  // CTAs per row tile that one epilogue thread can watch each continuation
-  int min_range = (p.k_blocks + 63) / 64;
-  if (min_range < 4) min_range = 4;
-  int next_begin = 0;
-  long long most = 0;
-  for (int i = 0; i < p.n_seg; ++i) {
-    Segment& sg = p.seg[i];
-    const long long tiles = (sg.n + kRowTile - 1) / kRowTile;
-    sg.total_kb = tiles * p.k_blocks;
-    long long c = sg.total_kb / min_range;
-    if (c < 1) c = 1;
-    if (c > grid) c = grid;
-    sg.ctas = (int)c;
-    sg.cta_begin = next_begin;            // small weights start where the previous one stopped
-    next_begin = (next_begin + sg.ctas) % grid;
-    most += (sg.total_kb + sg.ctas - 1) / sg.ctas;
-  }
-  int stages = (kMaxSmem - 2048 - kPsChunk * kRowTile * 4) / stage_bytes;
-  if (stages > 24) stages = 24;
-  if (most < stages) stages = (int)(most < 2 ? 2 : most);
-  if (g_opt_stages > 0 && g_opt_stages < stages) stages = (int)g_opt_stages;
-  if (stages < 1) return kErrUnsupported;
-  p.stages = stages;
-  const int tile_bytes = stages * stage_bytes;
-  const int smem = tile_bytes + kPsChunk * kRowTile * 4 + kBarrierBytes + 1024;
-  if (smem > kMaxSmem) return kErrUnsupported;
-  p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(ws) + kPsFlagsOffset);
-  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kPsPartialsOffset);
-
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kPsThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = g_opt_pdl ? 1 : 0;
-  g_last_launch[0] = 3; g_last_launch[1] = grid; g_last_launch[2] = 1;
-  g_last_launch[3] = stages; g_last_launch[4] = smem; g_last_launch[5] = p.mma_n;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_persist_kernel, tm_x, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
 }
@@ -1768,11 +1269,6 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "prefill_pair") == 0) { g_opt_pair = value ? 1 : 0; return kOk; }
-  if (strcmp(key, "decode_kernel") == 0) {
-    if (value < 0 || value > 2) return kErrBadArg;
-    g_opt_decode_kernel = value;
-    return kOk;
-  }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;
@@ -1786,18 +1282,9 @@ int bq::gemm_set_option(const char* key, long long value) {
   return kErrBadArg;
 }
 
-extern "C" size_t bq_gemm_workspace_bytes(int64_t M, int64_t, int64_t) {
-  // enough for the persistent kernel with the largest group; 16 bytes select the cluster kernel
-  const int sms = device_sms();
-  if (M <= 0 || M > g_opt_stream_max_m || sms <= 0) return 16;
-  return persist_scratch_bytes(sms, BQ_MAX_SEGMENTS, (int)(((M + 15) / 16) * 16));
-}
-
-extern "C" size_t bq_gemm_scratch_bytes(int64_t M, int n_seg) {
-  const int sms = device_sms();
-  if (M <= 0 || M > g_opt_stream_max_m || sms <= 0 || n_seg < 1) return 16;
-  if (n_seg > BQ_MAX_SEGMENTS) n_seg = BQ_MAX_SEGMENTS;
-  return persist_scratch_bytes(sms, n_seg, (int)(((M + 15) / 16) * 16));
+extern "C" size_t bq_gemm_workspace_bytes(int64_t, int64_t, int64_t) {
+  // the status word and the counters of the paired / push epilogues; partial sums never leave the chip
+  return 16;
 }
 
 namespace {
@@ -1805,14 +1292,14 @@ namespace {
 int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
                 const void* const* wq, const float* const* sw, void* const* y, const int64_t* N,
                 const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
-                const FuseParams* fuse, const void* const* res = nullptr,
+                const void* const* res = nullptr,
                 const int64_t* ld_res = nullptr, const PairSilu* pair = nullptr,
                 int split_forced = 0, const PushParams* push = nullptr) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
     return kErrBadArg;
-  if (ws == nullptr || ws_bytes < (fuse ? 32u : 16u) || !aligned_to(ws, 16)) return kErrWorkspace;
+  if (ws == nullptr || ws_bytes < 16u || !aligned_to(ws, 16)) return kErrWorkspace;
   if (K % 16 || !aligned_to(xq, 16)) return kErrUnsupported;
   if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
   const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
@@ -1826,11 +1313,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     if (N[i] > 0x7fffff00LL) return kErrTooLarge;
   }
   const bool stream_path = M <= g_opt_stream_max_m;
-  if ((fuse || pair) && !stream_path) return kErrUnsupported;   // decode-regime forms only
-  if (pair && (fuse || res || n_seg != 1)) return kErrBadArg;
+  if (pair && !stream_path) return kErrUnsupported;   // decode-regime form only
+  if (pair && (res || n_seg != 1)) return kErrBadArg;
   if (push) {
     if (!stream_path) return kErrUnsupported;
-    if (fuse || res || n_seg != 1) return kErrBadArg;
+    if (res || n_seg != 1) return kErrBadArg;
   }
   if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
     if (!stream_path || ld_res == nullptr) return kErrUnsupported;
@@ -1852,10 +1339,6 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   p.out_dtype = out_dtype;
   // the sticky status word is the 4th word of the scratch, as in the quantizer
   p.status = static_cast<unsigned int*>(ws) + 3;
-  if (fuse) {
-    p.fuse = *fuse;
-    p.fuse.words = static_cast<unsigned int*>(ws);
-  }
   if (pair) {
     p.pair = *pair;
     p.pair.on = 1;
@@ -1891,11 +1374,6 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    if (!fuse && !res && !pair && !push && g_opt_decode_kernel != 1) {
-      const size_t need = persist_scratch_bytes(device_sms(), n_seg, mma_n);
-      if (ws_bytes >= need) return launch_persist(tm_x, maps, p, ws, stream);
-      if (g_opt_decode_kernel == 2) return kErrWorkspace;
-    }
     return launch_stream(tm_x, maps, p, stream);
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
@@ -1909,49 +1387,7 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
                                     const void* const* wq, const float* const* sw, void* const* y,
                                     const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
                                     size_t ws_bytes, void* stream_v) {
-  return run_grouped(xq, sx, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v,
-                     nullptr);
-}
-
-extern "C" int bq_linear_w8a8_grouped(const void* a, const void* b, int mode, int act_dtype,
-                                      int64_t M, int64_t K, int64_t ld_a, int64_t ld_b,
-                                      int64_t chunk, int64_t chunk_stride, void* xq_out,
-                                      float* sx_out, int n_seg, const void* const* wq,
-                                      const float* const* sw, void* const* y, const int64_t* N,
-                                      const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes,
-                                      void* stream_v) {
-  if (!a || !xq_out || !sx_out || M <= 0 || K <= 0) return kErrBadArg;
-  if (mode < 1 || mode > 3 || (mode != 1 && !b)) return kErrBadArg;
-  if (act_dtype != BQ_DTYPE_F32 && act_dtype != BQ_DTYPE_BF16 && act_dtype != BQ_DTYPE_F16)
-    return kErrBadArg;
-  const size_t es = act_dtype == BQ_DTYPE_F32 ? 4 : 2;
-  if (K % 16 || !aligned_to(a, 16) || !aligned_to(xq_out, 16)) return kErrUnsupported;
-  if (mode == 1) {
-    if (ld_a != K) return kErrUnsupported;          // the plain form reads a dense [M, K]
-  } else {
-    if (ld_a < K || (ld_a * es) % 16 || (ld_b * es) % 16 || !aligned_to(b, 16)) return kErrUnsupported;
-    if (mode == 2 && ld_b < K) return kErrUnsupported;
-    if (mode == 3 && (chunk <= 0 || chunk % 8 || K % chunk || (chunk_stride * es) % 16))
-      return kErrUnsupported;
-  }
-  if (M * (K / 8) >= 0x7fffffffLL) return kErrTooLarge;
-  FuseParams f;
-  memset(&f, 0, sizeof(f));
-  f.mode = mode;
-  f.dtype = act_dtype;
-  f.q.a = a;
-  f.q.b = b;
-  f.q.q = static_cast<uint8_t*>(xq_out);
-  f.q.scale = sx_out;
-  f.q.n_groups = (unsigned int)(M * (K / 8));
-  f.q.tail = 0;
-  f.q.groups_per_row = (unsigned int)(K / 8);
-  f.q.ld_a = ld_a;
-  f.q.ld_b = ld_b;
-  f.q.chunk = (unsigned int)(mode == 3 ? chunk : K);
-  f.q.chunk_stride = chunk_stride;
-  return run_grouped(xq_out, sx_out, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes,
-                     stream_v, &f);
+  return run_grouped(xq, sx, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v);
 }
 
 extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* sw,
@@ -1988,7 +1424,7 @@ extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const
   const int k_blocks = (int)((K + kBK - 1) / kBK);
   const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight((int)I, k_blocks) : 1;
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
-                     nullptr, nullptr, nullptr, &pair, split);
+                     nullptr, nullptr, &pair, split);
 }
 
 namespace {
@@ -2022,7 +1458,7 @@ extern "C" int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx
   const int64_t Ns[1] = {N};
   const int64_t ldys[1] = {0};
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes, stream,
-                     nullptr, nullptr, nullptr, nullptr, 0, &push);
+                     nullptr, nullptr, nullptr, 0, &push);
 }
 
 extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
@@ -2046,7 +1482,7 @@ extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const 
   const int k_blocks = (int)((K + kBK - 1) / kBK);
   const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight(I, k_blocks) : 1;
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
-                     nullptr, nullptr, nullptr, &pair, split, &push);
+                     nullptr, nullptr, &pair, split, &push);
 }
 
 extern "C" int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word,
@@ -2073,7 +1509,7 @@ extern "C" int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float
   const void* rs[1] = {residual};
   const int64_t ldrs[1] = {ld_res};
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes, stream,
-                     nullptr, rs, ldrs);
+                     rs, ldrs);
 }
 
 

@@ -248,6 +248,35 @@ __device__ __forceinline__ void pdl_wait_prior_grids() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// ---- phase stamps (development builds only: -DBQ_PHASES) ------------------------------------
+// A build with BQ_PHASES records nanosecond stamps (%globaltimer) of the phases of every CTA of
+// the decode-regime kernels into a ring in device memory; the shipped library compiles none of
+// it.  Ring layout: [launch % kPhaseLaunches][cta < kPhaseCtas][kPhaseWords] of u64; word 8 is
+// the SM id, word 9 is (grid << 8 | kind) with kind 0 = GEMM, 1 = quantizer.
+constexpr int kPhaseLaunches = 1024, kPhaseCtas = 256, kPhaseWords = 10;
+#ifdef BQ_PHASES
+unsigned long long* phase_ring_for_launch(int* seq_out);   // host; cabi.cu
+__device__ __forceinline__ void phase_stamp(unsigned long long* ring, int seq, int idx) {
+  if (ring == nullptr || blockIdx.x >= kPhaseCtas) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  ring[((size_t)(seq % kPhaseLaunches) * kPhaseCtas + blockIdx.x) * kPhaseWords + idx] = t;
+}
+__device__ __forceinline__ void phase_meta(unsigned long long* ring, int seq, int kind) {
+  if (ring == nullptr || blockIdx.x >= kPhaseCtas) return;
+  unsigned int smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  unsigned long long* at = ring + ((size_t)(seq % kPhaseLaunches) * kPhaseCtas + blockIdx.x) * kPhaseWords;
+  at[8] = smid;
+  at[9] = ((unsigned long long)gridDim.x << 8) | (unsigned long long)kind;
+}
+#define BQ_STAMP(p, idx) ::bq::phase_stamp((p).phase_ring, (p).phase_seq, (idx))
+#define BQ_STAMP_META(p, kind) ::bq::phase_meta((p).phase_ring, (p).phase_seq, (kind))
+#else
+#define BQ_STAMP(p, idx) ((void)0)
+#define BQ_STAMP_META(p, kind) ((void)0)
+#endif
+
 // ---- thread-block clusters ----------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -44,19 +44,26 @@ using namespace bq::qd;
 // are issued before the first value is used.
 template <typename T, int MODE, int MAXH>
 __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
+  if (threadIdx.x == 0) { BQ_STAMP(p, 0); BQ_STAMP_META(p, 1); }
   bq::pdl_launch_dependents();
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
   Pack8<T> held[MAXH];
   Pack8<T> other[MODE == kPlain ? 1 : MAXH];
   bq::pdl_wait_prior_grids();   // the activation is the previous kernel's output
-  if (p.wait_flag != nullptr)
+  if (threadIdx.x == 0) BQ_STAMP(p, 2);
+  // a gathered buffer that peers store into while this kernel is resident is read with
+  // coherent loads, after the arrival wait
+  const bool coherent = p.wait_flag != nullptr;
+  if (coherent)
     grid_wait_arrivals(p.wait_flag, p.wait_seen, p.wait_count, static_cast<QuantWs*>(p.ws));
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) {
     const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
-    if (i < p.held && g < p.n_groups)
-      load_raw<T, MODE>(p, g, held[i], other[MODE == kPlain ? 0 : i]);
+    if (i < p.held && g < p.n_groups) {
+      if (coherent) load_raw<T, MODE, true>(p, g, held[i], other[MODE == kPlain ? 0 : i]);
+      else load_raw<T, MODE, false>(p, g, held[i], other[MODE == kPlain ? 0 : i]);
+    }
   }
   float m = 0.0f;
 #pragma unroll
@@ -73,11 +80,12 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
   if (owns_tail) {
     const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
     for (unsigned int i = 0; i < p.tail; ++i) {
-      tail_v[i] = widen(src[i]);
+      tail_v[i] = widen(coherent ? __ldcg(src + i) : src[i]);
       m = nan_max(m, fabsf(tail_v[i]));
     }
   }
   const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+  if (threadIdx.x == 0) BQ_STAMP(p, 4);
   if (tid == 0) p.scale[0] = sc;
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) {
@@ -90,69 +98,95 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
       dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
   }
   grid_depart(static_cast<QuantWs*>(p.ws), p.wait_flag != nullptr ? p.wait_seen : nullptr, p.wait_count);
+  if (threadIdx.x == 0) BQ_STAMP(p, 7);
 }
 
 // Streaming variant for activations that do not fit in the register file of
 // one co-resident grid: pass 1 reduces, pass 2 re-reads (L2) and casts.  Both
 // passes keep kUnroll independent groups in flight per thread.
-template <typename T, int MODE>
+// PHASE selects what runs: kBoth (the quantizer), kScaleOnly (pass 1 and the grid-wide
+// exchange; writes the scale, no codes), kCastOnly (pass 2 with the scale read from p.scale;
+// no exchange, so the grid need not be co-resident).  The two halves exist for the
+// column-parallel MLP: every rank takes the scale of its own shard, the ranks combine the
+// scales with a MAX all-reduce (max is exact and order-free, and the scale is a monotone
+// function of the amax), and every rank casts its shard with the combined scale.
+enum Phase { kBoth = 0, kScaleOnly = 1, kCastOnly = 2 };
+
+template <typename T, int MODE, int PHASE>
 __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
   constexpr int kUnroll = (MODE == kPlain) ? 4 : 2;
   bq::pdl_launch_dependents();
   const unsigned int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const unsigned int nthreads = gridDim.x * blockDim.x;
   bq::pdl_wait_prior_grids();
-  if (p.wait_flag != nullptr)
+  const bool coherent = p.wait_flag != nullptr;
+  if (coherent)
     grid_wait_arrivals(p.wait_flag, p.wait_seen, p.wait_count, static_cast<QuantWs*>(p.ws));
-  float m = 0.0f;
-  for (unsigned int g0 = tid; g0 < p.n_groups; g0 += nthreads * kUnroll) {
-    Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
-      if (g < p.n_groups) load_raw<T, MODE>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
-      if (g < p.n_groups) {
-        apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
-        m = absmax8(a[u], m);
-      }
-    }
-  }
   const bool owns_tail = (MODE == kPlain) && p.tail != 0 && tid == nthreads - 1;
-  if (owns_tail) {
-    const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
-    for (unsigned int i = 0; i < p.tail; ++i) m = nan_max(m, fabsf(widen(src[i])));
-  }
-  const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
-  if (tid == 0) p.scale[0] = sc;
-  // walk backwards: the groups read last in pass 1 are the likeliest still in L2
-  const long long last = (long long)p.n_groups - 1 - tid;
-  for (long long g0 = last; g0 >= 0; g0 -= (long long)nthreads * kUnroll) {
-    Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
+  float sc;
+  if constexpr (PHASE == kCastOnly) {
+    sc = __ldcg(p.scale);
+  } else {
+    float m = 0.0f;
+    for (unsigned int g0 = tid; g0 < p.n_groups; g0 += nthreads * kUnroll) {
+      Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const long long g = g0 - (long long)u * nthreads;
-      if (g >= 0) load_raw<T, MODE>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
-    }
+      for (int u = 0; u < kUnroll; ++u) {
+        const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
+        if (g < p.n_groups) {
+          if (coherent) load_raw<T, MODE, true>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+          else load_raw<T, MODE, false>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+        }
+      }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const long long g = g0 - (long long)u * nthreads;
-      if (g >= 0) {
-        apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
-        emit8(a[u], sc, p.q + static_cast<size_t>(g) * kGroup);
+      for (int u = 0; u < kUnroll; ++u) {
+        const unsigned long long g = (unsigned long long)g0 + (unsigned long long)u * nthreads;
+        if (g < p.n_groups) {
+          apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
+          m = absmax8(a[u], m);
+        }
       }
     }
+    if (owns_tail) {
+      const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+      for (unsigned int i = 0; i < p.tail; ++i)
+        m = nan_max(m, fabsf(widen(coherent ? __ldcg(src + i) : src[i])));
+    }
+    sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+    if (tid == 0) p.scale[0] = sc;
   }
-  if (owns_tail) {
-    const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
-    uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
-    for (unsigned int i = 0; i < p.tail; ++i)
-      dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(src[i]), sc), __NV_SATFINITE, __NV_E4M3);
+  if constexpr (PHASE != kScaleOnly) {
+    // walk backwards: the groups read last in pass 1 are the likeliest still in L2
+    const long long last = (long long)p.n_groups - 1 - tid;
+    for (long long g0 = last; g0 >= 0; g0 -= (long long)nthreads * kUnroll) {
+      Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long g = g0 - (long long)u * nthreads;
+        if (g >= 0) {
+          if (coherent) load_raw<T, MODE, true>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+          else load_raw<T, MODE, false>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long g = g0 - (long long)u * nthreads;
+        if (g >= 0) {
+          apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
+          emit8(a[u], sc, p.q + static_cast<size_t>(g) * kGroup);
+        }
+      }
+    }
+    if (owns_tail) {
+      const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+      uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
+      for (unsigned int i = 0; i < p.tail; ++i)
+        dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(coherent ? __ldcg(src + i) : src[i]), sc),
+                                       __NV_SATFINITE, __NV_E4M3);
+    }
   }
-  grid_depart(static_cast<QuantWs*>(p.ws), p.wait_flag != nullptr ? p.wait_seen : nullptr, p.wait_count);
+  if constexpr (PHASE != kCastOnly)
+    grid_depart(static_cast<QuantWs*>(p.ws), coherent ? p.wait_seen : nullptr, p.wait_count);
 }
 
 struct DeviceInfo {
@@ -176,7 +210,11 @@ long long g_opt_quant_held = 0;    // 0 = heuristic
 long long g_opt_quant_pdl = 1;     // programmatic dependent launch on by default
 
 template <typename Kernel>
-int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p, cudaStream_t stream) {
+int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p_in, cudaStream_t stream) {
+  QParams p = p_in;
+#ifdef BQ_PHASES
+  p.phase_ring = bq::phase_ring_for_launch(&p.phase_seq);
+#endif
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3((unsigned)block, 1, 1);
@@ -224,7 +262,7 @@ int launch_quant(QParams p, cudaStream_t stream) {
     return launch_with_pdl(quant_hold_kernel<T, MODE, kMaxH>, grid, block, p, stream);
   }
   p.held = 0;
-  return launch_with_pdl(quant_stream_kernel<T, MODE>, 2 * sms, 512, p, stream);
+  return launch_with_pdl(quant_stream_kernel<T, MODE, kBoth>, 2 * sms, 512, p, stream);
 }
 
 template <int MODE>
@@ -233,6 +271,27 @@ int dispatch_dtype(int dtype, const QParams& p, cudaStream_t stream) {
     case BQ_DTYPE_F32: return launch_quant<float, MODE>(p, stream);
     case BQ_DTYPE_BF16: return launch_quant<__nv_bfloat16, MODE>(p, stream);
     case BQ_DTYPE_F16: return launch_quant<__half, MODE>(p, stream);
+    default: return bq::kErrBadArg;
+  }
+}
+
+// One half of the quantizer (see Phase): always the streaming kernel.
+template <int MODE, int PHASE>
+int dispatch_phase(int dtype, const QParams& p, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return bq::kErrLaunch;
+  // the scale half waits on the whole grid (co-resident: 2 CTAs of 512 threads per SM at most);
+  // small inputs get a grid that matches their size
+  unsigned long long want = ((unsigned long long)p.n_groups + 511ull) / 512ull;
+  if (want < 1) want = 1;
+  const int grid = (int)(want < (unsigned long long)(2 * sms) ? want : (unsigned long long)(2 * sms));
+  switch (dtype) {
+    case BQ_DTYPE_F32:
+      return launch_with_pdl(quant_stream_kernel<float, MODE, PHASE>, grid, 512, p, stream);
+    case BQ_DTYPE_BF16:
+      return launch_with_pdl(quant_stream_kernel<__nv_bfloat16, MODE, PHASE>, grid, 512, p, stream);
+    case BQ_DTYPE_F16:
+      return launch_with_pdl(quant_stream_kernel<__half, MODE, PHASE>, grid, 512, p, stream);
     default: return bq::kErrBadArg;
   }
 }
@@ -327,6 +386,50 @@ extern "C" int bq_silu_mul_quant(const void* gate, const void* up, int dtype, in
   p.ld_a = ld_gate;
   p.ld_b = ld_up;
   return dispatch_dtype<kSiluMul>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+int fill_silu_mul(QParams* p, const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                  int64_t ld_gate, int64_t ld_up) {
+  if (!gate || !up || rows <= 0 || cols <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  const size_t es = elem_size(dtype);
+  if (cols % kGroup || ld_gate < cols || ld_up < cols || (ld_gate * es) % 16 || (ld_up * es) % 16 ||
+      !aligned_to(gate, 16) || !aligned_to(up, 16))
+    return bq::kErrUnsupported;
+  if (rows * (cols / kGroup) >= 0x7fffffffLL) return bq::kErrTooLarge;
+  p->a = gate;
+  p->b = up;
+  p->groups_per_row = static_cast<unsigned int>(cols / kGroup);
+  p->n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
+  p->ld_a = ld_gate;
+  p->ld_b = ld_up;
+  return bq::kOk;
+}
+}  // namespace
+
+extern "C" int bq_silu_mul_scale(const void* gate, const void* up, int dtype, int64_t rows,
+                                 int64_t cols, int64_t ld_gate, int64_t ld_up, float* scale_out,
+                                 void* ws, size_t ws_bytes, void* stream) {
+  if (!scale_out) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  QParams p{};
+  if (int rc = fill_silu_mul(&p, gate, up, dtype, rows, cols, ld_gate, ld_up)) return rc;
+  p.scale = scale_out;
+  p.ws = ws;
+  return dispatch_phase<kSiluMul, kScaleOnly>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_silu_mul_cast(const void* gate, const void* up, int dtype, int64_t rows,
+                                int64_t cols, int64_t ld_gate, int64_t ld_up, const float* scale,
+                                void* q_out, void* stream) {
+  if (!scale || !q_out) return bq::kErrBadArg;
+  if (!aligned_to(q_out, 8)) return bq::kErrUnsupported;
+  QParams p{};
+  if (int rc = fill_silu_mul(&p, gate, up, dtype, rows, cols, ld_gate, ld_up)) return rc;
+  p.scale = const_cast<float*>(scale);   // read only in this phase
+  p.q = static_cast<uint8_t*>(q_out);
+  return dispatch_phase<kSiluMul, kCastOnly>(dtype, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t rows,

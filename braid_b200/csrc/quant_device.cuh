@@ -1,5 +1,5 @@
 // Device-side building blocks of the FP8 activation quantizer, shared by the stand-alone
-// quantizer kernels (quant_act.cu) and the fused quantize-and-multiply kernel (gemm_w8a8.cu).
+// quantizer kernels (quant_act.cu, norm_quant.cu) and the paired gate/up epilogue (gemm_w8a8.cu).
 // The arithmetic is the reference's torch spelling as a CUDA device evaluates it
 // (braid/model/quant.py:108-115, :228-229): reciprocal-multiply scale, IEEE division,
 // comparison clamps (NaN survives), NaN-propagating max, round-to-nearest-even e4m3 cast; the
@@ -42,6 +42,8 @@ struct QParams {
   const unsigned int* wait_flag;
   unsigned int* wait_seen;
   unsigned int wait_count;
+  unsigned long long* phase_ring;   // development builds (BQ_PHASES) only, else nullptr
+  int phase_seq;
 };
 
 template <typename T> struct alignas(16) Pack8 { T v[8]; };
@@ -60,56 +62,25 @@ template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float
 // NaN-propagating max: once either side is NaN the result is NaN.
 __device__ __forceinline__ float nan_max(float m, float v) { return (v != v || v > m) ? v : m; }
 
-template <typename T>
+// COHERENT = false: read-only path (`ld.global.nc`), for inputs nobody writes while the kernel
+// is resident.  COHERENT = true: L2-coherent loads (`ld.global.cg`), for a gathered buffer that
+// other GPUs (and this GPU's own push launch) are still storing into while this kernel waits
+// for their arrival -- the non-coherent path promises nothing for such data.
+template <typename T, bool COHERENT = false>
 __device__ __forceinline__ Pack8<T> load8(const T* p) {
   Pack8<T> r;
   if constexpr (sizeof(T) == 4) {
-    const float4 lo = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    const float4* q = reinterpret_cast<const float4*>(p);
+    const float4 lo = COHERENT ? __ldcg(q) : __ldg(q);
+    const float4 hi = COHERENT ? __ldcg(q + 1) : __ldg(q + 1);
     r.v[0] = lo.x; r.v[1] = lo.y; r.v[2] = lo.z; r.v[3] = lo.w;
     r.v[4] = hi.x; r.v[5] = hi.y; r.v[6] = hi.z; r.v[7] = hi.w;
   } else {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+    const uint4 raw = COHERENT ? __ldcg(q) : __ldg(q);
     *reinterpret_cast<uint4*>(&r) = raw;
   }
   return r;
-}
-
-// Builds the 8 activation values of group g for the given prologue.
-template <typename T, int MODE>
-__device__ __forceinline__ Pack8<T> produce(const QParams& p, unsigned int g) {
-  if constexpr (MODE == kPlain) {
-    return load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
-  } else {
-    const unsigned int row = g / p.groups_per_row;
-    const unsigned int col = (g - row * p.groups_per_row) * kGroup;
-    const T* pa = reinterpret_cast<const T*>(p.a) + static_cast<long long>(row) * p.ld_a + col;
-    const T* pb;
-    if constexpr (MODE == kSiluMul) {
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b + col;
-    } else {
-      const unsigned int head = col / p.chunk;
-      pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
-           static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
-    }
-    const Pack8<T> a = load8(pa);
-    const Pack8<T> b = load8(pb);
-    Pack8<T> h;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if constexpr (MODE == kSiluMul) {
-        // silu in fp32, rounded to T; product in fp32, rounded to T
-        const float x = widen(a.v[i]);
-        const T s = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
-        h.v[i] = narrow<T>(widen(s) * widen(b.v[i]));
-      } else {
-        const float gt = widen(b.v[i]);
-        const T s = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
-        h.v[i] = narrow<T>(widen(a.v[i]) * widen(s));
-      }
-    }
-    return h;
-  }
 }
 
 template <typename T>
@@ -150,15 +121,10 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
 }
 
 // Raw operands of one group: one 8-pack for the plain mode, two for the prologues.
-template <typename T, int MODE> struct RawGroup {
-  Pack8<T> a;
-  Pack8<T> b;
-};
-
-template <typename T, int MODE>
+template <typename T, int MODE, bool COHERENT = false>
 __device__ __forceinline__ void load_raw(const QParams& p, unsigned int g, Pack8<T>& a, Pack8<T>& b) {
   if constexpr (MODE == kPlain) {
-    a = load8(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
+    a = load8<T, COHERENT>(reinterpret_cast<const T*>(p.a) + static_cast<size_t>(g) * kGroup);
   } else {
     const unsigned int row = g / p.groups_per_row;
     const unsigned int col = (g - row * p.groups_per_row) * kGroup;
@@ -171,8 +137,8 @@ __device__ __forceinline__ void load_raw(const QParams& p, unsigned int g, Pack8
       pb = reinterpret_cast<const T*>(p.b) + static_cast<long long>(row) * p.ld_b +
            static_cast<long long>(head) * p.chunk_stride + (col - head * p.chunk);
     }
-    a = load8(pa);
-    b = load8(pb);
+    a = load8<T, COHERENT>(pa);
+    b = load8<T, COHERENT>(pb);
   }
 }
 

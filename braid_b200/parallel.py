@@ -87,68 +87,44 @@ class ColumnParallelMLP:
         return cls(mk(inter, hidden), mk(inter, hidden), mk(hidden, inter), group, ops)
 
     def gather_bytes(self, rows: int) -> dict:
-        return {"h": rows * self.I * 2, "y": rows * self.H * 2}
+        """Bytes every rank ends up holding after each exchange (codes or bf16 for h, bf16 for y)."""
+        return {"h": rows * self.I * (1 if rows >= self.codes_from else 2), "y": rows * self.H * 2,
+                "h_form": "e4m3 codes + MAX all-reduce of the scale" if rows >= self.codes_from
+                else "bf16"}
 
-    # Rows per pipeline chunk of the overlapped form, and the row count from which it is used.
-    # Off by default: measured on 2 GPUs at M = 4096 it is slower than the plain form (0.79 ms
-    # against 0.72 ms per MLP) -- four 1024-row GEMMs run below the rate of one 4096-row GEMM and
-    # the concurrent all-gather takes bandwidth from them.
-    pipeline_rows = 1024
-    pipeline_from = 1 << 62
+    # From this many rows on, the h exchange moves FP8 codes instead of bf16 values (half the
+    # bytes, and nobody re-quantizes the gathered tensor); below it the exchange is bound by the
+    # latency of the collectives, and the codes form needs one more (the 4-byte MAX all-reduce).
+    codes_from = 257
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ops = self.ops
         *lead, K = x.shape
         x2 = x.reshape(-1, K)
+        M = x2.shape[0]
         i_sizes = [hi - lo for lo, hi in self.i_ranges]
         h_sizes = [hi - lo for lo, hi in self.h_ranges]
-        if (x2.shape[0] >= self.pipeline_from and len(set(i_sizes)) == 1 and len(set(h_sizes)) == 1):
-            return self._forward_pipelined(x2).reshape(*lead, self.H)
         xq, sx = ops.quantize_act(x2)                       # identical on every rank
-        g, u = ops.fp8_matmul_grouped(xq, sx, (self.gate, self.up), out_dtype=x.dtype)
-        h_local = F.silu(g) * u                             # bf16, as the reference rounds it
-        h = gather_columns(h_local, self.group, i_sizes)
-        hq, sh = ops.quantize_act(h)                        # full-tensor scale, identical everywhere
+        n = i_sizes[self.rank]
+        gu = torch.empty((M, 2 * n), dtype=x.dtype, device=x.device)
+        g, u = gu[:, :n], gu[:, n:]
+        ops.fp8_matmul_grouped(xq, sx, (self.gate, self.up), out_dtype=x.dtype, out=(g, u))
+        if M >= self.codes_from:
+            # Scale of this rank's shard of h = silu(gate) * up, MAX over the ranks (the scale is
+            # a monotone function of the amax and max is exact, so this IS the scale of the whole
+            # h on every rank), then the cast of the shard with it: codes equal, byte for byte,
+            # the ones a quantizer of the gathered h would produce.
+            sh = ops.silu_mul_scale(g, u)
+            dist.all_reduce(sh, op=dist.ReduceOp.MAX, group=self.group)
+            hq_local = ops.silu_mul_cast(g, u, sh)
+            hq = gather_columns(hq_local.view(torch.uint8), self.group, i_sizes).view(hq_local.dtype)
+        else:
+            h_local = F.silu(g) * u                         # bf16, as the reference rounds it
+            h = gather_columns(h_local, self.group, i_sizes)
+            hq, sh = ops.quantize_act(h)                    # full-tensor scale, identical everywhere
         (y_local,) = ops.fp8_matmul_grouped(hq, sh, (self.down,), out_dtype=x.dtype)
         y = gather_columns(y_local, self.group, h_sizes)
         return y.reshape(*lead, self.H)
-
-    def _gather_rows_async(self, local: torch.Tensor):
-        """Start the all-gather of one row chunk `[m, n]`; returns (work, flat `[world*m, n]`)."""
-        flat = torch.empty((self.world * local.shape[0], local.shape[1]), dtype=local.dtype,
-                           device=local.device)
-        return dist.all_gather_into_tensor(flat, local, group=self.group, async_op=True), flat
-
-    def _forward_pipelined(self, x2: torch.Tensor) -> torch.Tensor:
-        """Prefill sizes: the rows are cut into chunks and the all-gather of chunk c runs (on the
-        collective's own stream) while the GEMM of chunk c+1 computes, for both exchanges.  A row
-        of a GEMM does not depend on which rows share its launch and the two quantizers still
-        see whole tensors, so the result equals the unchunked form bit for bit."""
-        ops, world = self.ops, self.world
-        M = x2.shape[0]
-        chunks = [(lo, min(lo + self.pipeline_rows, M)) for lo in range(0, M, self.pipeline_rows)]
-        n_i, n_h = self.i_ranges[0][1] - self.i_ranges[0][0], self.h_ranges[0][1] - self.h_ranges[0][0]
-        xq, sx = ops.quantize_act(x2)
-        h = torch.empty((M, self.I), dtype=x2.dtype, device=x2.device)
-        pending = []
-        for lo, hi in chunks:
-            g, u = ops.fp8_matmul_grouped(xq[lo:hi], sx, (self.gate, self.up), out_dtype=x2.dtype)
-            h_local = (F.silu(g) * u).contiguous()
-            pending.append((lo, hi, h_local) + self._gather_rows_async(h_local))
-        for lo, hi, _keep, work, flat in pending:
-            work.wait()
-            h[lo:hi].view(hi - lo, world, n_i).copy_(flat.view(world, hi - lo, n_i).permute(1, 0, 2))
-        hq, sh = ops.quantize_act(h)
-        y = torch.empty((M, self.H), dtype=x2.dtype, device=x2.device)
-        pending = []
-        for lo, hi in chunks:
-            (y_local,) = ops.fp8_matmul_grouped(hq[lo:hi], sh, (self.down,), out_dtype=x2.dtype)
-            y_local = y_local.contiguous()
-            pending.append((lo, hi, y_local) + self._gather_rows_async(y_local))
-        for lo, hi, _keep, work, flat in pending:
-            work.wait()
-            y[lo:hi].view(hi - lo, world, n_h).copy_(flat.view(world, hi - lo, n_h).permute(1, 0, 2))
-        return y
 
     __call__ = forward
 
@@ -319,6 +295,15 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         return b.y[:M]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """The MLP output `[..., H]`.
+
+        At decode sizes the result is a VIEW of this rank's gathered `y` buffer, which every
+        rank overwrites during the next call on this object: consume it (or copy it) on the
+        launching stream before calling again.  `copy_out = True` returns a fresh tensor instead
+        (one small device copy).  Larger M takes the NCCL form, which always returns a fresh
+        tensor.  Ranks must be barriered, with their warm-up done, before the first call: a peer
+        that is more than the wait bound (about half a second) late makes the bounded waits run
+        out, which `last_status()` reports."""
         *lead, K = x.shape
         x2 = x.reshape(-1, K)
         M = x2.shape[0]
@@ -326,6 +311,22 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
             return super().forward(x)                    # prefill sizes: the NCCL form
         self.push_h(x2)
         self.wait_h_push_y(M)
-        return self.wait_y(M).reshape(*lead, self.H)
+        y = self.wait_y(M)
+        if self.copy_out:
+            y = y.clone()
+        return y.reshape(*lead, self.H)
+
+    copy_out = False
+
+    def last_status(self) -> int:
+        """Synchronises and returns non-zero if any bounded wait of this object's exchanges (or of
+        the kernels that carried them) has run out since the last check; the result of such a
+        call is built from incomplete data and must be discarded.  Call it where the host
+        already synchronises, never during capture."""
+        torch.cuda.synchronize(self.buffers.device)
+        bad = int(self.buffers.status.item())
+        if bad:
+            self.buffers.status.zero_()
+        return bad or int(self.ops.device_status(self.buffers.device))
 
     __call__ = forward

@@ -215,40 +215,13 @@ def _scratch_for(device_index: int) -> torch.Tensor:
 def _take_slot(device: torch.device) -> int:
     """Device address of the next scratch slot of this device."""
     global _launches
-    _launches += 1
     idx = device.index if device.index is not None else torch.cuda.current_device()
     buf = _scratch_for(idx)
-    slot = _next_slot[idx]
-    _next_slot[idx] = (slot + 1) % _SLOTS
+    with _LOCK:
+        _launches += 1
+        slot = _next_slot[idx]
+        _next_slot[idx] = (slot + 1) % _SLOTS
     return buf.data_ptr() + slot * _SLOT_BYTES
-
-
-# Scratch of the persistent weight-streaming GEMM: partial sums of row tiles that straddle two
-# SMs.  One buffer per device, grown on demand outside captures; launches that use it are
-# ordered on the stream they run on.
-_gemm_scratch: dict[int, torch.Tensor] = {}
-_PERSISTENT_DECODE = False     # set by set_option("decode_kernel", 0 or 2); the default is the cluster kernel
-
-
-def _gemm_scratch_for(device: torch.device, M: int, n_seg: int) -> tuple[int, int]:
-    """(address, bytes) of a GEMM scratch that is large enough, else of a plain 64-byte slot."""
-    global _launches
-    if not _PERSISTENT_DECODE:
-        return _take_slot(device), 16
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    need = int(_require_lib().bq_gemm_scratch_bytes(M, n_seg))
-    buf = _gemm_scratch.get(idx)
-    if need > 16 and (buf is None or buf.numel() < need):
-        if torch.cuda.is_current_stream_capturing():
-            return _take_slot(device), 16       # cannot grow inside a capture: cluster kernel
-        torch.cuda.synchronize(idx)
-        buf = torch.zeros(need, dtype=torch.uint8, device=torch.device("cuda", idx))
-        torch.cuda.synchronize(idx)
-        _gemm_scratch[idx] = buf
-    if need <= 16 or buf is None:
-        return _take_slot(device), 16
-    _launches += 1
-    return buf.data_ptr(), buf.numel()
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -275,28 +248,19 @@ def device_status(device: torch.device | int | None = None) -> int:
     bad = int(words.max().item())
     if bad:
         words.zero_()
-    big = _gemm_scratch.get(idx)
-    if big is not None:
-        word = big[:16].view(torch.int32)[3:4]
-        if int(word.item()):
-            bad = bad or int(word.item())
-            word.zero_()
     return bad
 
 
 def set_option(key: str, value: int) -> None:
     """Tuning switch of the library (`decode_split_k`, `decode_stages`, `quant_block`, ...)."""
-    global _PERSISTENT_DECODE
     _lib.check(_require_lib().bq_set_option(key.encode(), int(value)), f"set_option({key})")
-    if key == "decode_kernel":
-        _PERSISTENT_DECODE = int(value) != 1
 
 
 def last_gemm_launch() -> dict:
     """What the last GEMM call of this thread launched (kernel, grid, split, stages, smem, tile)."""
     out = (ctypes.c_int64 * 6)()
     _lib.check(_require_lib().bq_last_gemm_launch(out), "last_gemm_launch")
-    return {"kernel": {0: "stream", 1: "tile", 2: "pair", 3: "persist"}.get(int(out[0]), "?"),
+    return {"kernel": {0: "stream", 1: "tile", 2: "pair"}.get(int(out[0]), "?"),
             "grid": out[1], "split": out[2],
             "stages": out[3], "smem": out[4], "mma_n": out[5]}
 
@@ -388,6 +352,55 @@ def silu_mul_quant(gate: torch.Tensor, up: torch.Tensor) -> tuple[torch.Tensor, 
                                _take_slot(gate.device), 16, _stream_ptr(gate.device))
     _lib.check(rc, "silu_mul_quant")
     return q.reshape(*gate.shape[:-1], cols), scale
+
+
+def _silu_mul_args(gate: torch.Tensor, up: torch.Tensor, what: str):
+    _check_cuda(gate, what)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    code = _DTYPE_CODE.get(gate.dtype)
+    if code is None:
+        raise ValueError(f"activation must be fp32, bf16 or fp16, got {gate.dtype}")
+    cols = gate.shape[-1]
+    return code, cols, _as_rows(gate, cols), _as_rows(up, cols)
+
+
+def silu_mul_scale(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """The `[1, 1]` scale `quantize_act(F.silu(gate) * up)` would return, without the codes.
+
+    First half of the column-parallel MLP's exchange: every rank takes the scale of its own
+    column shard, a MAX all-reduce over the ranks turns it into the scale of the whole
+    intermediate (max is exact), and `silu_mul_cast` casts the shard with it."""
+    code, cols, g2, u2 = _silu_mul_args(gate, up, "silu_mul_scale")
+    if _quantizers_off():
+        return _act_scale(F.silu(gate) * up)
+    lib = _require_lib()
+    scale = torch.empty((1, 1), dtype=torch.float32, device=gate.device)
+    rc = lib.bq_silu_mul_scale(g2.data_ptr(), u2.data_ptr(), code, g2.shape[0], cols,
+                               g2.stride(0), u2.stride(0), scale.data_ptr(),
+                               _take_slot(gate.device), 16, _stream_ptr(gate.device))
+    _lib.check(rc, "silu_mul_scale")
+    return scale
+
+
+def silu_mul_cast(gate: torch.Tensor, up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 codes of `F.silu(gate) * up` under a scale decided elsewhere (a `[1, 1]` fp32 device
+    tensor): `clamp(h / scale, +-448)` cast, the second half of `silu_mul_quant`."""
+    code, cols, g2, u2 = _silu_mul_args(gate, up, "silu_mul_cast")
+    if scale.dtype is not torch.float32 or scale.numel() != 1 or not scale.is_cuda:
+        raise ValueError("scale must be a one-element fp32 CUDA tensor")
+    if _quantizers_off():
+        h = F.silu(gate) * up
+        return (h.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    lib = _require_lib()
+    global _launches
+    _launches += 1
+    q = torch.empty((g2.shape[0], cols), dtype=FP8, device=gate.device)
+    rc = lib.bq_silu_mul_cast(g2.data_ptr(), u2.data_ptr(), code, g2.shape[0], cols,
+                              g2.stride(0), u2.stride(0), scale.data_ptr(), q.data_ptr(),
+                              _stream_ptr(gate.device))
+    _lib.check(rc, "silu_mul_cast")
+    return q.reshape(*gate.shape[:-1], cols)
 
 
 def sigmoid_gate_quant(o: torch.Tensor, gate: torch.Tensor,
@@ -597,7 +610,7 @@ def fp8_matmul(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight,
     if not xq.is_contiguous():
         xq = xq.contiguous()
     y = torch.empty((M, N), dtype=out_dtype, device=xq.device)
-    ws_ptr, ws_bytes = _gemm_scratch_for(xq.device, M, 1)
+    ws_ptr, ws_bytes = _take_slot(xq.device), 16
     rc = lib.bq_gemm_w8a8_residual(xq.data_ptr(), w.data.data_ptr(), sx.data_ptr(), w.scale.data_ptr(),
                                    residual.data_ptr(), residual.stride(0), y.data_ptr(), code,
                                    M, N, K, N, ws_ptr, ws_bytes, _stream_ptr(xq.device))
@@ -651,98 +664,11 @@ def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8
         yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
         Ns = (ctypes.c_int64 * n)(*[w.data.shape[0] for w in ws_])
         ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
-        ws_ptr, ws_bytes = _gemm_scratch_for(xq.device, M, n)
+        ws_ptr, ws_bytes = _take_slot(xq.device), 16
         rc = lib.bq_gemm_w8a8_grouped(xq.data_ptr(), sx.data_ptr(), M, K, n, wq, sw, yp, Ns, ld,
                                       code, ws_ptr, ws_bytes, stream)
         _lib.check(rc, "fp8_matmul")
     return outs
-
-
-_FUSE_LINEAR = False    # quantize-and-multiply in one launch: correct, but measured about 4.5 us
-                        # slower per call than the two-launch form with programmatic dependent launch
-
-
-def set_fused_linear(enable: bool) -> None:
-    """Switch the one-launch quantize-and-multiply form on or off (results are identical)."""
-    global _FUSE_LINEAR
-    _FUSE_LINEAR = bool(enable)
-
-
-def linear_fused(a: torch.Tensor, weights: Sequence[FP8Weight], *, mode: str = "plain",
-                 b: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                 out: Sequence[torch.Tensor] | None = None):
-    """Quantization of the activation and the grouped GEMM in ONE launch (M <= 256).
-
-    mode "plain": activation `a` `[M, K]`; "silu_mul": `quantize(F.silu(a) * b)`;
-    "sigmoid_gate": `quantize(a * sigmoid(b))` with `b` dense or the per-head `[M, H, D]` view.
-    Returns `(outs, codes, scale)`, or `None` when the shape is not eligible (the caller then
-    uses the separate kernels, which give the same bits).
-    """
-    if not _FUSE_LINEAR or _quantizers_off() or not a.is_cuda or a.dim() != 2:
-        return None
-    M, K = a.shape
-    if M == 0 or M > 256 or K % 16:
-        return None
-    code_in = _DTYPE_CODE.get(a.dtype)
-    out_dtype = a.dtype if out_dtype is None else out_dtype
-    code_out = _DTYPE_CODE.get(out_dtype)
-    if code_in is None or code_out is None or not weights:
-        return None
-    if len(weights) > _lib.BQ_MAX_SEGMENTS or any(not isinstance(w, FP8Weight) for w in weights):
-        return None
-    lib = _require_lib()
-    ld_a = ld_b = chunk = chunk_stride = 0
-    bptr, mcode, keep = 0, 1, None
-    if a.stride(1) != 1 or a.data_ptr() % 16:
-        return None
-    if mode == "plain":
-        if not a.is_contiguous():
-            return None
-        ld_a = K
-    elif mode == "silu_mul":
-        if b is None or b.shape != a.shape or b.dtype != a.dtype or b.stride(1) != 1:
-            return None
-        mcode, bptr, ld_a, ld_b = 2, b.data_ptr(), a.stride(0), b.stride(0)
-    elif mode == "sigmoid_gate":
-        if b is None or b.dtype != a.dtype:
-            return None
-        if b.dim() == 3 and b.shape[0] == M and b.shape[1] * b.shape[2] == K and b.stride(2) == 1:
-            chunk, chunk_stride, ld_b = b.shape[2], b.stride(1), b.stride(0)
-        elif b.shape == a.shape and b.stride(1) == 1:
-            chunk, chunk_stride, ld_b = K, 0, b.stride(0)
-        else:
-            return None
-        mcode, bptr, ld_a = 3, b.data_ptr(), a.stride(0)
-    else:
-        raise ValueError(f"unknown mode {mode!r}")
-    es = a.element_size()
-    if (ld_a * es) % 16 or (ld_b * es) % 16 or bptr % 16 or (chunk_stride * es) % 16 or chunk % 8:
-        return None
-    outs = []
-    for i, w in enumerate(weights):
-        if w.data.shape[1] != K or not w.data.is_contiguous():
-            return None
-        y = out[i] if out is not None else torch.empty((M, w.data.shape[0]), dtype=out_dtype,
-                                                       device=a.device)
-        if y.shape != (M, w.data.shape[0]) or y.dtype != out_dtype or y.stride(1) != 1:
-            raise ValueError(f"out[{i}] must be [{M}, {w.data.shape[0]}] {out_dtype}")
-        outs.append(y)
-    xq = torch.empty((M, K), dtype=FP8, device=a.device)
-    sx = torch.empty((1, 1), dtype=torch.float32, device=a.device)
-    n = len(weights)
-    wq = (ctypes.c_void_p * n)(*[w.data.data_ptr() for w in weights])
-    sw = (ctypes.c_void_p * n)(*[w.scale.data_ptr() for w in weights])
-    yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in outs])
-    Ns = (ctypes.c_int64 * n)(*[w.data.shape[0] for w in weights])
-    ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in outs])
-    rc = lib.bq_linear_w8a8_grouped(a.data_ptr(), bptr, mcode, code_in, M, K, ld_a, ld_b, chunk,
-                                    chunk_stride, xq.data_ptr(), sx.data_ptr(), n, wq, sw, yp, Ns, ld,
-                                    code_out, _take_slot(a.device), 32, _stream_ptr(a.device))
-    del keep
-    if rc == _lib.BQ_ERR_UNSUPPORTED:
-        return None
-    _lib.check(rc, "linear_fused")
-    return outs, xq, sx
 
 
 # A residual waiting for the output projection of a mixer: set by the caller of the mixer
@@ -788,11 +714,7 @@ def fp8_linear(x: torch.Tensor, w: FP8Weight, residual: torch.Tensor | None = No
     res2 = residual.reshape(-1, N) if residual is not None else _claim_residual(w, lead, N, x.dtype)
     if isinstance(x, QuantizedActivation):
         return fp8_matmul(x.q, x.scale, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
-    x2 = x.reshape(-1, K)
-    fused = linear_fused(x2, (w,)) if (x2.is_cuda and res2 is None) else None
-    if fused is not None:
-        return fused[0][0].reshape(*lead, N)
-    xq, sx = quantize_act(x2)
+    xq, sx = quantize_act(x.reshape(-1, K))
     return fp8_matmul(xq, sx, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
 
 
@@ -821,13 +743,8 @@ def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.T
     if pre is not None:
         ys = iter(fp8_matmul_grouped(pre.q, pre.scale, fp8, out_dtype=pre.dtype))
     else:
-        x2 = x.reshape(-1, K)
-        fused = linear_fused(x2, fp8) if x2.is_cuda else None
-        if fused is not None:
-            ys = iter(fused[0])
-        else:
-            xq, sx = quantize_act(x2)
-            ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
+        xq, sx = quantize_act(x.reshape(-1, K))
+        ys = iter(fp8_matmul_grouped(xq, sx, fp8, out_dtype=x.dtype))
     out = []
     for w in weights:
         if isinstance(w, FP8Weight):
@@ -996,7 +913,7 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     M = pre.q.shape[0] if pre is not None else x2.shape[0]
     I = gate_proj.shape[0]
     res2 = residual.reshape(-1, down_proj.shape[0]) if residual is not None else None
-    if _PAIR_MLP and M <= 256 and x.device.type == "cuda" and not _FUSE_LINEAR:
+    if _PAIR_MLP and M <= 256 and x.device.type == "cuda":
         xq, sx = (pre.q, pre.scale) if pre is not None else quantize_act(x2)
         paired = gate_up_silu_quant(xq, sx, gate_proj, up_proj, x.dtype)
         if paired is not None:
@@ -1005,35 +922,16 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
         pre = QuantizedActivation(xq, sx, x.shape, x.dtype)     # do not quantize twice
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     halves = (gu[:, :I], gu[:, I:])
-    if pre is not None:
-        fp8_matmul_grouped(pre.q, pre.scale, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
-    elif linear_fused(x2, (gate_proj, up_proj), out=halves) is None:
-        xq, sx = quantize_act(x2)
-        fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
-    fused = linear_fused(halves[0], (down_proj,), mode="silu_mul", b=halves[1]) if res2 is None else None
-    if fused is not None:
-        y = fused[0][0]
-    else:
-        hq, sh = silu_mul_quant(halves[0], halves[1])
-        y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype, residual=res2)
+    xq, sx = (pre.q, pre.scale) if pre is not None else quantize_act(x2)
+    fp8_matmul_grouped(xq, sx, (gate_proj, up_proj), out_dtype=x.dtype, out=halves)
+    hq, sh = silu_mul_quant(halves[0], halves[1])
+    y = fp8_matmul(hq, sh, down_proj, out_dtype=x.dtype, residual=res2)
     return y.reshape(*lead, down_proj.shape[0])
 
 
 def gated_output_projection(o: torch.Tensor, gate: torch.Tensor, o_proj: FP8Weight) -> torch.Tensor:
     """`linear(o * torch.sigmoid(gate), o_proj)` (braid/model/attention.py:215-216) in 2 launches."""
     *lead, K = o.shape
-    o2 = o.reshape(-1, K)
-    g = gate
-    if gate.dim() == o.dim() + 1:        # [..., H, D] per-head view -> [rows, H, D]
-        try:
-            g = gate.view(o2.shape[0], gate.shape[-2], gate.shape[-1])
-        except RuntimeError:
-            g = None
-    elif gate.shape == o.shape:
-        g = gate.reshape(-1, K)
-    fused = linear_fused(o2, (o_proj,), mode="sigmoid_gate", b=g) if g is not None else None
-    if fused is not None:
-        return fused[0][0].reshape(*lead, o_proj.shape[0])
     oq, so = sigmoid_gate_quant(o, gate)
     res2 = _claim_residual(o_proj, lead, o_proj.shape[0], o.dtype)
     return fp8_matmul(oq.reshape(-1, K), so, o_proj, out_dtype=o.dtype,

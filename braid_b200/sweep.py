@@ -207,24 +207,136 @@ def fp8_library_peak(dev, seconds=2.0):
             "fp8_tflops_sustained": fl / (sustained * 1e-3) / 1e12}
 
 
+def _read_phase_ring(lib):
+    import ctypes
+    import numpy as np
+    launches, ctas, words = 1024, 256, 10
+    buf = np.zeros(launches * ctas * words, dtype=np.uint64)
+    n = ctypes.c_int(0)
+    lib.bq_debug_read_phases.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+    rc = lib.bq_debug_read_phases(buf.ctypes.data, ctypes.byref(n))
+    if rc != 0:
+        raise RuntimeError(f"bq_debug_read_phases: status {rc}")
+    return buf.reshape(launches, ctas, words).astype(np.int64), int(n.value)
+
+
+def phase_tables(args, dev, peaks):
+    """Per-phase timing of the decode-regime kernels from a development build of the library
+    (`python -m braid_b200.build --phases`, loaded through BRAID_B200_LIB).  Every CTA stamps
+    %globaltimer at: 0 entry, 1 set-up done, 2 dependency wait returned (producer thread),
+    3 first weight tile landed (MMA thread), 4 accumulator complete, 5 staged in shared memory
+    and cluster barrier passed, 6 K slices reduced and stored, 7 exit.  Quantizer CTAs stamp
+    0, 2, 4 (amax exchanged) and 7.  Times are medians over the CTAs of a launch, in microseconds
+    from the launch's first CTA entry; `gap_prev` is entry minus the previous launch's last exit
+    (negative = the launches overlapped)."""
+    import numpy as np
+    from . import _lib
+    lib = _lib.load()
+    if not hasattr(lib, "bq_debug_phases"):
+        raise RuntimeError("this build of the library has no phase stamps: build with "
+                           "`python -m braid_b200.build --phases` and set BRAID_B200_LIB")
+    lib.bq_debug_phases.argtypes = [__import__("ctypes").c_int]
+
+    def run_chain(body):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        assert lib.bq_debug_phases(1) == 0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            body()
+        for _ in range(4):
+            graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ring, n = _read_phase_ring(lib)
+        lib.bq_debug_phases(0)
+        rows, prev_end, t_first = [], None, None
+        for i in range(min(n, ring.shape[0])):
+            meta = ring[i, 0, 9]
+            grid, kind = int(meta >> 8), int(meta & 0xFF)
+            c = ring[i, :min(grid, ring.shape[1])]
+            t0 = int(c[:, 0].min())
+            t_first = t0 if t_first is None else t_first
+            med = lambda k: (float(np.median(c[:, k][c[:, k] > 0])) - t0) / 1e3 if (c[:, k] > 0).any() else None  # noqa: E731
+            row = {"launch": i, "kind": "gemm" if kind == 0 else "quant", "grid": grid,
+                   "at_us": (t0 - t_first) / 1e3,
+                   "gap_prev_us": None if prev_end is None else (t0 - prev_end) / 1e3,
+                   "entry_spread_us": (int(c[:, 0].max()) - t0) / 1e3,
+                   "setup": med(1), "dep_wait_done": med(2), "first_tile": med(3),
+                   "accum_done": med(4), "staged": med(5), "reduced": med(6), "exit": med(7),
+                   "last_exit": (int(c[:, 7].max()) - t0) / 1e3}
+            prev_end = int(c[:, 7].max())
+            rows.append(row)
+        return rows, a.elapsed_time(b) * 1e3
+
+    out = []
+    for name in ("mlp.gate_up", "gdn.in_proj_qkv_z", "attn.qkv", "mlp.down", "gdn.out_proj"):
+        ns, k = PROJECTIONS[name]
+        for m in (16, 128):
+            bank = _bank(ns, k, dev, min_bytes=1 << 29, max_copies=8)
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            xq, sx = Q.quantize_act(x)
+            outs = [torch.empty((m, n), dtype=torch.bfloat16, device=dev) for n in ns]
+            rows, total = run_chain(lambda: [Q.fp8_matmul_grouped(xq, sx, bank[i % len(bank)], out=outs)
+                                             for i in range(6)])
+            keep = rows[2:]           # the first launches of a replay start from an idle GPU
+            avg = lambda key: float(np.mean([r[key] for r in keep if r[key] is not None]))  # noqa: E731
+            bytes_ = sum(ns) * k + m * k + 2 * m * sum(ns)
+            rec = {"phases": name, "M": m, "us_per_launch": total / 6, "launch": Q.last_gemm_launch(),
+                   "stream_floor_us": bytes_ / peaks["hbm_gbs"] / 1e3,
+                   **{key: avg(key) for key in ("gap_prev_us", "entry_spread_us", "setup", "dep_wait_done",
+                                                 "first_tile", "accum_done", "staged", "reduced", "exit",
+                                                 "last_exit")}}
+            out.append(rec)
+            print(json.dumps(rec), flush=True)
+            del bank
+            torch.cuda.empty_cache()
+    # the launch-by-launch timeline of four layers of the decode step (quantizers and GEMMs)
+    from .projection_set import ProjectionSet, StackShapes
+    ps = ProjectionSet(StackShapes(), args.rows, dev, seed=0, layers=4)
+    x = ps.x.clone()
+    rows, total = run_chain(lambda: ps.step_b200(x, bf16_gates=False))
+    for r in rows:
+        print(json.dumps({"timeline": r}), flush=True)
+    print(json.dumps({"timeline_total_us": total, "launches": len(rows)}), flush=True)
+    return out
+
+
 def main(args):
     import bench   # peaks reader lives with the benchmark
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     Q.warm_fused(True)
     peaks = bench.measured_peaks()
-    out_dir = Path(os.environ.get("BQ_SWEEP_OUT", "gpurun_out"))   # where sweep.json is written
-    out_dir.mkdir(exist_ok=True)
+    out_dir = Path(os.environ.get("BQ_SWEEP_OUT", "out"))   # where sweep.json is written
     rows = []
     only = getattr(args, "only", None)
     if only in ("rms_norm", "rms_norm_dense", "gated_rms_norm"):
         print(json.dumps(quant_row(only, args.rows, 4096, dev, peaks, reps=3)), flush=True)
         print(json.dumps({"device_status": Q.device_status()}), flush=True)
         return
+    if only == "phases":
+        phase_tables(args, dev, peaks)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
     if only == "mlp_block":
         # the whole quantized MLP of one layer at --rows (paired gate/up kernel + down): what the
         # ncu capture of the paired epilogue runs
         print(json.dumps(mlp_block_row(args.rows, dev, peaks, reps=3)), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
+    if only == "quant_plain":
+        # the plain quantizer at --rows x 4096 (the streaming kernel at prefill sizes): what the
+        # ncu capture of quant_stream_kernel runs
+        print(json.dumps(quant_row("plain", args.rows, 4096, dev, peaks, reps=3)), flush=True)
         print(json.dumps({"device_status": Q.device_status()}), flush=True)
         return
     if only == "norms":
@@ -277,5 +389,6 @@ def main(args):
             r = quant_row(kind, m, 4096, dev, peaks)
             rows.append(r)
             print(json.dumps(r), flush=True)
+    out_dir.mkdir(exist_ok=True)
     (out_dir / "sweep.json").write_text(json.dumps({"fp8_peak": peak8, "rows": rows}, indent=1))
     print(json.dumps({"device_status": Q.device_status()}), flush=True)

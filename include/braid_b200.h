@@ -121,6 +121,26 @@ int bq_silu_mul_quant(const void* gate, const void* up, int dtype, int64_t rows,
                       void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The two halves of bq_silu_mul_quant, for a column-parallel MLP whose ranks each
+ * hold a column shard of gate and up: bq_silu_mul_scale writes only the scale of
+ * the shard (pass 1 and the grid-wide exchange), the ranks combine their scales
+ * with a MAX all-reduce (the scale is a monotone function of the amax and max is
+ * exact, so the result is the scale of the whole intermediate), and
+ * bq_silu_mul_cast writes the shard's codes under that scale.  The codes equal,
+ * byte for byte, those a quantizer of the gathered intermediate would write.
+ *
+ * Replaces: the `quantize_act` inside `linear(h, down_proj)` of
+ * braid/model/mlp.py:48-49 when h is sharded over GPUs (the reference itself is
+ * single-GPU).  Arguments as bq_silu_mul_quant; `scale` is a device float that
+ * bq_silu_mul_cast only reads.  bq_silu_mul_cast needs no scratch.
+ */
+int bq_silu_mul_scale(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                      int64_t ld_gate, int64_t ld_up, float* scale_out, void* ws, size_t ws_bytes,
+                      void* stream);
+int bq_silu_mul_cast(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                     int64_t ld_gate, int64_t ld_up, const float* scale, void* q_out, void* stream);
+
+/*
  * o * sigmoid(gate) fused into the quantizer, h = bf16(o * bf16(sigmoid(gate))).
  * `gate` may be the strided per-head view the attention layer produces: element
  * (r, c) lives at gate[r*ld_gate + (c / chunk)*chunk_stride + (c % chunk)], so
@@ -183,19 +203,13 @@ int bq_gated_rmsnorm_quant(const void* y, int y_dtype, int64_t ld_y, const void*
                            size_t ws_bytes, void* stream);
 
 /*
- * Bytes of scratch the GEMM entry points can use for a problem of this size on
- * the current device.  16 bytes (just the status word) always work and select
- * the cluster kernel, which is the default; with the size returned here
- * (M <= 256) the experimental persistent weight-streaming kernel can be chosen
- * with bq_set_option("decode_kernel", ...); it keeps partial sums of row tiles
- * that straddle two SMs in this buffer.  Zero it once (cudaMemset); the kernels
- * leave it zeroed where it matters.  bq_gemm_workspace_bytes assumes the
- * largest group (BQ_MAX_SEGMENTS weights); bq_gemm_scratch_bytes takes the
- * actual number of weights per launch.  Launches that share a scratch buffer
- * must be ordered on one stream.
+ * Bytes of scratch the GEMM entry points need: 16 (the sticky status word and
+ * the counters of the paired / push epilogues).  Split-K partial sums travel
+ * through distributed shared memory and never reach global memory.  Zero the
+ * scratch once (cudaMemset); the kernels leave it zeroed where it matters.
+ * Launches that share a scratch slot must be ordered on one stream.
  */
 size_t bq_gemm_workspace_bytes(int64_t M, int64_t N_total, int64_t K);
-size_t bq_gemm_scratch_bytes(int64_t M, int n_seg);
 
 /*
  * Per-tensor W8A8 GEMM:  Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, fp32
@@ -348,36 +362,6 @@ int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, 
                          void* ws, size_t ws_bytes, void* stream);
 
 /*
- * Quantize-and-multiply in ONE launch (decode regime, M <= 256): the activation
- * quantizer of bq_quantize_act / bq_silu_mul_quant / bq_sigmoid_gate_quant runs
- * inside the weight-streaming GEMM kernel, on the warps that would otherwise
- * idle until the epilogue, while the producer warp is already streaming
- * weights.  Codes and scale are also written out (xq_out, sx_out), so they can
- * be reused.  Results are bit-identical to the separate calls.
- *
- * Replaces: braid/model/quant.py:244-252 (`fp8_linear`: quantize_act followed
- * by fp8_matmul), :260-286 (`project`), and the two halves of the quantized
- * MLP, braid/model/mlp.py:44-49.
- *
- *   mode 1: a = x [M,K] dense                      (b unused)
- *   mode 2: a = gate, b = up, row strides ld_a/ld_b (SiLU(a)*b, K = columns)
- *   mode 3: a = o (ld_a), b = gate (ld_b, chunk, chunk_stride as in
- *           bq_sigmoid_gate_quant)                  (a*sigmoid(b))
- *   xq_out  device, M*K bytes, 16-byte aligned; sx_out device, one float
- *   ws      32 bytes of scratch, zeroed once, self-resetting (5 words used)
- *
- * Returns BQ_ERR_UNSUPPORTED when the shape needs the prefill kernel (M > 256)
- * or the launch could not be made fully resident; call the separate entry
- * points in that case.
- */
-int bq_linear_w8a8_grouped(const void* a, const void* b, int mode, int act_dtype, int64_t M,
-                           int64_t K, int64_t ld_a, int64_t ld_b, int64_t chunk,
-                           int64_t chunk_stride, void* xq_out, float* sx_out, int n_seg,
-                           const void* const* wq, const float* const* sw, void* const* y,
-                           const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
-                           size_t ws_bytes, void* stream);
-
-/*
  * Copies the sticky device status word of a scratch buffer to the host
  * (synchronises `stream`; never call during capture).  0 means every bounded
  * device wait so far completed; otherwise BQ_ERR_DEVICE_WAIT.  The word is
@@ -387,8 +371,6 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
 
 /*
  * Tuning hooks used by the benchmark and tests; not needed for normal use.
- * bq_set_option("decode_kernel", v)     1 = cluster kernel (default), 0 = persistent kernel when the
- *                                       scratch allows, 2 = persistent kernel or BQ_ERR_WORKSPACE
  * bq_set_option("prefill_pair", 0/1)    prefill regime on CTA pairs (default 1)
  * bq_set_option("decode_split_k", v)    0 = heuristic, else force the K slices per tile
  * bq_set_option("decode_stages", v)     0 = heuristic, else cap the pipeline depth
@@ -403,7 +385,7 @@ int bq_set_option(const char* key, int64_t value);
 
 /*
  * Describes the launch the last GEMM call on this thread chose:
- * out[0]=kernel (0 cluster stream, 1 tile, 2 CTA-pair tile, 3 persistent stream) out[1]=grid out[2]=cluster/split
+ * out[0]=kernel (0 cluster stream, 1 tile, 2 CTA-pair tile) out[1]=grid out[2]=cluster/split
  * out[3]=stages out[4]=dynamic smem bytes out[5]=batch tile (MMA N)
  */
 int bq_last_gemm_launch(int64_t out[6]);

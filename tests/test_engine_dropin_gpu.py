@@ -103,6 +103,86 @@ def test_every_quant_group_captures_and_replays_identically(Q, ref_engine_env, q
         torch.cuda.empty_cache()
 
 
+# ---- the reference's group-wiring gates (tests/test_quant.py:264-358) on the random-init stack ----
+GROUP_NAMES = ("mlp", "attn", "gdn", "head")
+
+
+def _wired_engine(E, ckpt, quant, use_kernels):
+    E.activate()
+    return E.build_engine(ckpt, quant=quant, use_kernels=use_kernels)
+
+
+def _drop(eng):
+    del eng
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("group", GROUP_NAMES)
+def test_a_group_quantizes_itself_and_nothing_else(Q, ref_engine_env, group):
+    """tests/test_quant.py:264-283: asking for one group must not quantize a neighbour; `attn`
+    and `gdn` sit on alternating layers of the same stack."""
+    E, ckpt, use_kernels = ref_engine_env
+    eng = _wired_engine(E, ckpt, group, use_kernels)
+    try:
+        got = {g: [isinstance(w, Q.FP8Weight) for w in ws] for g, ws in eng._projections().items()}
+        assert all(len(v) for v in got.values()), "the random stack must hold every group"
+        assert all(got[group]) or group == "gdn", f"{group} was not quantized"
+        if group == "gdn":      # a and b are excluded by design; everything else in the group goes
+            assert sum(got["gdn"]) == len(got["gdn"]) * 3 // 5
+        for other in set(GROUP_NAMES) - {group}:
+            assert not any(got[other]), f"asking for {group} also quantized {other}"
+    finally:
+        E.deactivate()
+        _drop(eng)
+
+
+def test_gates_stay_bf16_and_the_embedding_is_never_quantized(Q, ref_engine_env):
+    """tests/test_quant.py:286-320: `in_proj_a` / `in_proj_b` stay bf16 even under "all";
+    `embed_tokens` is gathered per token and is never quantized."""
+    E, ckpt, use_kernels = ref_engine_env
+    eng = _wired_engine(E, ckpt, "all", use_kernels)
+    try:
+        gdn = [lyr.mixer for lyr in eng.layers if lyr.is_gdn]
+        assert gdn, "no linear-attention layers in this stack"
+        for m in gdn:
+            assert not isinstance(m.in_proj_a, Q.FP8Weight) and m.in_proj_a.dtype is torch.bfloat16
+            assert not isinstance(m.in_proj_b, Q.FP8Weight) and m.in_proj_b.dtype is torch.bfloat16
+            assert all(isinstance(w, Q.FP8Weight) for w in (m.in_proj_qkv, m.in_proj_z, m.out_proj))
+        assert isinstance(eng.embed_tokens, torch.Tensor) and eng.embed_tokens.dtype is torch.bfloat16
+        assert isinstance(eng.lm_head, Q.FP8Weight)
+    finally:
+        E.deactivate()
+        _drop(eng)
+
+
+def test_each_group_removes_its_own_bytes_and_the_report_states_the_result(Q, ref_engine_env):
+    """tests/test_quant.py:323-358: FP8 is worth exactly the bytes it removes from `step_bytes`,
+    group by group, and `quant_report` shows what WAS quantized (3 of 5 for gdn), not the request."""
+    E, ckpt, use_kernels = ref_engine_env
+    base = _wired_engine(E, ckpt, "", use_kernels)
+    want = base.step_bytes()
+    E.deactivate()
+    _drop(base)
+    for group in GROUP_NAMES:
+        eng = _wired_engine(E, ckpt, group, use_kernels)
+        try:
+            got = eng.step_bytes()
+            assert got[group] < want[group] * 0.75, f"{group}: {got[group]} vs bf16 {want[group]}"
+            for other in set(GROUP_NAMES) - {group}:
+                assert got[other] == want[other], f"{group} moved {other}'s bytes"
+            if group == "gdn":
+                rep = eng.quant_report()
+                assert "[on]" in rep and "[off]" in rep
+                line = next(x for x in rep.splitlines() if x.strip().startswith("gdn"))
+                n_q, n = line.split()[1].split("/")
+                assert int(n_q) == int(n) * 3 // 5, line
+                assert "active" in rep.splitlines()[-1]
+        finally:
+            E.deactivate()
+            _drop(eng)
+
+
 def _truncated(ckpt, layers):
     """The first `layers` layers of the shared checkpoint (same tensors, shorter schedule)."""
     import importlib

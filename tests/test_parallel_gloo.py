@@ -55,8 +55,26 @@ class _CpuOps:
     @staticmethod
     def fp8_matmul_grouped(xq, sx, weights, out_dtype=torch.bfloat16, out=None):
         # exact per-element sums in float64 so that a row slice equals the full product's slice
-        return [((xq.double() * sx.double()) @ (w.data.double() * w.scale.double()).t()).to(out_dtype)
-                for w in weights]
+        ys = [((xq.double() * sx.double()) @ (w.data.double() * w.scale.double()).t()).to(out_dtype)
+              for w in weights]
+        if out is not None:
+            for o, y in zip(out, ys):
+                o.copy_(y)
+            return list(out)
+        return ys
+
+    @staticmethod
+    def silu_mul_scale(gate, up):
+        import torch.nn.functional as F
+        from oracle import cpu_spelling as C
+        return C.quantize(F.silu(gate) * up)[1]
+
+    @staticmethod
+    def silu_mul_cast(gate, up, scale):
+        import torch.nn.functional as F
+        from oracle import cpu_spelling as C
+        h = F.silu(gate) * up
+        return (h.float() / scale).clamp(-C.FP8_MAX, C.FP8_MAX).to(C.FP8)
 
 
 def _worker(rank, world, port, hidden, inter, rows, ret):
@@ -73,8 +91,8 @@ def _worker(rank, world, port, hidden, inter, rows, ret):
         gate, up, down = mk(inter, hidden), mk(inter, hidden), mk(hidden, inter)
         x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
         mlp = ColumnParallelMLP(gate, up, down, group=None, ops=ops)
-        if rows >= 40:                      # exercise the chunked, overlapped form on CPU sizes
-            mlp.pipeline_rows, mlp.pipeline_from = 16, 32
+        if rows >= 40:                      # exercise the codes exchange (scale MAX all-reduce) on CPU sizes
+            mlp.codes_from = 32
         y = mlp(x.view(1, rows, hidden))
         # single-process reference with the same stand-in
         xq, sx = ops.quantize_act(x)

@@ -49,6 +49,48 @@ def test_ragged_small_and_streaming_sizes(Q, shape, dt):
     _assert_same(q, s, qr, sr, f"{dt} {shape}")
 
 
+@pytest.mark.parametrize("cols", [4096, 12288])
+def test_config_4_activations_on_the_streaming_kernel(Q, cols):
+    """BASELINE config 4: 16 packed sequences (M ~ 8192 rows) of width 4096 (layer input) and
+    12288 (MLP intermediate), far beyond what one co-resident grid can hold in registers."""
+    g = torch.Generator().manual_seed(4)
+    M = int(torch.randint(64, 1025, (16,), generator=g).sum())
+    x = randn_cpu((M, cols), seed=cols).cuda()
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    _assert_same(q, s, qr, sr, f"{M}x{cols}")
+    if cols == 12288:
+        gu = randn_cpu((M, 2 * cols), seed=7, scale=2.0).cuda()
+        q, s = Q.silu_mul_quant(gu[:, :cols], gu[:, cols:])
+        qr, sr = TS.quantize_act(TS.silu_mul(gu[:, :cols], gu[:, cols:]))
+        _assert_same(q, s, qr, sr, "silu_mul prologue at prefill size")
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", DTYPES, ids=DT_IDS)
+@pytest.mark.parametrize("shape", [(1, 64), (37, 1536), (128, 12288), (4096, 1536)])
+def test_scale_and_cast_halves_equal_the_whole_quantizer(Q, dt, shape):
+    """`silu_mul_scale` + `silu_mul_cast` (the column-parallel MLP's exchange) against
+    `silu_mul_quant`; and a shard cast under the scale of the whole tensor equals the matching
+    columns of the whole tensor's codes."""
+    M, I = shape
+    gu = randn_cpu((M, 2 * I), seed=M + I, dtype=dt, scale=2.0).cuda()
+    g_, u_ = gu[:, :I], gu[:, I:]
+    q, s = Q.silu_mul_quant(g_, u_)
+    s2 = Q.silu_mul_scale(g_, u_)
+    assert torch.equal(s, s2)
+    assert torch.equal(u8(Q.silu_mul_cast(g_, u_, s2)), u8(q))
+    if I % 32 == 0:
+        half = I // 2
+        shards = [(g_[:, :half], u_[:, :half]), (g_[:, half:], u_[:, half:])]
+        scales = torch.stack([Q.silu_mul_scale(a, b) for a, b in shards])
+        smax = scales.max().reshape(1, 1)
+        assert torch.equal(smax, s)
+        parts = [Q.silu_mul_cast(a, b, smax) for a, b in shards]
+        assert torch.equal(u8(torch.cat(parts, dim=1)), u8(q))
+    assert Q.device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(8, 4096), (37, 12288)])
 def test_matches_the_cpu_oracle_with_the_cuda_scale_spelling(Q, shape):
     x = randn_cpu(shape, seed=5, scale=3.5)
