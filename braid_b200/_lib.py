@@ -47,8 +47,8 @@ SIGNATURES = {
     "bq_gemm_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "bq_gemm_w8a8_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _int, _i64, _i64, _i64, _i64,
                                      _vp, _sz, _vp]),
-    "bq_gate_up_silu_quant_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp,
-                                          _vp, _sz, _vp]),
+    "bq_gate_up_silu_quant_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp,
+                                          _vp, _vp, _sz, _vp]),
     "bq_enable_peer_access": (_int, [_int]),
     "bq_peer_alloc": (_int, [_sz, ctypes.POINTER(_vp), _vp]),
     "bq_peer_free": (_int, [_vp]),
@@ -56,7 +56,7 @@ SIGNATURES = {
     "bq_peer_close": (_int, [_vp]),
     "bq_gemm_w8a8_push": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _int,
                                  ctypes.POINTER(_vp), _i64, ctypes.POINTER(_vp), _vp, _sz, _vp]),
-    "bq_gate_up_silu_push_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int,
+    "bq_gate_up_silu_push_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int,
                                          ctypes.POINTER(_vp), _i64, ctypes.POINTER(_vp), _vp, _sz, _vp]),
     "bq_wait_flag": (_int, [_vp, _vp, ctypes.c_uint, _vp, _vp]),
     "bq_quantize_act_after": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _vp, ctypes.c_uint, _vp, _sz, _vp]),
@@ -64,6 +64,10 @@ SIGNATURES = {
                                     ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                     ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
                                     _vp, _sz, _vp]),
+    "bq_project_mixed": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _int,
+                                ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_int),
+                                ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int,
+                                _vp, _sz, _vp]),
     "bq_read_device_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "bq_set_option": (_int, [ctypes.c_char_p, _i64]),
     "bq_last_gemm_launch": (_int, [ctypes.POINTER(_i64)]),

@@ -18,11 +18,12 @@
 //    one activation (q/k/v, qkv/z, gate/up) go in one launch, each segment with
 //    its own scale.
 //
-//  * gemm_tile_kernel (M > 256, the prefill regime; tensor-bound, judged in
-//    TFLOP/s).  Persistent, warp-specialised: one TMA producer warp, one MMA
-//    issuer warp, four epilogue warps; 128x256 output tiles; two 256-column
-//    accumulators in tensor memory so a tile's epilogue overlaps the next
-//    tile's main loop.
+//  * gemm_pair_kernel (M > 256, the prefill regime; tensor-bound, judged in
+//    TFLOP/s).  Persistent, warp-specialised CTA pairs (cta_group::2): one TMA
+//    producer warp, one MMA issuer warp, four epilogue warps; 256x256 output
+//    tiles; two 256-column accumulators in tensor memory so a tile's epilogue
+//    overlaps the next tile's main loop; the epilogue stages 128-byte row
+//    pieces in shared memory and hands them to TMA stores.
 //
 // Every mbarrier wait is bounded (ptx.cuh); a wait that runs out sets the sticky
 // status word and the CTA unwinds through the normal teardown.
@@ -48,6 +49,11 @@ constexpr int kUmmaK = 32;       // K elements one f8 MMA consumes
 constexpr int kRowTile = 128;    // MMA M
 constexpr int kATileBytes = kRowTile * kBK;   // 16 KiB
 constexpr int kMaxSmem = 232448;              // 227 KiB opt-in limit per CTA
+#ifndef BQ_STREAM_THREADS
+#define BQ_STREAM_THREADS 384
+#endif
+constexpr int kStreamThreads = BQ_STREAM_THREADS;   // weight-streaming kernel: warps 0 / 1 load and
+constexpr int kStreamWarps = kStreamThreads / 32;   // issue MMAs, ALL warps run the epilogue
 constexpr int kBarrierBytes = 1024;           // mbarriers + tmem slot + flags
 
 struct Segment {
@@ -58,6 +64,9 @@ struct Segment {
                        // the output has been rounded to that type (two roundings, as the separate
                        // GEMM and add kernels give)
   long long ld_res;
+  int dense;           // stream kernel: 1 = a 16-bit (bf16 / fp16) weight multiplied with the
+                       // unquantized activation (kind::f16 MMA, no scales), 0 = e4m3 weight
+  int y_tma;           // pair kernel: the output can be described to TMA (16-byte aligned base and pitch)
   int n;               // weight rows (output columns) of this segment
   int tile_begin;      // tile kernel: index of the segment's first tile
   int split;           // stream kernel: K slices of this weight (1, 2, 4 or 8)
@@ -65,10 +74,14 @@ struct Segment {
   int cluster_begin;   // stream kernel: index of the segment's first cluster
 };
 
-// SiLU(gate)*up and the quantization of the product, done in the epilogue of ONE GEMM over a
-// weight whose row tiles interleave 64 gate rows with the 64 up rows of the same columns.
+// SiLU(gate)*up and the quantization of the product, done in the epilogue of ONE GEMM whose
+// 128-row MMA tiles are put together from 64 gate rows and the 64 up rows of the same output
+// columns -- two TMA boxes per pipeline stage, read from the two weights where they lie (the
+// reference keeps gate_proj and up_proj as two tensors, braid/model/mlp.py:27-29; nothing is
+// repacked or copied).
 struct PairSilu {
   int on;
+  const void* wq_up;       // device: the up weight [I, K] (segment 0's weight pointer is the gate weight)
   const float* sw_up;      // device: dequant scale of the up half (seg.sw is the gate half's)
   uint8_t* hq;             // device: e4m3 codes of h, [M, ld_hq]
   long long ld_hq;
@@ -100,6 +113,8 @@ struct GemmParams {
   int M;               // activation rows
   int mma_n;           // stream kernel: padded batch = MMA N (multiple of 16)
   int k_blocks;        // ceil(K / 128)
+  int k_blocks_dense;  // stream kernel: 128-byte K blocks of a 16-bit row, ceil(2K / 128)
+  int dense_fmt;       // stream kernel: tcgen05 operand format of the 16-bit segments (0 f16, 1 bf16)
   int cluster;         // stream kernel: CTAs per cluster = largest split of the launch
   int stages;
   int out_dtype;
@@ -204,8 +219,10 @@ __device__ __forceinline__ float4 add_res4(float4 v, uint4 raw, int out_dtype) {
 template <int SPLIT, bool RES>
 __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
   // rows in flight per thread (half as many when residual values are held as well)
-  constexpr int kRows = (RES && SPLIT < 8) ? 8 / SPLIT : 16 / SPLIT;
-  constexpr int kWarps = 8;
+  constexpr int kRows = ((RES && SPLIT < 8) ? 8 / SPLIT : 16 / SPLIT) > (kStreamWarps > 8 ? 2 : 1)
+                            ? ((RES && SPLIT < 8) ? 8 / SPLIT : 16 / SPLIT) / (kStreamWarps > 8 ? 2 : 1)
+                            : 1;
+  constexpr int kWarps = kStreamWarps;
   const int n4 = e.lane * 4;                 // 4 consecutive output columns
   for (int m0 = e.m_begin + e.warp; m0 < e.m_end; m0 += kWarps * kRows) {
     float4 v[kRows][SPLIT];
@@ -268,8 +285,10 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
 template <int SPLIT, typename T>
 __device__ __forceinline__ float silu_pair_rows(const EpilogueArgs& e, float scale_up, float* part_rw) {
   using namespace bq::qd;
-  constexpr int kRows = (SPLIT < 8) ? 8 / SPLIT : 1;
-  constexpr int kWarps = 8;
+  constexpr int kRows = ((SPLIT < 8) ? 8 / SPLIT : 1) > (kStreamWarps > 8 ? 2 : 1)
+                            ? ((SPLIT < 8) ? 8 / SPLIT : 1) / (kStreamWarps > 8 ? 2 : 1)
+                            : 1;
+  constexpr int kWarps = kStreamWarps;
   const int n4 = e.lane * 4;
   const bool up_half = e.lane >= 16;
   const float sc = up_half ? scale_up : e.scale;
@@ -329,7 +348,7 @@ __device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const floa
                                                uint8_t* hq, long long ld_hq, int col0) {
   using namespace bq::qd;
   const int hcol = (e.lane & 15) * 4 + (e.lane >= 16 ? 2 : 0);
-  for (int m = e.m_begin + e.warp; m < e.m_end; m += 8) {
+  for (int m = e.m_begin + e.warp; m < e.m_end; m += kStreamWarps) {
     const T* hrow = reinterpret_cast<const T*>(part + m * kRowTile);
     const float2 f = make_float2(quant_one(widen(hrow[hcol]), sc), quant_one(widen(hrow[hcol + 1]), sc));
     const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
@@ -348,8 +367,8 @@ __device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const floa
 #ifndef BQ_STREAM_MIN_CTAS
 #define BQ_STREAM_MIN_CTAS 2
 #endif
-__global__ void __launch_bounds__(256, BQ_STREAM_MIN_CTAS)
-gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
+__global__ void __launch_bounds__(kStreamThreads, BQ_STREAM_MIN_CTAS)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xd,
                    const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p,
                    const int smem_tile_bytes) {
   extern __shared__ uint8_t smem_dyn[];
@@ -366,7 +385,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   volatile uint32_t* const tmem_slot =
       reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
-  float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // 8 floats
+  float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // one float per warp
 
   if (threadIdx.x == 0) { BQ_STAMP(p, 0); BQ_STAMP_META(p, 0); }
   pdl_launch_dependents();   // the next kernel may start its own set-up right away
@@ -389,7 +408,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   const bool active = row0 < seg.n;             // padding CTAs only keep the cluster barriers
 
   // this CTA's K slice, balanced to within one block
-  const int kb_base = p.k_blocks / split, kb_rem = p.k_blocks % split;
+  // a 16-bit segment (a weight the reference keeps unquantized) walks 128-byte K blocks of
+  // 64 elements over the dense activation; everything else about the pipeline is the same
+  const bool dense = seg.dense != 0;
+  const int seg_k_blocks = dense ? p.k_blocks_dense : p.k_blocks;
+  const CUtensorMap* const x_map = dense ? &tm_xd : &tm_x;
+  const int kb_base = seg_k_blocks / split, kb_rem = seg_k_blocks % split;
   const int kb_count = active ? kb_base + (krank < kb_rem ? 1 : 0) : 0;
   const int kb_begin = krank * kb_base + (krank < kb_rem ? krank : kb_rem);
 
@@ -397,8 +421,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   while (tmem_cols < static_cast<uint32_t>(p.mma_n)) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(x_map);
     tma_prefetch_desc(&tm_w.w[sg]);
+    if (p.pair.on) tma_prefetch_desc(&tm_w.w[1]);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -432,15 +457,26 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
       // Weights do not depend on any earlier kernel: fill the pipeline with them
       // first, and only then wait for the kernel that produces the activation.
       const int prefill = kb_count < p.stages ? kb_count : p.stages;
+      // one 128-row box, or (paired gate/up) two 64-row boxes from the two weights
+      const bool paired = p.pair.on != 0;
+      const int half_row0 = tile_in_seg * (kRowTile / 2);
+      auto load_w = [&](int slot, int kx) {
+        const uint32_t dst = a_base + slot * kATileBytes;
+        if (paired) {
+          tma_load_2d(dst, &tm_w.w[0], full_bar(slot), kx, half_row0, pol_w);
+          tma_load_2d(dst + kATileBytes / 2, &tm_w.w[1], full_bar(slot), kx, half_row0, pol_w);
+        } else {
+          tma_load_2d(dst, &tm_w.w[sg], full_bar(slot), kx, row0, pol_w);
+        }
+      };
       for (int i = 0; i < prefill; ++i) {
         mbar_expect_tx(full_bar(i), kATileBytes + b_tile_bytes);
-        tma_load_2d(a_base + i * kATileBytes, &tm_w.w[sg], full_bar(i), (kb_begin + i) * kBK, row0,
-                    pol_w);
+        load_w(i, (kb_begin + i) * kBK);
       }
       pdl_wait_prior_grids();
       BQ_STAMP(p, 2);
       for (int i = 0; i < prefill; ++i)
-        tma_load_2d(b_base + i * b_tile_bytes, &tm_x, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
+        tma_load_2d(b_base + i * b_tile_bytes, x_map, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
       for (int i = prefill; i < kb_count; ++i) {
         const int s = i % p.stages, use = i / p.stages;
         if (!mbar_wait(empty_bar(s), (use - 1) & 1)) {
@@ -449,14 +485,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         }
         mbar_expect_tx(full_bar(s), kATileBytes + b_tile_bytes);
         const int kx = (kb_begin + i) * kBK;
-        tma_load_2d(a_base + s * kATileBytes, &tm_w.w[sg], full_bar(s), kx, row0, pol_w);
-        tma_load_2d(b_base + s * b_tile_bytes, &tm_x, full_bar(s), kx, 0, pol_x);
+        load_w(s, kx);
+        tma_load_2d(b_base + s * b_tile_bytes, x_map, full_bar(s), kx, 0, pol_x);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (elect_one()) {
-      const uint32_t idesc = idesc_e4m3(kRowTile, p.mma_n);
+      const uint32_t idesc = dense ? idesc_f16(kRowTile, p.mma_n, p.dense_fmt)
+                                   : idesc_e4m3(kRowTile, p.mma_n);
       for (int i = 0; i < kb_count; ++i) {
         const int s = i % p.stages, use = i / p.stages;
         if (!mbar_wait(full_bar(s), use & 1)) {
@@ -469,8 +506,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
         const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
 #pragma unroll
         for (int j = 0; j < kBK / kUmmaK; ++j) {
-          // +32 bytes along K inside the swizzle span = +2 in descriptor units
-          mma_f8(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
+          // +32 bytes along K inside the swizzle span = +2 in descriptor units (32 e4m3 or 16
+          // 16-bit elements: one MMA's K either way)
+          if (dense) mma_f16(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
+          else mma_f8(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
         }
         mma_commit(empty_bar(s));   // stage is free once these MMAs retire
       }
@@ -483,8 +522,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
   pdl_wait_prior_grids();   // scales are read and outputs written only after this
   // the epilogue warps get here at once and have the scale ready long before
   // the accumulator is
-  const float sw = __ldg(seg.sw);
-  const float sx_ready = __ldg(p.sx);
+  const float sw = dense ? 1.0f : __ldg(seg.sw);
+  const float sx_ready = dense ? 1.0f : __ldg(p.sx);
   bool ok = mbar_wait(accum_bar, 0);
   tc_fence_after();
   if (threadIdx.x == 0) BQ_STAMP(p, 4);
@@ -499,7 +538,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     const int quad = warp & 3;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const int n_local = quad * 32 + lane;
-    for (int c = (warp >> 2) * 16; c < p.mma_n; c += 32) {
+    for (int c = (warp >> 2) * 16; c < p.mma_n; c += 4 * kStreamWarps) {
       uint32_t r[16];
       tmem_ld16(lane_addr + c, r);
       tmem_ld_wait();
@@ -565,7 +604,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     if (ok) {
       const int col0 = tile_in_seg * (kRowTile / 2);
       const int hcol = (lane & 15) * 4 + (lane >= 16 ? 2 : 0);
-      for (int m = m_begin + warp; m < m_end; m += 8) {
+      for (int m = m_begin + warp; m < m_end; m += kStreamWarps) {
         const long long at = static_cast<long long>(m) * p.push.ld + col0 + hcol;
         if (p.out_dtype == BQ_DTYPE_F32) {
           const float2 v = *reinterpret_cast<const float2*>(part + m * kRowTile + hcol);
@@ -590,7 +629,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x,
     if (threadIdx.x == 0) {
       float w = s_quant[0];
 #pragma unroll
-      for (int i = 1; i < 8; ++i) w = nan_max(w, s_quant[i]);
+      for (int i = 1; i < kStreamWarps; ++i) w = nan_max(w, s_quant[i]);
       unsigned int* const words = p.pair.words;
       if (p.pair.expected > 1) {
         // an aborted CTA still arrives (with 0), so the others are not left waiting
@@ -679,151 +718,6 @@ __global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, u
 }
 
 // ---------------------------------------------------------------------------
-// Persistent tile kernel (prefill regime)
-// ---------------------------------------------------------------------------
-constexpr int kTileN = 256;                       // MMA N = weight rows per tile
-constexpr int kBTileBytesBig = kTileN * kBK;      // 32 KiB
-constexpr int kStageBytesBig = kATileBytes + kBTileBytesBig;
-constexpr int kStagesBig = 4;
-constexpr int kTileThreads = 192;
-
-__global__ void __launch_bounds__(kTileThreads, 1)
-gemm_tile_kernel(const __grid_constant__ CUtensorMap tm_x,
-                 const __grid_constant__ WeightMaps tm_w, const GemmParams p) {
-  extern __shared__ uint8_t smem_dyn[];
-  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-  const uint32_t bar_base = base + kStagesBig * kStageBytesBig;
-  auto a_tile = [&](int s) { return base + s * kStageBytesBig; };
-  auto b_tile = [&](int s) { return base + s * kStageBytesBig + kATileBytes; };
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStagesBig + s); };
-  auto acc_full = [&](int b) { return bar_base + 8u * (2 * kStagesBig + b); };
-  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kStagesBig + 2 + b); };
-  volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(
-      base_ptr + kStagesBig * kStageBytesBig + 8 * (2 * kStagesBig + 4));
-  volatile uint32_t* const abort_flag = tmem_slot + 1;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tm_x);
-    for (int i = 0; i < p.n_seg; ++i) tma_prefetch_desc(&tm_w.w[i]);
-    for (int s = 0; s < kStagesBig; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);     // one arrival per epilogue warp
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  pdl_launch_dependents();
-  pdl_wait_prior_grids();   // the activation codes and scales come from the previous kernel
-
-  if (warp == 0) {
-    if (elect_one()) {
-      const uint64_t pol = policy_evict_last();   // both operands are re-read by other tiles
-      int it = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const int sg = find_segment(p, t);
-        const int local = t - p.seg[sg].tile_begin;
-        const int m0 = (local % p.m_tiles) * kRowTile;
-        const int n0 = (local / p.m_tiles) * kTileN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const int s = it % kStagesBig, use = it / kStagesBig;
-          if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), kStageBytesBig);
-          tma_load_2d(a_tile(s), &tm_x, full_bar(s), kb * kBK, m0, pol);
-          tma_load_2d(b_tile(s), &tm_w.w[sg], full_bar(s), kb * kBK, n0, pol);
-        }
-      }
-      if (!ok) *abort_flag = 1;
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (elect_one()) {
-      const uint32_t idesc = idesc_e4m3(kRowTile, kTileN);
-      int it = 0, tile_iter = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tile_iter) {
-        const int b = tile_iter & 1, use_b = tile_iter >> 1;
-        if (use_b > 0 && !mbar_wait(acc_empty(b), (use_b - 1) & 1)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + b * kTileN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const int s = it % kStagesBig, use = it / kStagesBig;
-          if (!mbar_wait(full_bar(s), use & 1)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t da = smem_desc_sw128(a_tile(s));
-          const uint64_t db = smem_desc_sw128(b_tile(s));
-#pragma unroll
-          for (int j = 0; j < kBK / kUmmaK; ++j)
-            mma_f8(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
-          mma_commit(empty_bar(s));
-        }
-        if (ok) mma_commit(acc_full(b));
-      }
-      if (!ok) *abort_flag = 1;
-    }
-    __syncwarp();
-  } else {
-    // epilogue warps 2..5; a warp may only touch TMEM lanes [32*(warp%4), +32)
-    const int quad = warp & 3;
-    int tile_iter = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      const int b = tile_iter & 1, use_b = tile_iter >> 1;
-      const int sg = find_segment(p, t);
-      const Segment seg = p.seg[sg];
-      const int local = t - seg.tile_begin;
-      const int m0 = (local % p.m_tiles) * kRowTile;
-      const int n0 = (local / p.m_tiles) * kTileN;
-      if (!mbar_wait(acc_full(b), use_b & 1)) { ok = false; break; }
-      tc_fence_after();
-      const float scale = __ldg(p.sx) * __ldg(seg.sw);
-      const int m = m0 + quad * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * kTileN;
-      for (int c = 0; c < kTileN; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c, r);          // warp-collective: no divergence before it
-        tmem_ld_wait();
-        if (m < p.M && (n0 + c) < seg.n) {
-          const long long idx = (long long)m * seg.ldy + n0 + c;
-#pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            float4 v = make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
-                                   __uint_as_float(r[j + 2]) * scale,
-                                   __uint_as_float(r[j + 3]) * scale);
-            store_out4(seg.y, idx + j, p.out_dtype, v);
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(b));
-    }
-    if (!ok) *abort_flag = 1;
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, (unsigned int)kErrDeviceWait);
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
-}
-
-// ---------------------------------------------------------------------------
 // Persistent tile kernel on CTA pairs (prefill regime, cta_group::2)
 // ---------------------------------------------------------------------------
 // Two CTAs on neighbouring SMs share one 256 x 256 output tile: each loads 128
@@ -831,15 +725,138 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tm_x,
 // lone CTA needs for 128 x 256), the leader issues one MMA that spans both SMs,
 // and each CTA keeps the accumulator of its own 128 rows in its tensor memory.
 // Shared-memory traffic per flop drops by a third, which is what limits the
-// single-CTA kernel.  Roles per CTA as in gemm_tile_kernel; the MMA warp works
-// in the leader only.
+// a lone CTA with a 128 x 256 tile.  Warp roles per CTA: 0 = TMA producer, 1 = MMA issuer
+// (leader CTA only), 2..5 = epilogue.
+//
+// Epilogue: a warp owns 32 rows of the CTA's 128 x 256 accumulator (its TMEM lane quarter).
+// It walks them in pieces of 128 bytes of output per row (64 columns of a 16-bit type, 32 of
+// fp32): tcgen05.ld -> scale -> cast -> one 32-row x 128-byte box in shared memory, written
+// in the 128-byte swizzle pattern so that neither the lane-per-row writes nor the reader
+// meet bank conflicts -> one TMA store of the box (clipped at M and N by the tensor map),
+// two boxes per warp in flight.  Outputs whose base or row pitch is not 16-byte aligned
+// cannot be described to TMA: the same staged box is then written with coalesced 128-byte
+// row segments by the warp itself.
 constexpr int kPairStageBytes = 2 * kATileBytes;    // 16 KB activation rows + 16 KB weight rows
 constexpr int kPairStages = 6;
 constexpr int kPairTile = 256;
+constexpr int kTileThreads = 192;
+constexpr int kStoreBoxBytes = 32 * 128;            // 32 rows x 128 bytes
+constexpr int kPairStagingBytes = 4 * 2 * kStoreBoxBytes;   // four epilogue warps, two boxes each
+
+// Order in which a weight's 256 x 256 tiles are visited: bands of kRasterM tile rows, inside a
+// band the row index runs fastest.  The ~74 tiles in flight at a time then cover about
+// 8 x 9 tiles -- (8 + 9) x 256 x K operand bytes, which stay in L2 for every K of the model --
+// instead of all tile rows of two or three tile columns (M x K activation bytes per wave:
+// 100 MB at M = 8192, K = 12288, more than L2 holds).
+constexpr int kRasterM = 8;
+__device__ __forceinline__ void pair_tile_coords(int local, int m_tiles, int n_tiles, int& m_idx,
+                                                 int& n_idx) {
+  const int band_tiles = kRasterM * n_tiles;      // every band but the last is full
+  const int band = local / band_tiles;
+  const int r = local - band * band_tiles;
+  const int m_begin = band * kRasterM;
+  const int height = (m_tiles - m_begin) < kRasterM ? (m_tiles - m_begin) : kRasterM;
+  n_idx = r / height;
+  m_idx = m_begin + (r - n_idx * height);
+}
+
+struct alignas(64) OutMaps {
+  CUtensorMap y[BQ_MAX_SEGMENTS];
+};
+
+// 16 accumulator values -> scaled, cast to the output type, as 16-byte pieces.
+template <int ES>
+__device__ __forceinline__ void cast16(const uint32_t (&r)[16], float scale, int out_dtype,
+                                       uint4 (&out)[ES == 4 ? 4 : 2]) {
+  if constexpr (ES == 4) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      out[q] = make_uint4(__float_as_uint(__uint_as_float(r[4 * q]) * scale),
+                          __float_as_uint(__uint_as_float(r[4 * q + 1]) * scale),
+                          __float_as_uint(__uint_as_float(r[4 * q + 2]) * scale),
+                          __float_as_uint(__uint_as_float(r[4 * q + 3]) * scale));
+  } else {
+    uint32_t w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float a = __uint_as_float(r[2 * q]) * scale, b = __uint_as_float(r[2 * q + 1]) * scale;
+      if (out_dtype == BQ_DTYPE_BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        w[q] = *reinterpret_cast<const uint32_t*>(&v);
+      } else {
+        const __half2 v = __floats2half2_rn(a, b);
+        w[q] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    }
+    out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// The epilogue of one warp for one tile: 32 rows x 256 columns.
+template <int ES>
+__device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Segment& seg,
+                                                   const CUtensorMap* ymap, bool use_tma,
+                                                   uint32_t taddr, float scale, int m_row0, int n0,
+                                                   uint8_t* stage, uint32_t stage_addr, int lane,
+                                                   int& box_iter) {
+  constexpr int kCols = 128 / ES;              // output columns per 128-byte piece
+  constexpr int kPieces = ES == 4 ? 4 : 2;     // 16-byte pieces per 16 accumulator columns
+  for (int c = 0; c < kPairTile; c += kCols, ++box_iter) {
+    // pieces beyond this weight's rows are never stored (warp-uniform).  They must not take a
+    // box either: the wait below counts committed stores, one per box in use.
+    if ((n0 + c) >= seg.n) break;
+    const int buf = box_iter & 1;
+    uint8_t* const box = stage + buf * kStoreBoxBytes;
+    // the TMA store that read this box two pieces ago must have finished reading it
+    if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < kCols; j += 16) {
+      uint32_t r[16];
+      tmem_ld16(taddr + c + j, r);          // warp-collective: no divergence before it
+      tmem_ld_wait();
+      uint4 v[kPieces];
+      cast16<ES>(r, scale, p.out_dtype, v);
+#pragma unroll
+      for (int q = 0; q < kPieces; ++q) {
+        const int piece = (j * ES) / 16 + q;                  // 0..7 along the 128-byte row
+        *reinterpret_cast<uint4*>(box + lane * 128 + ((piece ^ (lane & 7)) << 4)) = v[q];
+      }
+    }
+    if (use_tma) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(ymap, stage_addr + buf * kStoreBoxBytes, n0 + c, m_row0);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    } else {
+      __syncwarp();
+      // 8 lanes cover one 128-byte row segment, 4 rows per pass
+      const int piece = lane & 7;
+      const int col = n0 + c + piece * (16 / ES);
+#pragma unroll
+      for (int pass = 0; pass < 8; ++pass) {
+        const int row = pass * 4 + (lane >> 3);
+        const int m = m_row0 + row;
+        const uint4 v = *reinterpret_cast<const uint4*>(box + row * 128 + ((piece ^ (row & 7)) << 4));
+        if (m < p.M && col < seg.n) {         // n is a multiple of 16: a piece is in or out as a whole
+          uint8_t* dst = static_cast<uint8_t*>(seg.y) + ((long long)m * seg.ldy + col) * ES;
+          // rows are 8-byte aligned at least (checked by the host)
+          *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+          *reinterpret_cast<uint2*>(dst + 8) = make_uint2(v.z, v.w);
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kTileThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
-                 const __grid_constant__ WeightMaps tm_w, const __grid_constant__ GemmParams p) {
+                 const __grid_constant__ WeightMaps tm_w, const __grid_constant__ OutMaps tm_y,
+                 const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* const base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
@@ -853,6 +870,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
   volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(
       base_ptr + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
+  // store boxes of the epilogue warps, after the barrier block (1024-byte aligned: the swizzle
+  // pattern of a box is a function of its address bits)
+  uint8_t* const staging = base_ptr + kPairStages * kPairStageBytes + kBarrierBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
@@ -892,8 +912,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
       for (int t = pair; t < p.total_tiles && ok; t += n_pairs) {
         const int sg = find_segment(p, t);
         const int local = t - p.seg[sg].tile_begin;
-        const int m0 = (local % m_tiles) * kPairTile + rank * kRowTile;
-        const int n0 = (local / m_tiles) * kPairTile + rank * kRowTile;
+        int m_idx, n_idx;
+        pair_tile_coords(local, m_tiles, (p.seg[sg].n + kPairTile - 1) / kPairTile, m_idx, n_idx);
+        const int m0 = m_idx * kPairTile + rank * kRowTile;
+        const int n0 = n_idx * kPairTile + rank * kRowTile;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kPairStages, use = it / kPairStages;
           if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
@@ -938,8 +960,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    int tile_iter = 0;
+    int tile_iter = 0, box_iter = 0;
     bool ok = true;
+    uint8_t* const stage = staging + quad * 2 * kStoreBoxBytes;
+    const uint32_t stage_addr = smem_u32(stage);
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty(0), 0);
     const uint32_t leader_acc_empty1 = map_to_cta(acc_empty(1), 0);
     for (int t = pair; t < p.total_tiles && ok; t += n_pairs, ++tile_iter) {
@@ -947,32 +971,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
       const int sg = find_segment(p, t);
       const Segment seg = p.seg[sg];
       const int local = t - seg.tile_begin;
-      const int m0 = (local % m_tiles) * kPairTile + rank * kRowTile;
-      const int n0 = (local / m_tiles) * kPairTile;
+      int m_idx, n_idx;
+      pair_tile_coords(local, m_tiles, (seg.n + kPairTile - 1) / kPairTile, m_idx, n_idx);
+      const int m0 = m_idx * kPairTile + rank * kRowTile;
+      const int n0 = n_idx * kPairTile;
       if (!mbar_wait(acc_full(b), use_b & 1)) { ok = false; break; }
       tc_fence_after();
       const float scale = __ldg(p.sx) * __ldg(seg.sw);
-      const int m = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * kPairTile;
-      for (int c = 0; c < kPairTile; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c, r);
-        tmem_ld_wait();
-        if (m < p.M && (n0 + c) < seg.n) {
-          const long long idx = (long long)m * seg.ldy + n0 + c;
-#pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            float4 v = make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
-                                   __uint_as_float(r[j + 2]) * scale,
-                                   __uint_as_float(r[j + 3]) * scale);
-            store_out4(seg.y, idx + j, p.out_dtype, v);
-          }
-        }
-      }
+      const bool use_tma = seg.y_tma != 0;
+      if (p.out_dtype == BQ_DTYPE_F32)
+        pair_epilogue_rows<4>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, m0 + quad * 32, n0, stage,
+                              stage_addr, lane, box_iter);
+      else
+        pair_epilogue_rows<2>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, m0 + quad * 32, n0, stage,
+                              stage_addr, lane, box_iter);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(b == 0 ? leader_acc_empty0 : leader_acc_empty1);
     }
+    // the boxes must stay valid until the last stores have read them
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
     if (!ok) *abort_flag = 1;
   }
 
@@ -1021,6 +1041,25 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, int
   return rc == CUDA_SUCCESS ? kOk : kErrUnsupported;
 }
 
+// [M, N] output of the prefill kernel, row pitch ldy elements: boxes of 32 rows x 128 bytes,
+// 128-byte swizzle; rows beyond M and columns beyond N are clipped by the store.
+int make_out_map(CUtensorMap* out, void* ptr, long long M, long long N, long long ldy, int out_dtype) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return kErrNoDriver;
+  const cuuint64_t es = out_dtype == BQ_DTYPE_F32 ? 4 : 2;
+  const CUtensorMapDataType dt = out_dtype == BQ_DTYPE_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : out_dtype == BQ_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldy * es};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(out, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? kOk : kErrUnsupported;
+}
+
 int device_sms() {
   static int sms[64] = {0};
   int dev = 0;
@@ -1036,7 +1075,6 @@ int device_sms() {
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
-long long g_opt_pair = 1;       // prefill regime on CTA pairs (cta_group::2)
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -1046,11 +1084,9 @@ int configure_once() {
   if (rc < 0) {
     cudaError_t e1 = cudaFuncSetAttribute(gemm_stream_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    cudaError_t e2 = cudaFuncSetAttribute(gemm_tile_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     cudaError_t e3 = cudaFuncSetAttribute(gemm_pair_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    rc = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? kOk : kErrLaunch;
+    rc = (e1 == cudaSuccess && e3 == cudaSuccess) ? kOk : kErrLaunch;
     if (rc != kOk) (void)cudaGetLastError();
   }
   return rc;
@@ -1067,7 +1103,7 @@ int max_resident_ctas(int cluster, int smem) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)(cluster * 64), 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.blockDim = dim3(kStreamThreads, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1093,7 +1129,7 @@ int max_resident_ctas(int cluster, int smem) {
   else
     (void)cudaGetLastError();
   int per_sm = 233472 / (smem + 1024);
-  const int by_regs = 65536 / (((regs + 7) / 8) * 8 * 256);
+  const int by_regs = 65536 / (((regs + 7) / 8) * 8 * kStreamThreads);
   if (per_sm > by_regs) per_sm = by_regs;
   if (per_sm > 2) per_sm = 2;
   if (per_sm < 1) per_sm = 1;
@@ -1124,8 +1160,8 @@ int split_for_weight(long long n_rows, int k_blocks) {
   return s;
 }
 
-int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p,
-                  cudaStream_t stream) {
+int launch_stream(const CUtensorMap& tm_x, const CUtensorMap& tm_xd, const WeightMaps& maps,
+                  GemmParams& p, cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return kErrLaunch;
   p.mma_n = ((p.M + 15) / 16) * 16;
@@ -1134,7 +1170,8 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   int cluster = 1, min_split = 8;
   for (int i = 0; i < p.n_seg; ++i) {
     p.seg[i].split = p.seg[i].split_forced > 0 ? p.seg[i].split_forced
-                                               : split_for_weight(p.seg[i].n, p.k_blocks);
+                                               : split_for_weight(p.seg[i].n, p.seg[i].dense ? p.k_blocks_dense
+                                                                                             : p.k_blocks);
     if (p.seg[i].split > cluster) cluster = p.seg[i].split;
     if (p.seg[i].split < min_split) min_split = p.seg[i].split;
   }
@@ -1148,7 +1185,12 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   }
   const long long grid = (long long)clusters * cluster;
   if (grid > 0x7fffffffLL) return kErrTooLarge;
-  const int kb_max = (p.k_blocks + min_split - 1) / min_split;
+  int kb_max = (p.k_blocks + min_split - 1) / min_split;
+  for (int i = 0; i < p.n_seg; ++i)
+    if (p.seg[i].dense) {
+      const int kb = (p.k_blocks_dense + p.seg[i].split - 1) / p.seg[i].split;
+      if (kb > kb_max) kb_max = kb;
+    }
   const int staging = p.mma_n * kRowTile * 4;
   // Shared memory per CTA: small enough that the whole grid is resident at once
   // (up to 2 CTAs per SM: 256 threads x ~128 registers each), so one CTA's
@@ -1185,7 +1227,7 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.blockDim = dim3(kStreamThreads, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1202,38 +1244,18 @@ int launch_stream(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p
 #ifdef BQ_PHASES
   p.phase_ring = bq::phase_ring_for_launch(&p.phase_seq);
 #endif
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, maps, p, tile_bytes);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel, tm_x, tm_xd, maps, p, tile_bytes);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
 }
 
-int launch_tile(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, const OutMaps& ymaps, GemmParams& p,
+                cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return kErrLaunch;
-  const int smem = kStagesBig * kStageBytesBig + kBarrierBytes + 1024;
-  int grid = p.total_tiles < sms ? p.total_tiles : sms;
-  g_last_launch[0] = 1; g_last_launch[1] = grid; g_last_launch[2] = 1;
-  g_last_launch[3] = kStagesBig; g_last_launch[4] = smem; g_last_launch[5] = kTileN;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kTileThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = g_opt_pdl ? 1 : 0;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tile_kernel, tm_x, maps, p);
-  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
-  return kOk;
-}
-
-int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, cudaStream_t stream) {
-  const int sms = device_sms();
-  if (sms <= 0) return kErrLaunch;
-  const int smem = kPairStages * kPairStageBytes + kBarrierBytes + 1024;
+  const int smem = kPairStages * kPairStageBytes + kBarrierBytes + kPairStagingBytes + 1024;
+  static_assert(kPairStages * kPairStageBytes + kBarrierBytes + kPairStagingBytes + 1024 <= kMaxSmem,
+                "pair kernel: pipeline + store boxes exceed the shared memory of an SM");
   int pairs = p.total_tiles < sms / 2 ? p.total_tiles : sms / 2;
   if (pairs < 1) pairs = 1;
   g_last_launch[0] = 2; g_last_launch[1] = 2 * pairs; g_last_launch[2] = 2;
@@ -1253,7 +1275,7 @@ int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, GemmParams& p, 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_opt_pdl ? 2 : 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, tm_x, maps, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, tm_x, maps, ymaps, p);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
   return kOk;
 }
@@ -1268,7 +1290,6 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
-  if (strcmp(key, "prefill_pair") == 0) { g_opt_pair = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
     g_opt_cta_target = value;
@@ -1289,12 +1310,21 @@ extern "C" size_t bq_gemm_workspace_bytes(int64_t, int64_t, int64_t) {
 
 namespace {
 
+// Weights of a mixed launch that are NOT quantized: kind[i] != 0 marks segment i as a 16-bit
+// weight [N_i, K] of type `dtype`, multiplied with the unquantized activation `x` [M, K].
+struct DenseArgs {
+  const void* x;
+  int dtype;
+  const int* kind;
+};
+
 int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg,
                 const void* const* wq, const float* const* sw, void* const* y, const int64_t* N,
                 const int64_t* ldy, int out_dtype, void* ws, size_t ws_bytes, void* stream_v,
                 const void* const* res = nullptr,
                 const int64_t* ld_res = nullptr, const PairSilu* pair = nullptr,
-                int split_forced = 0, const PushParams* push = nullptr) {
+                int split_forced = 0, const PushParams* push = nullptr,
+                const DenseArgs* dn = nullptr) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
@@ -1304,7 +1334,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (M > 0x7fffff00LL || K > 0x7fffff00LL) return kErrTooLarge;
   const int out_align = out_dtype == BQ_DTYPE_F32 ? 16 : 8;
   for (int i = 0; i < n_seg; ++i) {   // argument checks first: no CUDA call before they pass
-    if (!wq[i] || !sw[i] || N[i] <= 0) return kErrBadArg;
+    const bool is_dense = dn != nullptr && dn->kind[i] != 0;
+    if (!wq[i] || (!sw[i] && !is_dense) || N[i] <= 0) return kErrBadArg;
     if (N[i] % 16 || !aligned_to(wq[i], 16)) return kErrUnsupported;
     if (pair == nullptr && push == nullptr) {   // the pair and push forms do not write y
       if (!y[i]) return kErrBadArg;
@@ -1313,6 +1344,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     if (N[i] > 0x7fffff00LL) return kErrTooLarge;
   }
   const bool stream_path = M <= g_opt_stream_max_m;
+  if (dn != nullptr) {    // 16-bit segments exist in the weight-streaming kernel only
+    if (!stream_path || pair || push || res) return kErrUnsupported;
+    if (!dn->x || (dn->dtype != BQ_DTYPE_BF16 && dn->dtype != BQ_DTYPE_F16)) return kErrBadArg;
+    if (!aligned_to(dn->x, 16)) return kErrUnsupported;
+  }
   if (pair && !stream_path) return kErrUnsupported;   // decode-regime form only
   if (pair && (res || n_seg != 1)) return kErrBadArg;
   if (push) {
@@ -1336,6 +1372,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   p.sx = sx;
   p.M = (int)M;
   p.k_blocks = (int)((K + kBK - 1) / kBK);
+  p.k_blocks_dense = (int)((2 * K + kBK - 1) / kBK);
+  p.dense_fmt = (dn != nullptr && dn->dtype == BQ_DTYPE_BF16) ? 1 : 0;
   p.out_dtype = out_dtype;
   // the sticky status word is the 4th word of the scratch, as in the quantizer
   p.status = static_cast<unsigned int*>(ws) + 3;
@@ -1349,10 +1387,12 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.push.done = static_cast<unsigned int*>(ws);   // first scratch word: zero between launches
   }
 
-  const bool pair_path = !stream_path && g_opt_pair != 0;
-  const int w_box_rows = (stream_path || pair_path) ? kRowTile : kTileN;
-  const int tile_n = pair_path ? kPairTile : w_box_rows;
+  const bool pair_path = !stream_path;
+  const int w_box_rows = kRowTile;
+  const int tile_n = pair_path ? kPairTile : kRowTile;
   p.m_tiles = pair_path ? (int)((M + kPairTile - 1) / kPairTile) : (int)((M + kRowTile - 1) / kRowTile);
+  OutMaps ymaps;
+  memset(&ymaps, 0, sizeof(ymaps));
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
@@ -1362,23 +1402,37 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.seg[i].res = res ? res[i] : nullptr;
     p.seg[i].ld_res = res ? ld_res[i] : 0;
     p.seg[i].n = (int)N[i];
+    p.seg[i].dense = (dn != nullptr && dn->kind[i] != 0) ? 1 : 0;
     p.seg[i].tile_begin = tiles;
     const long long nt = (N[i] + tile_n - 1) / tile_n;
     const long long add = stream_path ? nt : nt * p.m_tiles;
     if (tiles + add > 0x3fffffffLL) return kErrTooLarge;
     tiles += (int)add;
-    if (int rc = make_map(&maps.w[i], wq[i], N[i], K, w_box_rows)) return rc;
+    if (pair_path) {
+      const size_t es = out_dtype == BQ_DTYPE_F32 ? 4 : 2;
+      p.seg[i].y_tma = aligned_to(y[i], 16) && (ldy[i] * es) % 16 == 0 &&
+                       make_out_map(&ymaps.y[i], y[i], M, N[i], ldy[i], out_dtype) == kOk;
+    }
+    if (pair) {
+      // two maps over the two weights, 64-row boxes: the kernel puts a tile together from both
+      if (int rc = make_map(&maps.w[0], wq[0], N[0] / 2, K, kRowTile / 2)) return rc;
+      if (int rc = make_map(&maps.w[1], pair->wq_up, N[0] / 2, K, kRowTile / 2)) return rc;
+    } else if (int rc = make_map(&maps.w[i], wq[i], N[i], p.seg[i].dense ? 2 * K : K, w_box_rows)) {
+      return rc;     // a 16-bit weight is described by its bytes: [N, 2K]
+    }
   }
   p.total_tiles = tiles;
   CUtensorMap tm_x;
   if (stream_path) {
     const int mma_n = (int)(((M + 15) / 16) * 16);
     if (int rc = make_map(&tm_x, xq, M, K, mma_n)) return rc;
-    return launch_stream(tm_x, maps, p, stream);
+    CUtensorMap tm_xd = tm_x;
+    if (dn != nullptr)
+      if (int rc = make_map(&tm_xd, dn->x, M, 2 * K, mma_n)) return rc;
+    return launch_stream(tm_x, tm_xd, maps, p, stream);
   }
   if (int rc = make_map(&tm_x, xq, M, K, kRowTile)) return rc;
-  if (pair_path) return launch_pair(tm_x, maps, p, stream);
-  return launch_tile(tm_x, maps, p, stream);
+  return launch_pair(tm_x, maps, ymaps, p, stream);
 }
 
 }  // namespace
@@ -1388,6 +1442,22 @@ extern "C" int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, 
                                     const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
                                     size_t ws_bytes, void* stream_v) {
   return run_grouped(xq, sx, M, K, n_seg, wq, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v);
+}
+
+extern "C" int bq_project_mixed(const void* xq, const float* sx, const void* x_dense, int dense_dtype,
+                                int64_t M, int64_t K, int n_seg, const void* const* w,
+                                const float* const* sw, const int* kind, void* const* y,
+                                const int64_t* N, const int64_t* ldy, int out_dtype, void* ws,
+                                size_t ws_bytes, void* stream_v) {
+  if (kind == nullptr) return kErrBadArg;
+  bool any_dense = false;
+  for (int i = 0; i < n_seg && i < BQ_MAX_SEGMENTS; ++i) any_dense = any_dense || kind[i] != 0;
+  if (!any_dense)
+    return run_grouped(xq, sx, M, K, n_seg, w, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v);
+  if (out_dtype != dense_dtype) return kErrUnsupported;   // F.linear returns the activation's type
+  const DenseArgs dn{x_dense, dense_dtype, kind};
+  return run_grouped(xq, sx, M, K, n_seg, w, sw, y, N, ldy, out_dtype, ws, ws_bytes, stream_v,
+                     nullptr, nullptr, nullptr, 0, nullptr, &dn);
 }
 
 extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, const float* sw,
@@ -1402,19 +1472,21 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
                               stream);
 }
 
-extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_pair,
-                                          const float* sw_gate, const float* sw_up, int64_t M,
+extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_gate,
+                                          const void* wq_up, const float* sw_gate,
+                                          const float* sw_up, int64_t M,
                                           int64_t I, int64_t K, int act_dtype, void* hq_out,
                                           float* sh_out, void* ws, size_t ws_bytes, void* stream) {
-  if (!wq_pair || !sw_gate || !sw_up || !hq_out || !sh_out || I <= 0) return kErrBadArg;
-  if (I % (kRowTile / 2) || !aligned_to(hq_out, 2)) return kErrUnsupported;
+  if (!wq_gate || !wq_up || !sw_gate || !sw_up || !hq_out || !sh_out || I <= 0) return kErrBadArg;
+  if (I % (kRowTile / 2) || !aligned_to(hq_out, 2) || !aligned_to(wq_up, 16)) return kErrUnsupported;
   PairSilu pair;
   memset(&pair, 0, sizeof(pair));
+  pair.wq_up = wq_up;
   pair.sw_up = sw_up;
   pair.hq = static_cast<uint8_t*>(hq_out);
   pair.ld_hq = I;
   pair.sh = sh_out;
-  const void* wqs[1] = {wq_pair};
+  const void* wqs[1] = {wq_gate};
   const float* sws[1] = {sw_gate};
   void* ys[1] = {nullptr};
   const int64_t Ns[1] = {2 * I};
@@ -1461,20 +1533,22 @@ extern "C" int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx
                      nullptr, nullptr, nullptr, 0, &push);
 }
 
-extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
-                                         const float* sw_gate, const float* sw_up, int64_t M,
+extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_gate,
+                                         const void* wq_up, const float* sw_gate,
+                                         const float* sw_up, int64_t M,
                                          int64_t I, int64_t K, int act_dtype, int n_peers,
                                          void* const* h_dst, int64_t ld_h, void* const* flags,
                                          void* ws, size_t ws_bytes, void* stream) {
-  if (!wq_pair || !sw_gate || !sw_up || I <= 0) return kErrBadArg;
-  if (I % (kRowTile / 2)) return kErrUnsupported;
+  if (!wq_gate || !wq_up || !sw_gate || !sw_up || I <= 0) return kErrBadArg;
+  if (I % (kRowTile / 2) || !aligned_to(wq_up, 16)) return kErrUnsupported;
   PushParams push;
   if (int rc = fill_push(&push, n_peers, h_dst, ld_h, flags, I, act_dtype == BQ_DTYPE_F32 ? 8 : 4))
     return rc;
   PairSilu pair;
   memset(&pair, 0, sizeof(pair));
+  pair.wq_up = wq_up;
   pair.sw_up = sw_up;
-  const void* wqs[1] = {wq_pair};
+  const void* wqs[1] = {wq_gate};
   const float* sws[1] = {sw_gate};
   void* ys[1] = {nullptr};
   const int64_t Ns[1] = {2 * I};

@@ -105,6 +105,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       : "memory");
 }
 
+// 2-D tiled store from this CTA's shared memory (bulk async-group completion); the part of the
+// box outside the tensor is not written.  x is the innermost coordinate: x * element size must
+// be a multiple of 16 bytes, and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tm), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+
 // ---- tcgen05 ----------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -133,6 +142,19 @@ __device__ __forceinline__ void mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], 16-bit x 16-bit (f16 or bf16, per the instruction descriptor)
+// -> fp32; K = 16 elements per instruction.
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -179,6 +201,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 __host__ __device__ constexpr uint32_t idesc_e4m3(int mma_m, int mma_n) {
   return (1u << 4) | (static_cast<uint32_t>(mma_n >> 3) << 17) |
          (static_cast<uint32_t>(mma_m >> 4) << 24);
+}
+
+// Instruction descriptor for kind::f16 with both operands of one 16-bit type (fmt 0 = f16,
+// 1 = bf16), fp32 accumulation, both K-major; same field positions as above.
+__host__ __device__ constexpr uint32_t idesc_f16(int mma_m, int mma_n, int fmt) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         (static_cast<uint32_t>(mma_n >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
 // ---- CTA pairs (cta_group::2): one MMA spans two SMs ---------------------------------

@@ -250,7 +250,6 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         self.buffers = PeerBuffers(rows_max, self.I, self.H, dtype, dev)
         # every rank's launch signals each rank once per exchange
         self.count_h = self.count_y = self.world
-        self.ops.paired_gate_up(self.gate, self.up)      # built here, outside any capture
 
     def _init_shards(self, gate, up, down, ops, world, rank):
         if ops is None:

@@ -260,7 +260,7 @@ def last_gemm_launch() -> dict:
     """What the last GEMM call of this thread launched (kernel, grid, split, stages, smem, tile)."""
     out = (ctypes.c_int64 * 6)()
     _lib.check(_require_lib().bq_last_gemm_launch(out), "last_gemm_launch")
-    return {"kernel": {0: "stream", 1: "tile", 2: "pair"}.get(int(out[0]), "?"),
+    return {"kernel": {0: "stream", 2: "pair"}.get(int(out[0]), "?"),
             "grid": out[1], "split": out[2],
             "stages": out[3], "smem": out[4], "mma_n": out[5]}
 
@@ -727,12 +727,65 @@ def linear(x: torch.Tensor, w: torch.Tensor | FP8Weight,
     return y if residual is None else residual + y
 
 
+_DENSE_SEGMENTS = True
+
+
+def set_dense_segments(enable: bool) -> None:
+    """Whether `project` runs the unquantized 16-bit members of a mixed set (the GDN gates the
+    reference keeps in bf16) as extra segments of its one launch (default) or through
+    `F.linear`, as the reference does.  The FP8 members do not change; a 16-bit member differs
+    from `F.linear` only by the summation order of its tensor-core GEMM."""
+    global _DENSE_SEGMENTS
+    _DENSE_SEGMENTS = bool(enable)
+
+
+def _project_mixed(xq, sx, dense: torch.Tensor, weights, lead, K):
+    """One launch for FP8 and 16-bit weights together, or None when the set does not qualify."""
+    M = xq.shape[0]
+    dt = dense.dtype
+    if (not _DENSE_SEGMENTS or M == 0 or M > 256 or dt not in (torch.bfloat16, torch.float16)
+            or len(weights) > _lib.BQ_MAX_SEGMENTS):
+        return None
+    d2 = dense.reshape(-1, K)
+    if not d2.is_contiguous() or d2.data_ptr() % 16:
+        return None
+    for w in weights:
+        if isinstance(w, FP8Weight):
+            if w.data.shape[1] != K or not w.data.is_contiguous():
+                return None
+        elif (w.dtype != dt or w.dim() != 2 or w.shape[1] != K or w.shape[0] % 16
+              or not w.is_contiguous() or w.data_ptr() % 16 or not w.is_cuda):
+            return None
+    lib = _require_lib()
+    n = len(weights)
+    raw = [w.data if isinstance(w, FP8Weight) else w for w in weights]
+    outs = [torch.empty((M, r.shape[0]), dtype=dt, device=xq.device) for r in raw]
+    wp = (ctypes.c_void_p * n)(*[r.data_ptr() for r in raw])
+    sw = (ctypes.c_void_p * n)(*[w.scale.data_ptr() if isinstance(w, FP8Weight) else None
+                                 for w in weights])
+    kind = (ctypes.c_int * n)(*[0 if isinstance(w, FP8Weight) else 1 for w in weights])
+    yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in outs])
+    Ns = (ctypes.c_int64 * n)(*[r.shape[0] for r in raw])
+    ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in outs])
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    rc = lib.bq_project_mixed(xq.data_ptr(), sx.data_ptr(), d2.data_ptr(), _DTYPE_CODE[dt], M, K, n,
+                              wp, sw, kind, yp, Ns, ld, _DTYPE_CODE[dt], _take_slot(xq.device), 16,
+                              _stream_ptr(xq.device))
+    if rc == _lib.BQ_ERR_UNSUPPORTED:
+        return None
+    _lib.check(rc, "project")
+    return [y.reshape(*lead, y.shape[1]) for y in outs]
+
+
 def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.Tensor]:
     """`F.linear(x, w)` for several projections that share one activation.
 
-    The activation is quantized once (braid/model/quant.py:260-286) and all FP8
-    weights of the call go through one grouped launch; weights left in bf16 take
-    `F.linear` untouched, so mixed sets (GDN's qkv/z with its bf16 a/b gates) work.
+    The activation is quantized once (braid/model/quant.py:260-286) and all FP8 weights of
+    the call go through one grouped launch.  Weights left in bf16 (GDN's a/b gates beside its
+    FP8 qkv/z) ride in the same launch at decode sizes, as 16-bit tensor-core segments over
+    the unquantized activation; where that does not apply (larger M, fp32 engines,
+    `set_dense_segments(False)`) they take `F.linear`, as in the reference.
     """
     pre = x if isinstance(x, QuantizedActivation) else None
     if not any(isinstance(w, FP8Weight) for w in weights):
@@ -740,6 +793,16 @@ def project(x: torch.Tensor, *weights: torch.Tensor | FP8Weight) -> list[torch.T
         return [F.linear(dense, w) for w in weights]
     *lead, K = x.shape
     fp8 = [w for w in weights if isinstance(w, FP8Weight)]
+    if len(fp8) < len(weights) and (pre is None or pre.dense is not None):
+        if pre is not None:
+            xq, sx, dense = pre.q, pre.scale, pre.dense
+        else:
+            dense = x
+            xq, sx = quantize_act(x.reshape(-1, K))
+        mixed = _project_mixed(xq, sx, dense, weights, lead, K)
+        if mixed is not None:
+            return mixed
+        pre = QuantizedActivation(xq, sx, x.shape, x.dtype, dense)     # do not quantize twice
     if pre is not None:
         ys = iter(fp8_matmul_grouped(pre.q, pre.scale, fp8, out_dtype=pre.dtype))
     else:
@@ -763,46 +826,26 @@ def maybe_quantize(w: torch.Tensor, enabled: bool) -> torch.Tensor | FP8Weight:
 
 
 # ---------------------------------------------------------------------------
-# gate/up as ONE weight with interleaved row tiles (a layout made for the kernel)
+# gate and up in ONE launch: every MMA tile is put together from 64 gate rows and the 64 up rows
+# of the same output columns (two TMA boxes per stage, read from the two weights where they lie),
+# so the epilogue can form silu(gate) * up, its amax and its FP8 codes without either half ever
+# being written.  The reference keeps `gate_proj` and `up_proj` as two tensors with two scales
+# (braid/model/mlp.py:27-29) and so does this: nothing is repacked or copied.
 # ---------------------------------------------------------------------------
-# Row tile t of the paired weight holds gate rows [64t, 64t+64) followed by up rows [64t, 64t+64),
-# so one 128-row MMA tile yields gate AND up of the same 64 columns and the epilogue can form
-# silu(gate) * up, its amax and its FP8 codes without the two halves ever being written.  The
-# reference keeps `gate_proj` and `up_proj` as two tensors with two scales (braid/model/mlp.py:
-# 27-29); both scales are kept, the paired copy is built once per weight pair outside captures.
 _PAIR_MLP = True
-_PAIRED: dict[tuple[int, int], tuple] = {}
 
 
 def set_paired_mlp(enable: bool) -> None:
-    """Use (default) or not the interleaved gate/up copy and the 3-launch MLP.  Off saves the
-    extra copy of the two weights (2 * I * K bytes per layer); results are identical."""
+    """Use (default) or not the one-launch gate/up form and the 3-launch MLP (results are
+    identical either way; off gives the four-launch form at every size)."""
     global _PAIR_MLP
     _PAIR_MLP = bool(enable)
-    if not enable:
-        _PAIRED.clear()
 
 
-def paired_gate_up(gate: FP8Weight, up: FP8Weight) -> torch.Tensor | None:
-    """The interleaved `[2I, K]` e4m3 copy of a gate/up pair, cached per pair of tensors.
-    `None` when the shapes do not pair (I not a multiple of 64) or when it would have to be built
-    during a stream capture."""
-    import weakref
-    key = (gate.data.data_ptr(), up.data.data_ptr())
-    hit = _PAIRED.get(key)
-    if hit is not None and hit[0]() is gate.data and hit[1]() is up.data:
-        return hit[2]
-    I, K = gate.data.shape
-    if (up.data.shape != (I, K) or I % 64 or not gate.data.is_contiguous()
-            or not up.data.is_contiguous() or torch.cuda.is_current_stream_capturing()):
-        return None
-    for k in [k for k, v in _PAIRED.items() if v[0]() is None or v[1]() is None]:
-        del _PAIRED[k]
-    g8 = gate.data.view(torch.uint8).view(I // 64, 64, K)
-    u8 = up.data.view(torch.uint8).view(I // 64, 64, K)
-    paired = torch.stack((g8, u8), dim=1).reshape(2 * I, K).view(FP8)
-    _PAIRED[key] = (weakref.ref(gate.data), weakref.ref(up.data), paired)
-    return paired
+def _pairable(gate: FP8Weight, up: FP8Weight, K: int) -> bool:
+    I = gate.data.shape[0]
+    return (up.data.shape == gate.data.shape and I % 64 == 0 and gate.data.shape[1] == K
+            and gate.data.is_contiguous() and up.data.is_contiguous())
 
 
 def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
@@ -815,8 +858,7 @@ def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: 
     code = _DTYPE_CODE.get(act_dtype)
     if not _PAIR_MLP or _quantizers_off() or code is None or M == 0 or M > 256:
         return None
-    paired = paired_gate_up(gate, up)
-    if paired is None or gate.data.shape[1] != K:
+    if not _pairable(gate, up, K):
         return None
     lib = _require_lib()
     I = gate.data.shape[0]
@@ -824,8 +866,8 @@ def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: 
     sh = torch.empty((1, 1), dtype=torch.float32, device=xq.device)
     if not xq.is_contiguous():
         xq = xq.contiguous()
-    rc = lib.bq_gate_up_silu_quant_w8a8(xq.data_ptr(), sx.data_ptr(), paired.data_ptr(),
-                                        gate.scale.data_ptr(), up.scale.data_ptr(), M, I, K, code,
+    rc = lib.bq_gate_up_silu_quant_w8a8(xq.data_ptr(), sx.data_ptr(), gate.data.data_ptr(),
+                                        up.data.data_ptr(), gate.scale.data_ptr(), up.scale.data_ptr(), M, I, K, code,
                                         hq.data_ptr(), sh.data_ptr(), _take_slot(xq.device), 16,
                                         _stream_ptr(xq.device))
     if rc == _lib.BQ_ERR_UNSUPPORTED:
@@ -866,17 +908,15 @@ def gemm_push(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight, out_dtype: torch
 def gate_up_silu_push(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
                       act_dtype: torch.dtype, dst_ptrs: Sequence[int], ld: int,
                       flag_ptrs: Sequence[int]) -> None:
-    """This rank's slice of `F.silu(xq @ gate^T) * (xq @ up^T)` in one launch over the paired
-    shard, stored into every rank's gathered `h` buffer, followed by the signals."""
+    """This rank's slice of `F.silu(xq @ gate^T) * (xq @ up^T)` in one launch over its gate and
+    up shards, stored into every rank's gathered `h` buffer, followed by the signals."""
     _check_gemm_inputs(xq, sx)
     lib = _require_lib()
-    paired = paired_gate_up(gate, up)
-    if paired is None:
-        raise ValueError("gate/up shard cannot be paired (rows must be a multiple of 64; build "
-                         "the pair outside stream capture)")
     M, K = xq.shape
-    rc = lib.bq_gate_up_silu_push_w8a8(xq.data_ptr(), sx.data_ptr(), paired.data_ptr(),
-                                       gate.scale.data_ptr(), up.scale.data_ptr(), M,
+    if not _pairable(gate, up, K):
+        raise ValueError("gate/up shards must be two contiguous [I, K] weights, I a multiple of 64")
+    rc = lib.bq_gate_up_silu_push_w8a8(xq.data_ptr(), sx.data_ptr(), gate.data.data_ptr(),
+                                       up.data.data_ptr(), gate.scale.data_ptr(), up.scale.data_ptr(), M,
                                        gate.data.shape[0], K, _DTYPE_CODE[act_dtype], len(dst_ptrs),
                                        _ptr_array(dst_ptrs), ld, _ptr_array(flag_ptrs),
                                        _take_slot(xq.device), 16, _stream_ptr(xq.device))
@@ -900,8 +940,8 @@ def wait_flag(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.
 def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
                 down_proj: FP8Weight, residual: torch.Tensor | None = None) -> torch.Tensor:
     """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 3 launches at decode
-    sizes: quantize(x) -> gate and up as one GEMM over the paired weight with SiLU*mul and the
-    quantization of h in its epilogue -> down GEMM (with `residual` added in its epilogue).
+    sizes: quantize(x) -> gate and up as one GEMM (tiles put together from both weights) with
+    SiLU*mul and the quantization of h in its epilogue -> down GEMM (with `residual` added in its epilogue).
     Larger M, unpaired shapes or `set_paired_mlp(False)`: 4 launches (quantize -> grouped GEMM
     writing gate|up into one `[M, 2I]` buffer -> SiLU*mul inside the quantizer of h -> down).
     Either way the result is bit-identical to the reference's nine-plus-kernel sequence built

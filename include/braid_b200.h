@@ -260,21 +260,23 @@ int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const
  * -- neither gate, up nor h is written; only the codes and the scale are.  Bit-identical to
  * bq_gemm_w8a8_grouped(gate, up) followed by bq_silu_mul_quant.
  *
- * The kernel needs gate and up of the same columns in one MMA tile, so it takes the two
- * weights as ONE [2I, K] e4m3 tensor whose 128-row tiles interleave them: rows
- * [128t, 128t+64) = gate rows [64t, 64t+64), rows [128t+64, 128t+128) = up rows [64t, 64t+64).
- * Both per-tensor scales are kept.  I must be a multiple of 64.
+ * The kernel needs gate and up of the same columns in one MMA tile: every 128-row tile is put
+ * together in shared memory from 64 rows of the gate weight and the 64 rows of the up weight
+ * with the same indices (two TMA boxes per pipeline stage).  The two weights stay where and
+ * as the reference keeps them -- two [I, K] tensors with two scales; nothing is repacked.
+ * I must be a multiple of 64.
  *
  * Replaces: braid/model/mlp.py:46-48 (`gate = fp8_matmul(..)`, `up = fp8_matmul(..)`,
  * `h = F.silu(gate) * up`) and the `quantize_act` inside `linear(h, down_proj)` (:49).
  *
- *   wq_pair  device, [2I, K] e4m3 codes in the interleaved layout, 16-byte aligned
+ *   wq_gate, wq_up  device, [I, K] e4m3 codes each, contiguous, 16-byte aligned
  *   hq_out   device, M*I bytes, contiguous [M, I];  sh_out  device, one float
  *   ws       16 bytes, zero before the first call, self-resetting (as for bq_quantize_act)
  * Returns BQ_ERR_UNSUPPORTED when the launch cannot be resident at once or M > 256.
  */
-int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_pair,
-                               const float* sw_gate, const float* sw_up, int64_t M, int64_t I,
+int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_gate,
+                               const void* wq_up, const float* sw_gate, const float* sw_up,
+                               int64_t M, int64_t I,
                                int64_t K, int act_dtype, void* hq_out, float* sh_out,
                                void* ws, size_t ws_bytes, void* stream);
 
@@ -320,12 +322,13 @@ int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const flo
                       void* ws, size_t ws_bytes, void* stream);
 
 /*
- * h shard = T(T(silu(gate)) * up) of this rank's interleaved gate/up shard (layout as for
+ * h shard = T(T(silu(gate)) * up) of this rank's gate and up shards (two [I, K] tensors as for
  * bq_gate_up_silu_quant_w8a8, I = columns of this rank) pushed to every rank.  The amax of h
  * spans all ranks' shards, so quantization is left to bq_quantize_act on the gathered buffer.
  */
-int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_pair,
-                              const float* sw_gate, const float* sw_up, int64_t M, int64_t I,
+int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_gate,
+                              const void* wq_up, const float* sw_gate, const float* sw_up,
+                              int64_t M, int64_t I,
                               int64_t K, int act_dtype, int n_peers, void* const* h_dst,
                               int64_t ld_h, void* const* flags,
                               void* ws, size_t ws_bytes, void* stream);
@@ -362,6 +365,29 @@ int bq_gemm_w8a8_grouped(const void* xq, const float* sx, int64_t M, int64_t K, 
                          void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * `project` with a mixed set of weights in ONE launch (decode regime, M <= 256): segments
+ * with kind[i] == 0 are e4m3 weights multiplied with the quantized activation exactly as in
+ * bq_gemm_w8a8_grouped; segments with kind[i] != 0 are weights the reference leaves
+ * unquantized (bf16 / fp16, [N_i, K] row-major) and are multiplied with the UNQUANTIZED
+ * activation `x_dense` [M, K] of the same 16-bit type on the tensor cores (kind::f16, fp32
+ * accumulation, no scales; sw[i] is ignored and may be null).  The FP8 segments are
+ * bit-identical to separate calls; a 16-bit segment is `F.linear(x, w)` up to the summation
+ * order of a tensor-core GEMM (it is not bit-identical to the cuBLAS kernel torch would pick).
+ *
+ * Replaces: braid/model/quant.py:260-286 (`project`) including its `F.linear(x, w)` arm for
+ * weights left in bf16 -- the GDN gates in_proj_a / in_proj_b of braid/model/gdn.py:254-255.
+ *
+ *   x_dense      device, [M, K] of dense_dtype (BQ_DTYPE_BF16 or BQ_DTYPE_F16), contiguous,
+ *                16-byte aligned; out_dtype must equal dense_dtype when a 16-bit segment exists
+ *   w[i]         device, e4m3 codes (kind 0) or 16-bit values (kind != 0), contiguous [N_i, K]
+ * Returns BQ_ERR_UNSUPPORTED for M > 256: call bq_gemm_w8a8_grouped and a dense GEMM instead.
+ */
+int bq_project_mixed(const void* xq, const float* sx, const void* x_dense, int dense_dtype, int64_t M,
+                     int64_t K, int n_seg, const void* const* w, const float* const* sw,
+                     const int* kind, void* const* y, const int64_t* N, const int64_t* ldy,
+                     int out_dtype, void* ws, size_t ws_bytes, void* stream);
+
+/*
  * Copies the sticky device status word of a scratch buffer to the host
  * (synchronises `stream`; never call during capture).  0 means every bounded
  * device wait so far completed; otherwise BQ_ERR_DEVICE_WAIT.  The word is
@@ -371,7 +397,6 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
 
 /*
  * Tuning hooks used by the benchmark and tests; not needed for normal use.
- * bq_set_option("prefill_pair", 0/1)    prefill regime on CTA pairs (default 1)
  * bq_set_option("decode_split_k", v)    0 = heuristic, else force the K slices per tile
  * bq_set_option("decode_stages", v)     0 = heuristic, else cap the pipeline depth
  * bq_set_option("decode_cta_target", v) CTAs a small weight is sliced to reach (default 160)
@@ -385,7 +410,7 @@ int bq_set_option(const char* key, int64_t value);
 
 /*
  * Describes the launch the last GEMM call on this thread chose:
- * out[0]=kernel (0 cluster stream, 1 tile, 2 CTA-pair tile) out[1]=grid out[2]=cluster/split
+ * out[0]=kernel (0 weight-streaming cluster kernel, 2 CTA-pair tile kernel) out[1]=grid out[2]=cluster/split
  * out[3]=stages out[4]=dynamic smem bytes out[5]=batch tile (MMA N)
  */
 int bq_last_gemm_launch(int64_t out[6]);

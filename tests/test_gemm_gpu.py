@@ -141,19 +141,28 @@ def test_lm_head_at_full_vocabulary(Q, M):
     assert Q.device_status() == 0
 
 
-def test_both_prefill_kernels_agree(Q):
-    """The single-CTA tile kernel and the CTA-pair kernel accumulate K in the same order: same bits."""
-    _, _, xq, sx, fw = _operands(Q, 1000, 4096 + 16, 1040, seed=77)
-    try:
-        Q.set_option("prefill_pair", 1)
-        a = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
-        assert Q.last_gemm_launch()["kernel"] == "pair"
-        Q.set_option("prefill_pair", 0)
-        b = Q.fp8_matmul(xq, sx, fw, out_dtype=torch.float32)
-        assert Q.last_gemm_launch()["kernel"] == "tile"
-    finally:
-        Q.set_option("prefill_pair", 1)
-    assert torch.equal(a, b)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+def test_prefill_store_paths_agree_and_stay_in_bounds(Q, dt):
+    """The prefill epilogue hands 128-byte row pieces to TMA stores when the output can be
+    described to TMA (16-byte aligned base and row pitch) and writes the same staged pieces with
+    plain coalesced stores otherwise: same bits either way, ragged M and N clipped, nothing
+    outside the output touched."""
+    M, N, K = 1000, 4096 + 16, 1040
+    _, _, xq, sx, fw = _operands(Q, M, N, K, seed=77)
+    want = Q.fp8_matmul(xq, sx, fw, out_dtype=dt)                 # contiguous: the TMA path
+    assert Q.last_gemm_launch()["kernel"] == "pair"
+    ref = TS.dequant_matmul(xq, sx, fw.data, fw.scale)
+    assert max_rel(want, ref) <= (TOL_F32 if dt is torch.float32 else TOL_BF16)
+    # 16-bit outputs: a pitch of N + 4 elements is 8-byte but not 16-byte aligned (plain stores);
+    # fp32 outputs must be 16-byte aligned anyway, so every legal one takes the TMA path
+    for off, pitch in ((0, N + 4), (4, N + 4), (8, N + 24)):
+        big = torch.full((M + 2, pitch + 16), 7.0, device="cuda", dtype=dt)
+        out = big[1:M + 1, off:off + N]
+        Q.fp8_matmul_grouped(xq, sx, (fw,), out_dtype=dt, out=(out,))
+        assert torch.equal(out, want), (off, pitch)
+        mask = torch.ones_like(big, dtype=torch.bool)
+        mask[1:M + 1, off:off + N] = False
+        assert (big[mask] == 7.0).all(), (off, pitch)
     assert Q.device_status() == 0
 
 
@@ -238,13 +247,57 @@ def test_project_matches_linear_per_weight(Q, M):
 
 
 def test_project_leaves_bf16_weights_on_the_bf16_path(Q):
+    """tests/test_quant.py:221-242: a weight left in bf16 is multiplied unquantized.  Through
+    `F.linear` (the reference's arm, selectable) the result is that call's bits; as a 16-bit
+    segment of the one launch (default) it is the same product up to summation order."""
     x = randn_cpu((4, 256), seed=16).cuda()
     a = randn_cpu((512, 256), seed=17, scale=0.02).cuda()
     b = randn_cpu((32, 256), seed=18, scale=0.02).cuda()
-    got_a, got_b = Q.project(x, Q.quantize_weight(a), b)
-    assert torch.equal(got_b, F.linear(x, b))
-    ga, gb = Q.project(x, a, b)
+    Q.set_dense_segments(False)
+    try:
+        got_a, got_b = Q.project(x, Q.quantize_weight(a), b)
+        assert torch.equal(got_b, F.linear(x, b))
+    finally:
+        Q.set_dense_segments(True)
+    n0 = Q.launch_count()
+    seg_a, seg_b = Q.project(x, Q.quantize_weight(a), b)
+    assert Q.launch_count() - n0 == 2                       # one quantizer, one GEMM launch
+    assert torch.equal(seg_a, got_a)                        # the FP8 member does not change
+    assert seg_b.dtype is torch.bfloat16 and seg_b.shape == (4, 32)
+    assert max_rel(seg_b, F.linear(x.float(), b.float())) <= 2 ** -8
+    ga, gb = Q.project(x, a, b)                             # no FP8 member: untouched torch path
     assert torch.equal(ga, F.linear(x, a)) and torch.equal(gb, F.linear(x, b))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("M", [1, 16, 37, 128, 256])
+def test_gdn_input_projection_as_one_launch(Q, dt, M):
+    """braid/model/gdn.py:254-255: `project(x, qkv, z, a, b)` with qkv / z in FP8 and the gates
+    a / b unquantized (32 x 4096 each, braid/model/gdn.py:73-81), at the 9B widths.  FP8 members
+    bit-equal to the grouped FP8 launch; a and b within bf16 rounding of the exact product and
+    almost everywhere bit-equal to `F.linear`; run-to-run identical; graph-capturable."""
+    H = 4096
+    x = randn_cpu((M, H), seed=M, dtype=dt).cuda()
+    qkv = Q.quantize_weight(randn_cpu((8192, H), seed=1, scale=0.02).cuda())
+    z = Q.quantize_weight(randn_cpu((4096, H), seed=2, scale=0.02).cuda())
+    a = randn_cpu((32, H), seed=3, dtype=dt, scale=0.02).cuda()
+    b = randn_cpu((32, H), seed=4, dtype=dt, scale=0.05).cuda()
+    ys = Q.project(x, qkv, z, a, b)
+    assert Q.last_gemm_launch()["kernel"] == "stream"
+    xq, sx = Q.quantize_act(x)
+    for got, want in zip(ys[:2], Q.fp8_matmul_grouped(xq, sx, (qkv, z), out_dtype=dt)):
+        assert torch.equal(got, want)
+    for got, w in zip(ys[2:], (a, b)):
+        exact = F.linear(x.double(), w.double())
+        assert got.dtype is dt and got.shape == (M, 32)
+        assert max_rel(got, exact) <= (2 ** -8 if dt is torch.bfloat16 else 2 ** -10)
+        assert (got != F.linear(x, w)).float().mean().item() < 0.1
+    again = Q.project(x, qkv, z, a, b)
+    assert all(torch.equal(p, q) for p, q in zip(ys, again))
+    # a pre-quantized activation that kept its dense form takes the same launch
+    pre = Q.QuantizedActivation(xq, sx, x.shape, dt, dense=x)
+    assert all(torch.equal(p, q) for p, q in zip(ys, Q.project(pre, qkv, z, a, b)))
+    assert Q.device_status() == 0
 
 
 def test_leading_dims_and_dispatch(Q):
@@ -447,12 +500,11 @@ def test_paired_mlp_equals_the_four_launch_mlp_and_replays(Q):
         got = Q.mlp_forward(x, wg, wu, wd)
         assert Q.launch_count() - n0 == (3 if M <= 128 else 4)
         assert torch.equal(got, want) and torch.equal(Q.mlp_forward(x, wg, wu, wd, residual=r), want_r)
-    # the paired copy is cached per pair of tensors and rebuilt for new ones
-    p1 = Q.paired_gate_up(wg, wu)
-    assert p1 is Q.paired_gate_up(wg, wu) and p1.shape == (2 * I, H)
-    assert torch.equal(p1.view(torch.uint8)[:64], wg.data.view(torch.uint8)[:64])
-    assert torch.equal(p1.view(torch.uint8)[64:128], wu.data.view(torch.uint8)[:64])
-    assert torch.equal(p1.view(torch.uint8)[128:192], wg.data.view(torch.uint8)[64:128])
+    # the one-launch form reads the two weights in place: no copy of either is made or kept
+    free0 = torch.cuda.mem_get_info()[0]
+    Q.mlp_forward(randn_cpu((16, H), seed=2).cuda(), wg, wu, wd)
+    torch.cuda.synchronize()
+    assert free0 - torch.cuda.mem_get_info()[0] < 32 << 20
     # capture + replay
     x = randn_cpu((128, H), seed=9).cuda()
     eager = Q.mlp_forward(x, wg, wu, wd).clone()
