@@ -364,6 +364,11 @@ def projection_tables(dev, peaks):
         "frac_hbm_M128": {r["proj"]: r["frac_hbm"] for r in rows if r["M"] == 128},
         "vs_scaled_mm": {"min": ratio[0], "median": statistics.median(ratio), "max": ratio[-1]} if ratio else None,
         "note": "attn.o_proj has out_proj's shape; frac = algorithmic bytes (N*K + M*K + 2*M*N) / time / peak"}
+    try:
+        per_projection["lm_head"] = sweep.lm_head_rows(dev, peaks)
+    except Exception as e:  # noqa: BLE001
+        torch.cuda.synchronize()
+        per_projection["lm_head"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
     g = torch.Generator().manual_seed(4)
     m4 = int(torch.randint(64, 1025, (16,), generator=g).sum().item())
     peak8 = sweep.fp8_library_peak(dev, seconds=1.0)

@@ -90,6 +90,24 @@ struct PairSilu {
   unsigned int expected;   // CTAs that take part in the exchange (the active ones)
 };
 
+// Greedy pick fused into the lm_head GEMM: every CTA (one 128-row tile of the vocabulary, K not
+// split) reduces, per batch row, the largest of ITS 128 logits -- taken after the rounding to the
+// output type the logits tensor would have had, lowest index winning ties, NaN winning over
+// everything, which is `logits.argmax(-1)` as torch evaluates it -- and writes one (value,
+// index) pair per row; a second, tiny kernel reduces the pairs of all tiles.
+struct ArgmaxOut {
+  int on;
+  int store_logits;          // 0 = the logits themselves are not written at all
+  uint2* partial;            // device: [tiles][M] pairs {value as fp32 bits, vocabulary index}
+};
+
+// a beats b: NaN first, then the larger value, then the lower index
+__device__ __forceinline__ bool argmax_beats(float av, int ai, float bv, int bi) {
+  const bool an = av != av, bn = bv != bv;
+  if (an || bn) return an && (!bn || ai < bi);
+  return av > bv || (av == bv && ai < bi);
+}
+
 // Column-parallel form: the output tile (or, in the paired form, h) is stored straight into the
 // gathered buffer of every rank of the node -- plain stores through peer-mapped pointers, this
 // rank's own buffer included.  The CTAs of the launch count themselves on a local word; the last
@@ -116,11 +134,13 @@ struct GemmParams {
   int k_blocks_dense;  // stream kernel: 128-byte K blocks of a 16-bit row, ceil(2K / 128)
   int dense_fmt;       // stream kernel: tcgen05 operand format of the 16-bit segments (0 f16, 1 bf16)
   int cluster;         // stream kernel: CTAs per cluster = largest split of the launch
-  int stages;
+  int stages;          // stream kernel: depth of the weight ring; pair kernel: pipeline depth
+  int b_stages;        // stream kernel: depth of the activation ring
   int out_dtype;
   int m_tiles;         // tile kernel: ceil(M / 128)
   int total_tiles;     // tile kernel
   unsigned int* status;
+  ArgmaxOut argmax;
   unsigned long long* phase_ring;   // development builds (BQ_PHASES) only, else nullptr
   int phase_seq;
   PairSilu pair;
@@ -275,6 +295,66 @@ __device__ __forceinline__ void reduce_store(const EpilogueArgs& e) {
   }
 }
 
+// Per batch row of this CTA's share: the best of the tile's 128 logits (see ArgmaxOut).  K is
+// not split in an argmax launch, so the staged tile is final.
+template <typename T>
+__device__ __forceinline__ void argmax_rows(const EpilogueArgs& e, int n_total, uint2* partial_tile) {
+  using namespace bq::qd;
+  const int n4 = e.lane * 4;
+  for (int m = e.m_begin + e.warp; m < e.m_end; m += kStreamWarps) {
+    const float4 v = *reinterpret_cast<const float4*>(e.part + m * kRowTile + n4);
+    const float r[4] = {widen(narrow<T>(v.x * e.scale)), widen(narrow<T>(v.y * e.scale)),
+                        widen(narrow<T>(v.z * e.scale)), widen(narrow<T>(v.w * e.scale))};
+    float bv = 0.0f;
+    int bi = 0x7fffffff;                      // "nothing yet": loses against any real column
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = e.row0 + n4 + j;
+      if (idx < n_total && (bi == 0x7fffffff || argmax_beats(r[j], idx, bv, bi))) { bv = r[j]; bi = idx; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || argmax_beats(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+    }
+    if (e.lane == 0) partial_tile[m] = make_uint2(__float_as_uint(bv), static_cast<unsigned int>(bi));
+  }
+}
+
+// Second stage of the greedy pick: one CTA per batch row reduces the pairs of all tiles.
+__global__ void __launch_bounds__(128) argmax_finish_kernel(const uint2* partial, int tiles, int M,
+                                                            long long* idx_out) {
+  pdl_wait_prior_grids();
+  const int m = blockIdx.x;
+  float bv = 0.0f;
+  int bi = 0x7fffffff;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const uint2 pr = __ldcg(partial + static_cast<size_t>(t) * M + m);
+    const float ov = __uint_as_float(pr.x);
+    const int oi = static_cast<int>(pr.y);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || argmax_beats(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+  }
+  __shared__ float s_v[4];
+  __shared__ int s_i[4];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || argmax_beats(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w)
+      if (s_i[w] != 0x7fffffff && (bi == 0x7fffffff || argmax_beats(s_v[w], s_i[w], bv, bi))) {
+        bv = s_v[w];
+        bi = s_i[w];
+      }
+    idx_out[m] = bi;
+  }
+}
+
 // Interleaved gate/up tile: columns 0..63 of the tile are gate rows, 64..127 the up rows of the
 // same 64 output columns.  Sums the K slices like reduce_store, rounds both halves to the
 // activation type T exactly as the plain GEMM would have stored them, forms
@@ -361,7 +441,12 @@ __device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const floa
 // Weight-streaming kernel (swap-AB, cluster split-K)
 // ---------------------------------------------------------------------------
 // Shared memory, after aligning the dynamic base to 1024 bytes:
-//   [stages x 16 KiB weight tiles][stages x (mma_n*128) activation tiles] ... [barrier block]
+//   [stages x 16 KiB weight tiles][b_stages x (mma_n*128) activation tiles] ... [barrier block]
+// Two rings with their own barriers and their own producer thread.  The weight ring is as deep
+// as the shared memory allows: its tiles come from HBM, and the bytes in flight per SM are what
+// sets the streaming rate.  The activation ring is shallow (2 to 4 tiles at wide batches): its
+// tiles are L2 hits shared by every row tile, and a wide batch tile is as large as a weight
+// tile, so every activation slot given up is a weight tile more in flight.
 // The tile area is reused after the main loop as the fp32 staging buffer
 // part[m][128] that the cluster reduction reads.
 #ifndef BQ_STREAM_MIN_CTAS
@@ -378,12 +463,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const uint32_t a_base = base;
   const uint32_t b_base = base + p.stages * kATileBytes;
   const uint32_t bar_base = base + smem_tile_bytes;          // 8-byte aligned
-  // barrier block: full[s] at +8s, empty[s] at +8(stages+s), accum at +8*2*stages
+  // barrier block: weight ring full / empty, activation ring full, accumulator.  One
+  // tcgen05.commit per K block: it arrives on the weight slot's "empty" barrier, and the
+  // activation producer watches the same barrier for the block whose activation slot it wants
+  // to refill.
+  const int n_bars = 2 * p.stages + p.b_stages;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
-  const uint32_t accum_bar = bar_base + 8u * (2 * p.stages);
+  auto full_bar_b = [&](int s) { return bar_base + 8u * (2 * p.stages + s); };
+  const uint32_t accum_bar = bar_base + 8u * n_bars;
   volatile uint32_t* const tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (2 * p.stages + 1));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + smem_tile_bytes + 8 * (n_bars + 1));
   volatile uint32_t* const abort_flag = tmem_slot + 1;
   float* const s_quant = reinterpret_cast<float*>(const_cast<uint32_t*>(tmem_slot) + 2);   // one float per warp
 
@@ -428,6 +518,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    for (int s = 0; s < p.b_stages; ++s) mbar_init(full_bar_b(s), 1);
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -450,43 +541,58 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   if (warp == 0) {
     if (elect_one()) {
-      // weights are read once: evict first; the activation tile is shared by
-      // every row tile: keep it in L2
+      // Weights do not depend on any earlier kernel: this thread never waits for the kernel
+      // that produces the activation, it only follows the MMAs through the weight ring.
+      // weights are read once: evict first
       const uint64_t pol_w = policy_evict_first();
-      const uint64_t pol_x = policy_evict_last();
-      // Weights do not depend on any earlier kernel: fill the pipeline with them
-      // first, and only then wait for the kernel that produces the activation.
-      const int prefill = kb_count < p.stages ? kb_count : p.stages;
       // one 128-row box, or (paired gate/up) two 64-row boxes from the two weights
       const bool paired = p.pair.on != 0;
       const int half_row0 = tile_in_seg * (kRowTile / 2);
-      auto load_w = [&](int slot, int kx) {
-        const uint32_t dst = a_base + slot * kATileBytes;
-        if (paired) {
-          tma_load_2d(dst, &tm_w.w[0], full_bar(slot), kx, half_row0, pol_w);
-          tma_load_2d(dst + kATileBytes / 2, &tm_w.w[1], full_bar(slot), kx, half_row0, pol_w);
-        } else {
-          tma_load_2d(dst, &tm_w.w[sg], full_bar(slot), kx, row0, pol_w);
-        }
-      };
-      for (int i = 0; i < prefill; ++i) {
-        mbar_expect_tx(full_bar(i), kATileBytes + b_tile_bytes);
-        load_w(i, (kb_begin + i) * kBK);
-      }
-      pdl_wait_prior_grids();
-      BQ_STAMP(p, 2);
-      for (int i = 0; i < prefill; ++i)
-        tma_load_2d(b_base + i * b_tile_bytes, x_map, full_bar(i), (kb_begin + i) * kBK, 0, pol_x);
-      for (int i = prefill; i < kb_count; ++i) {
-        const int s = i % p.stages, use = i / p.stages;
-        if (!mbar_wait(empty_bar(s), (use - 1) & 1)) {
+      // slot and phase are carried along: an integer division by a run-time depth costs a
+      // single issuing thread more than the loads it issues
+      int s = 0;
+      uint32_t phase = 1;                      // parity of the completion that frees slot s
+      for (int i = 0; i < kb_count; ++i) {
+        if (i >= p.stages && !mbar_wait(empty_bar(s), phase)) {
           *abort_flag = 1;
           break;
         }
-        mbar_expect_tx(full_bar(s), kATileBytes + b_tile_bytes);
+        mbar_expect_tx(full_bar(s), kATileBytes);
         const int kx = (kb_begin + i) * kBK;
-        load_w(s, kx);
-        tma_load_2d(b_base + s * b_tile_bytes, x_map, full_bar(s), kx, 0, pol_x);
+        const uint32_t dst = a_base + s * kATileBytes;
+        if (paired) {
+          tma_load_2d(dst, &tm_w.w[0], full_bar(s), kx, half_row0, pol_w);
+          tma_load_2d(dst + kATileBytes / 2, &tm_w.w[1], full_bar(s), kx, half_row0, pol_w);
+        } else {
+          tma_load_2d(dst, &tm_w.w[sg], full_bar(s), kx, row0, pol_w);
+        }
+        if (++s == p.stages) { s = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    if (elect_one()) {
+      // the activation tile is shared by every row tile: keep it in L2
+      const uint64_t pol_x = policy_evict_last();
+      pdl_wait_prior_grids();   // the kernel that produces the activation has completed
+      BQ_STAMP(p, 2);
+      // Activation slot s was last read by the MMAs of block j = i - b_stages, whose completion
+      // is completion number j / stages of weight slot j % stages.  That barrier cannot complete
+      // a second time before this thread has looked: block j + stages >= i needs THIS load first
+      // (the host keeps b_stages <= stages).
+      int s = 0, js = 0;                       // activation slot of block i, weight slot of block j
+      uint32_t jphase = 0;                     // parity of completion j / stages
+      for (int i = 0; i < kb_count; ++i) {
+        if (i >= p.b_stages) {
+          if (!mbar_wait(empty_bar(js), jphase)) {
+            *abort_flag = 1;
+            break;
+          }
+          if (++js == p.stages) { js = 0; jphase ^= 1u; }
+        }
+        mbar_expect_tx(full_bar_b(s), b_tile_bytes);
+        tma_load_2d(b_base + s * b_tile_bytes, x_map, full_bar_b(s), (kb_begin + i) * kBK, 0, pol_x);
+        if (++s == p.b_stages) s = 0;
       }
     }
     __syncwarp();
@@ -494,16 +600,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (elect_one()) {
       const uint32_t idesc = dense ? idesc_f16(kRowTile, p.mma_n, p.dense_fmt)
                                    : idesc_e4m3(kRowTile, p.mma_n);
+      int s = 0, sb = 0;
+      uint32_t phase = 0, phase_b = 0;
       for (int i = 0; i < kb_count; ++i) {
-        const int s = i % p.stages, use = i / p.stages;
-        if (!mbar_wait(full_bar(s), use & 1)) {
+        if (!mbar_wait(full_bar(s), phase) || !mbar_wait(full_bar_b(sb), phase_b)) {
           *abort_flag = 1;
           break;
         }
         tc_fence_after();
         if (i == 0) BQ_STAMP(p, 3);
         const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
-        const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
+        const uint64_t db = smem_desc_sw128(b_base + sb * b_tile_bytes);
 #pragma unroll
         for (int j = 0; j < kBK / kUmmaK; ++j) {
           // +32 bytes along K inside the swizzle span = +2 in descriptor units (32 e4m3 or 16
@@ -511,7 +618,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           if (dense) mma_f16(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
           else mma_f8(tmem_base, da + 2u * j, db + 2u * j, idesc, (i | j) != 0 ? 1u : 0u);
         }
-        mma_commit(empty_bar(s));   // stage is free once these MMAs retire
+        mma_commit(empty_bar(s));   // both slots are free once these MMAs retire
+        if (++s == p.stages) { s = 0; phase ^= 1u; }
+        if (++sb == p.b_stages) { sb = 0; phase_b ^= 1u; }
       }
       mma_commit(accum_bar);        // accumulator complete
     }
@@ -578,6 +687,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       else { BQ_PAIR_ROWS(float) }
 #undef BQ_PAIR_ROWS
       pair_max = mx;
+    } else if (p.argmax.on) {
+      uint2* const mine = p.argmax.partial + static_cast<size_t>(tile_in_seg) * p.M;
+      if (p.out_dtype == BQ_DTYPE_BF16) argmax_rows<__nv_bfloat16>(ea, seg.n, mine);
+      else if (p.out_dtype == BQ_DTYPE_F16) argmax_rows<__half>(ea, seg.n, mine);
+      else argmax_rows<float>(ea, seg.n, mine);
+      if (p.argmax.store_logits) reduce_store<1, false>(ea);
     } else if (seg.res == nullptr) {
       switch (split) {
         case 1: reduce_store<1, false>(ea); break;
@@ -1074,6 +1189,7 @@ int device_sms() {
 
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
+long long g_opt_b_stages = 0;   // activation ring depth: 0 = heuristic, -1 = as deep as the weight ring
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
 thread_local long long g_last_launch[6] = {0, 0, 0, 0, 0, 0};
 
@@ -1202,13 +1318,27 @@ int launch_stream(const CUtensorMap& tm_x, const CUtensorMap& tm_xd, const Weigh
   // Leave room for the NEXT kernel's CTAs: with programmatic dependent launch they
   // become resident while this kernel still runs and pre-load their weights.
   if (g_opt_smem_cap > 0 && budget > g_opt_smem_cap) budget = (int)g_opt_smem_cap;
-  int stages = budget / stage_bytes;
+  int stages = budget / stage_bytes;            // both rings equally deep: the starting point
   if (stages > kb_max) stages = kb_max;
   if (stages > 24) stages = 24;
   if (stages < 2) stages = kb_max < 2 ? kb_max : 2;
   if (g_opt_stages > 0 && g_opt_stages < stages) stages = (int)g_opt_stages;
+  int b_stages = stages;
+  // Wide batch tiles: a shallow activation ring (its tiles are L2 hits), the rest goes to
+  // weight tiles in flight.  Two slots cover the L2 latency at the rate one CTA of a two-per-SM
+  // launch consumes tiles; a CTA that has the SM to itself consumes twice as fast.
+  long long want_b = g_opt_b_stages;
+  if (want_b == 0) want_b = b_tile >= 8192 ? (per_sm == 2 ? 2 : 4) : -1;
+  if (want_b > 0 && want_b < b_stages && !(g_opt_stages > 0)) {
+    b_stages = (int)want_b;
+    stages = (budget - b_stages * b_tile) / kATileBytes;
+    if (stages > kb_max) stages = kb_max;
+    if (stages > 24) stages = 24;
+    if (b_stages > stages) b_stages = stages;
+  }
   p.stages = stages;
-  int tile_bytes = stages * stage_bytes;
+  p.b_stages = b_stages;
+  int tile_bytes = stages * kATileBytes + b_stages * b_tile;
   if (tile_bytes < staging) tile_bytes = staging;
   const int smem = tile_bytes + kBarrierBytes + 1024;
   if (smem > kMaxSmem) return kErrUnsupported;
@@ -1288,6 +1418,7 @@ int gemm_set_option(const char* key, long long value);
 int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_split_k") == 0) { g_opt_split = value; return kOk; }
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
+  if (strcmp(key, "decode_b_stages") == 0) { g_opt_b_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
@@ -1324,7 +1455,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
                 const void* const* res = nullptr,
                 const int64_t* ld_res = nullptr, const PairSilu* pair = nullptr,
                 int split_forced = 0, const PushParams* push = nullptr,
-                const DenseArgs* dn = nullptr) {
+                const DenseArgs* dn = nullptr, const ArgmaxOut* am = nullptr) {
   if (!xq || !sx || !wq || !sw || !y || !N || !ldy || M <= 0 || K <= 0) return kErrBadArg;
   if (n_seg < 1 || n_seg > BQ_MAX_SEGMENTS) return kErrBadArg;
   if (out_dtype != BQ_DTYPE_F32 && out_dtype != BQ_DTYPE_BF16 && out_dtype != BQ_DTYPE_F16)
@@ -1337,7 +1468,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     const bool is_dense = dn != nullptr && dn->kind[i] != 0;
     if (!wq[i] || (!sw[i] && !is_dense) || N[i] <= 0) return kErrBadArg;
     if (N[i] % 16 || !aligned_to(wq[i], 16)) return kErrUnsupported;
-    if (pair == nullptr && push == nullptr) {   // the pair and push forms do not write y
+    if (pair == nullptr && push == nullptr && !(am != nullptr && !am->store_logits)) {   // forms that write y
       if (!y[i]) return kErrBadArg;
       if (ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(y[i], out_align)) return kErrUnsupported;
     }
@@ -1382,6 +1513,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     p.pair.on = 1;
     p.pair.words = static_cast<unsigned int*>(ws);
   }
+  if (am) {
+    if (!stream_path || pair || push || res || dn || n_seg != 1) return kErrUnsupported;
+    p.argmax = *am;
+    p.argmax.on = 1;
+  }
   if (push) {
     p.push = *push;
     p.push.done = static_cast<unsigned int*>(ws);   // first scratch word: zero between launches
@@ -1396,8 +1532,9 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
-    p.seg[i].y = (pair || push) ? nullptr : y[i];
-    p.seg[i].ldy = (pair || push) ? 0 : ldy[i];
+    const bool no_y = pair || push || (am != nullptr && !am->store_logits);
+    p.seg[i].y = no_y ? nullptr : y[i];
+    p.seg[i].ldy = no_y ? 0 : ldy[i];
     p.seg[i].split_forced = split_forced;
     p.seg[i].res = res ? res[i] : nullptr;
     p.seg[i].ld_res = res ? ld_res[i] : 0;
@@ -1470,6 +1607,50 @@ extern "C" int bq_gemm_w8a8(const void* xq, const void* wq, const float* sx, con
   const int64_t ldys[1] = {ldy};
   return bq_gemm_w8a8_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes,
                               stream);
+}
+
+extern "C" size_t bq_lm_head_argmax_workspace_bytes(int64_t M, int64_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  return static_cast<size_t>((N + kRowTile - 1) / kRowTile) * static_cast<size_t>(M) * sizeof(uint2);
+}
+
+extern "C" int bq_lm_head_argmax(const void* xq, const void* wq, const float* sx, const float* sw,
+                                 int out_dtype, int64_t M, int64_t N, int64_t K, void* logits_or_null,
+                                 int64_t ldy, int64_t* idx_out, void* partial, size_t partial_bytes,
+                                 void* ws, size_t ws_bytes, void* stream) {
+  if (!idx_out || !partial || M <= 0 || N <= 0) return kErrBadArg;
+  if (M > g_opt_stream_max_m) return kErrUnsupported;
+  if (partial_bytes < bq_lm_head_argmax_workspace_bytes(M, N) || !aligned_to(partial, 8) ||
+      !aligned_to(idx_out, 8))
+    return kErrWorkspace;
+  ArgmaxOut am;
+  memset(&am, 0, sizeof(am));
+  am.store_logits = logits_or_null != nullptr ? 1 : 0;
+  am.partial = static_cast<uint2*>(partial);
+  const void* wqs[1] = {wq};
+  const float* sws[1] = {sw};
+  void* ys[1] = {logits_or_null};
+  const int64_t Ns[1] = {N};
+  const int64_t ldys[1] = {ldy};
+  // K is not split: every tile's logits are final inside one CTA
+  if (int rc = run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, out_dtype, ws, ws_bytes, stream,
+                           nullptr, nullptr, nullptr, 1, nullptr, nullptr, &am))
+    return rc;
+  const int tiles = (int)((N + kRowTile - 1) / kRowTile);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)M, 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_finish_kernel, am.partial, tiles, (int)M,
+                                           reinterpret_cast<long long*>(idx_out));
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return kErrLaunch; }
+  return kOk;
 }
 
 extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_gate,

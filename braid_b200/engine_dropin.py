@@ -146,6 +146,13 @@ def activate(fuse_mlp: bool = True, fuse_norms: bool = True) -> list[str]:
         _swap("braid.model.layer", "DecoderLayer", ("forward", "__call__"),
               integrate.fused_layer_forward, done)
         _swap("braid.model.gdn", "GatedDeltaNet", ("_readout",), integrate.fused_gdn_readout, done)
+        # the final norm in front of lm_head (braid/model/engine.py:263,348): the engine module
+        # holds `rms_norm` by name and uses it nowhere else
+        eng_mod = sys.modules["braid.model.engine"]
+        if ("braid.model.engine", "rms_norm") not in _SAVED:
+            _SAVED[("braid.model.engine", "rms_norm")] = eng_mod.rms_norm
+        eng_mod.rms_norm = integrate.fused_final_norm
+        done.append("braid.model.engine.rms_norm")
     return done
 
 

@@ -100,3 +100,17 @@ def fused_gdn_readout(self, z, y, B, T, dtype):
     core = Q.gated_rms_norm_quant(y.reshape(B, T, g.inner_size), z.reshape(B, T, g.inner_size),
                                   self.norm, self.cfg.rms_norm_eps, g.head_dim)
     return Q.linear(core, self.out_proj)
+
+
+def fused_final_norm(x, weight, eps):
+    """Replacement for the `rms_norm` name the engine module imported (braid/model/engine.py:29):
+    its two call sites are the final norm in front of lm_head (:263, :348).  Returns the
+    normalised tensor torch would have returned, bit for bit, but computed together with its FP8
+    codes in one launch; the codes ride along on the tensor (`quant.attach_quantized`), so the
+    `linear(h, self.lm_head)` that follows skips its quantizer when lm_head is FP8.  Anything the
+    kernel does not take runs the reference's spelling."""
+    if (not x.is_cuda or x.dtype not in Q._DTYPE_CODE or weight.dtype is not __import__("torch").float32
+            or weight.numel() != x.shape[-1]):
+        return Q.torch_rms_norm(x, weight, eps)
+    qa = Q.rms_norm_quant(x, weight, eps, keep_dense=True)
+    return Q.attach_quantized(qa.dense, qa)

@@ -473,6 +473,24 @@ class QuantizedActivation:
         return self.dense
 
 
+def attach_quantized(dense: torch.Tensor, qa: "QuantizedActivation") -> torch.Tensor:
+    """Let an ordinary tensor carry its own quantization: `linear(dense, fp8_weight)` then skips
+    the quantizer and multiplies the attached codes.  For call sites that cannot be handed a
+    `QuantizedActivation` because other code reads the tensor too (the engine's final norm,
+    braid/model/engine.py:263,348).  The attachment is ignored once the tensor has been modified
+    in place."""
+    dense._bq_quantized = (qa.q, qa.scale, dense._version)
+    return dense
+
+
+def _attached(x) -> tuple | None:
+    pre = getattr(x, "_bq_quantized", None)
+    if pre is None or pre[2] != x._version or pre[0].shape[-1] != x.shape[-1] \
+            or pre[0].numel() != x.numel():
+        return None
+    return pre
+
+
 def torch_rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
     """The reference's spelling (braid/model/norm.py:31-45): fp32 norm, one cast back."""
     return F.rms_norm(x.float(), (x.shape[-1],), gamma, eps).type_as(x)
@@ -671,6 +689,44 @@ def fp8_matmul_grouped(xq: torch.Tensor, sx: torch.Tensor, weights: Sequence[FP8
     return outs
 
 
+def lm_head_argmax(x, w: FP8Weight, return_logits: bool = False):
+    """Greedy tokens straight from the lm_head GEMM: `linear(x, w).argmax(-1)` with the per-row
+    argmax taken in the GEMM's epilogue (braid/model/engine.py:349 + braid/serve/scheduler.py:346).
+    `x` is `[..., K]` (a tensor, a tensor carrying its quantization, or a `QuantizedActivation`).
+    Returns int64 indices of shape `x.shape[:-1]`; with `return_logits` also the logits, which are
+    otherwise never written.  Exactly equal to the argmax of the logits `linear` would return."""
+    *lead, K = x.shape
+    if isinstance(x, QuantizedActivation):
+        xq, sx, dt = x.q, x.scale, x.dtype
+    else:
+        pre = _attached(x)
+        dt = x.dtype
+        xq, sx = (pre[0].reshape(-1, K), pre[1]) if pre is not None else quantize_act(x.reshape(-1, K))
+    _check_gemm_inputs(xq, sx)
+    M, N = xq.shape[0], w.data.shape[0]
+    code = _DTYPE_CODE.get(dt)
+    if M == 0 or M > 256 or code is None or w.data.shape[1] != K or not w.data.is_contiguous():
+        logits = fp8_matmul(xq, sx, w, out_dtype=dt)
+        idx = logits.argmax(-1).reshape(lead)
+        return (idx, logits.reshape(*lead, N)) if return_logits else idx
+    lib = _require_lib()
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    global _launches
+    _launches += 1                      # the second-stage reduction
+    need = int(lib.bq_lm_head_argmax_workspace_bytes(M, N))
+    partial = torch.empty(need // 8, dtype=torch.int64, device=xq.device)
+    idx = torch.empty(M, dtype=torch.int64, device=xq.device)
+    logits = torch.empty((M, N), dtype=dt, device=xq.device) if return_logits else None
+    rc = lib.bq_lm_head_argmax(xq.data_ptr(), w.data.data_ptr(), sx.data_ptr(), w.scale.data_ptr(), code,
+                               M, N, K, logits.data_ptr() if return_logits else None, N, idx.data_ptr(),
+                               partial.data_ptr(), need, _take_slot(xq.device), 16,
+                               _stream_ptr(xq.device))
+    _lib.check(rc, "lm_head_argmax")
+    idx = idx.reshape(lead)
+    return (idx, logits.reshape(*lead, N)) if return_logits else idx
+
+
 # A residual waiting for the output projection of a mixer: set by the caller of the mixer
 # (`residual_into`), taken by the first `fp8_linear` on exactly that weight.
 _PENDING_RESIDUAL: list | None = None
@@ -714,7 +770,8 @@ def fp8_linear(x: torch.Tensor, w: FP8Weight, residual: torch.Tensor | None = No
     res2 = residual.reshape(-1, N) if residual is not None else _claim_residual(w, lead, N, x.dtype)
     if isinstance(x, QuantizedActivation):
         return fp8_matmul(x.q, x.scale, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
-    xq, sx = quantize_act(x.reshape(-1, K))
+    pre = _attached(x)
+    xq, sx = (pre[0].reshape(-1, K), pre[1]) if pre is not None else quantize_act(x.reshape(-1, K))
     return fp8_matmul(xq, sx, w, out_dtype=x.dtype, residual=res2).reshape(*lead, N)
 
 

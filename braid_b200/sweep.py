@@ -101,6 +101,28 @@ def gemm_row(name, ns, k, m, dev, peaks, inner=None, reps=15, library=True):
     return row
 
 
+def lm_head_rows(dev, peaks, ms=(16, 128), vocab=248320, k=4096, reps=7):
+    """The `head` group (braid/model/engine.py:349): logits GEMM + `argmax(-1)` as the scheduler
+    runs it (braid/serve/scheduler.py:346) against the GEMM with the pick in its epilogue (no
+    logits written)."""
+    bank = _bank([vocab], k, dev, min_bytes=2 << 30, max_copies=3)
+    rows = []
+    for m in ms:
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        xq, sx = Q.quantize_act(x)
+        pre = Q.QuantizedActivation(xq, sx, x.shape, x.dtype)
+        t_logits = _time_graph(lambda i: Q.fp8_matmul(xq, sx, bank[i][0]).argmax(-1), len(bank), 3, reps)
+        t_pick = _time_graph(lambda i: Q.lm_head_argmax(pre, bank[i][0]), len(bank), 3, reps)
+        bytes_ = vocab * k + m * k
+        rows.append({"proj": "lm_head", "M": m, "logits_then_argmax_us": t_logits * 1e3,
+                     "argmax_in_epilogue_us": t_pick * 1e3, "speedup": t_logits / t_pick,
+                     "gbs": bytes_ / (t_pick * 1e-3) / 1e9,
+                     "frac_hbm": bytes_ / (t_pick * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+    del bank
+    torch.cuda.empty_cache()
+    return rows
+
+
 def quant_row(kind, m, cols, dev, peaks, reps=15):
     n_bank = max(2, min(64, (256 << 20) // (m * cols * 2)))
     if kind == "plain":
@@ -331,6 +353,11 @@ def main(args):
         # the whole quantized MLP of one layer at --rows (paired gate/up kernel + down): what the
         # ncu capture of the paired epilogue runs
         print(json.dumps(mlp_block_row(args.rows, dev, peaks, reps=3)), flush=True)
+        print(json.dumps({"device_status": Q.device_status()}), flush=True)
+        return
+    if only == "lm_head_argmax":
+        for r in lm_head_rows(dev, peaks):
+            print(json.dumps(r), flush=True)
         print(json.dumps({"device_status": Q.device_status()}), flush=True)
         return
     if only == "quant_plain":

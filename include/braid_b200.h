@@ -254,6 +254,29 @@ int bq_gemm_w8a8_residual(const void* xq, const void* wq, const float* sx, const
                           void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * lm_head with the greedy pick in its epilogue (decode regime, M <= 256):
+ *   logits = (Xq . Wq^T) * sx * sw rounded to out_dtype, idx_out[m] = argmax_n logits[m, n]
+ * with torch's conventions (lowest index among equal maxima, NaN beats everything).  Every CTA
+ * reduces its 128 vocabulary rows per batch row and writes one (value, index) pair into
+ * `partial`; a second small kernel reduces the pairs.  The logits themselves are written only
+ * when `logits_or_null` is given ([M, N], row pitch ldy); without them the 2*M*N output bytes
+ * never reach memory.  The index equals `logits.argmax(-1)` of bq_gemm_w8a8's output exactly.
+ *
+ * Replaces: `linear(h, self.lm_head)[:, 0]` of braid/model/engine.py:349 followed by
+ * `logits.argmax(-1)` of braid/serve/scheduler.py:346 (the greedy rows of `_sample_rows`).
+ *
+ *   idx_out   device, M int64
+ *   partial   device scratch, bq_lm_head_argmax_workspace_bytes(M, N) bytes, 8-byte aligned;
+ *             need not be zeroed; calls that overlap on the GPU must not share it
+ *   ws        16 bytes as for bq_gemm_w8a8
+ */
+size_t bq_lm_head_argmax_workspace_bytes(int64_t M, int64_t N);
+int bq_lm_head_argmax(const void* xq, const void* wq, const float* sx, const float* sw,
+                      int out_dtype, int64_t M, int64_t N, int64_t K, void* logits_or_null,
+                      int64_t ldy, int64_t* idx_out, void* partial, size_t partial_bytes,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/*
  * The first half of the quantized MLP in ONE launch (decode regime, M <= 256):
  *   gate = Xq.Wg^T, up = Xq.Wu^T (each rounded to the activation type as bq_gemm_w8a8 would),
  *   h = T(T(silu(gate)) * up), then amax / scale / e4m3 codes of h
@@ -399,6 +422,7 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
  * Tuning hooks used by the benchmark and tests; not needed for normal use.
  * bq_set_option("decode_split_k", v)    0 = heuristic, else force the K slices per tile
  * bq_set_option("decode_stages", v)     0 = heuristic, else cap the pipeline depth
+ * bq_set_option("decode_b_stages", v)   activation ring depth: 0 = heuristic, -1 = as the weight ring
  * bq_set_option("decode_cta_target", v) CTAs a small weight is sliced to reach (default 160)
  * bq_set_option("decode_smem_cap", v)   0 = none, else cap pipeline bytes per CTA
  * bq_set_option("stream_max_m", v)      largest M the weight-streaming kernel takes (<= 256)

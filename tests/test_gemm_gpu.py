@@ -142,6 +142,51 @@ def test_lm_head_at_full_vocabulary(Q, M):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+@pytest.mark.parametrize("M,V,K", [(1, 248320, 4096), (128, 248320, 4096), (37, 1040, 272),
+                                   (4, 4096, 256), (256, 16, 16)])
+def test_lm_head_argmax_equals_argmax_of_the_logits(Q, dt, M, V, K):
+    """braid/model/engine.py:349 + braid/serve/scheduler.py:346: the greedy token of every row,
+    taken in the GEMM's epilogue, equals `linear(h, lm_head).argmax(-1)` exactly -- ties between
+    equal logits (bf16 rounding makes them common, and duplicated vocabulary rows force them)
+    go to the lowest index; the logits, when asked for, are the plain GEMM's bits."""
+    if dt is not torch.bfloat16 and V > 5000:
+        pytest.skip("dtype variants on the small shapes")
+    g = torch.Generator(device="cuda").manual_seed(V + M)
+    w = (torch.randn(V, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    fw = Q.quantize_weight(w)
+    del w
+    if V >= 1040:      # duplicated rows: exact ties far apart in the vocabulary (different tiles)
+        codes = fw.data.view(torch.uint8)
+        codes[V - 7] = codes[3]
+        codes[V // 2 + 1] = codes[V // 2 - 300]
+    x = randn_cpu((M, K), seed=M + K, dtype=dt).cuda()
+    if V >= 1040:      # make the duplicated rows the winners of two batch rows
+        lut = fw.data[3].to(dt)
+        x[0] = lut * 8
+        if M > 1:
+            x[M - 1] = fw.data[V // 2 - 300].to(dt) * 8
+    want_logits = Q.linear(x, fw)
+    want = want_logits.argmax(-1)
+    n0 = Q.launch_count()
+    got = Q.lm_head_argmax(x, fw)
+    assert Q.launch_count() - n0 == 3                # quantizer, GEMM with the pick, tiny reduction
+    assert got.dtype is torch.int64 and got.shape == (M,)
+    assert torch.equal(got, want), (got[:4], want[:4])
+    if V >= 1040:
+        assert int(got[0]) == 3                       # the lower of the two tied indices
+    idx2, logits = Q.lm_head_argmax(x, fw, return_logits=True)
+    assert torch.equal(idx2, want) and torch.equal(logits, want_logits)
+    # a NaN in a row makes every logit of that row NaN: index 0, as torch picks
+    if M >= 4:
+        x[2, 5] = float("nan")
+        assert torch.equal(Q.lm_head_argmax(x, fw), Q.linear(x, fw).argmax(-1))
+    # leading dims and a tensor that carries its quantization
+    x3 = x.reshape(M, 1, K)
+    assert Q.lm_head_argmax(x3, fw).shape == (M, 1)
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
 def test_prefill_store_paths_agree_and_stay_in_bounds(Q, dt):
     """The prefill epilogue hands 128-byte row pieces to TMA stores when the output can be
     described to TMA (16-byte aligned base and row pitch) and writes the same staged pieces with
