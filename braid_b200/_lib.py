@@ -71,6 +71,9 @@ SIGNATURES = {
     "bq_lm_head_argmax_workspace_bytes": (_sz, [_i64, _i64]),
     "bq_lm_head_argmax": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _sz,
                                  _vp, _sz, _vp]),
+    "bq_gate_up_silu_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _i64, _vp,
+                                    _vp, _sz, _vp]),
+    "bq_cast_act": (_int, [_vp, _int, _i64, _vp, _vp, _vp]),
     "bq_read_device_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "bq_set_option": (_int, [ctypes.c_char_p, _i64]),
     "bq_last_gemm_launch": (_int, [ctypes.POINTER(_i64)]),

@@ -81,6 +81,8 @@ struct Segment {
 // repacked or copied).
 struct PairSilu {
   int on;
+  int prefill;             // M > 256: the CTA-pair kernel writes h itself ([M, I], activation type)
+                           // and the scale of h; the codes are a separate cast pass
   const void* wq_up;       // device: the up weight [I, K] (segment 0's weight pointer is the gate weight)
   const float* sw_up;      // device: dequant scale of the up half (seg.sw is the gate half's)
   uint8_t* hq;             // device: e4m3 codes of h, [M, ld_hq]
@@ -843,20 +845,21 @@ __global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, u
 // a lone CTA with a 128 x 256 tile.  Warp roles per CTA: 0 = TMA producer, 1 = MMA issuer
 // (leader CTA only), 2..5 = epilogue.
 //
-// Epilogue: a warp owns 32 rows of the CTA's 128 x 256 accumulator (its TMEM lane quarter).
-// It walks them in pieces of 128 bytes of output per row (64 columns of a 16-bit type, 32 of
-// fp32): tcgen05.ld -> scale -> cast -> one 32-row x 128-byte box in shared memory, written
-// in the 128-byte swizzle pattern so that neither the lane-per-row writes nor the reader
-// meet bank conflicts -> one TMA store of the box (clipped at M and N by the tensor map),
-// two boxes per warp in flight.  Outputs whose base or row pitch is not 16-byte aligned
+// Epilogue: eight warps; a warp owns 32 rows (its TMEM lane quarter) and one half of the
+// columns of the CTA's 128 x 256 accumulator.  It walks them in pieces of 128 bytes of output
+// per row (64 columns of a 16-bit type, 32 of fp32): tcgen05.ld -> scale -> cast -> one 32-row x
+// 128-byte box in shared memory, written in the 128-byte swizzle pattern so that neither the
+// lane-per-row writes nor the reader meet bank conflicts -> one TMA store of the box (clipped
+// at M and N by the tensor map); the next piece waits until the store has read the box.  Outputs whose base or row pitch is not 16-byte aligned
 // cannot be described to TMA: the same staged box is then written with coalesced 128-byte
 // row segments by the warp itself.
 constexpr int kPairStageBytes = 2 * kATileBytes;    // 16 KB activation rows + 16 KB weight rows
 constexpr int kPairStages = 6;
 constexpr int kPairTile = 256;
-constexpr int kTileThreads = 192;
+constexpr int kPairEpiWarps = 8;                    // two per TMEM lane quarter
+constexpr int kTileThreads = 64 + 32 * kPairEpiWarps;
 constexpr int kStoreBoxBytes = 32 * 128;            // 32 rows x 128 bytes
-constexpr int kPairStagingBytes = 4 * 2 * kStoreBoxBytes;   // four epilogue warps, two boxes each
+constexpr int kPairStagingBytes = kPairEpiWarps * kStoreBoxBytes;   // one box per epilogue warp
 
 // Order in which a weight's 256 x 256 tiles are visited: bands of kRasterM tile rows, inside a
 // band the row index runs fastest.  The ~74 tiles in flight at a time then cover about
@@ -908,31 +911,63 @@ __device__ __forceinline__ void cast16(const uint32_t (&r)[16], float scale, int
   }
 }
 
-// The epilogue of one warp for one tile: 32 rows x 256 columns.
-template <int ES>
+// h = T(T(silu(gate)) * up) of 16 columns from the 16 gate and the 16 up accumulator values of
+// the same columns, each first rounded to T as the plain GEMM would have stored it
+// (braid/model/mlp.py:46-48), as 16-byte pieces; returns max |h| folded into `mx`.
+template <typename T>
+__device__ __forceinline__ void silu16(const uint32_t (&g)[16], const uint32_t (&u)[16], float sg,
+                                       float su, uint4 (&out)[sizeof(T) == 4 ? 4 : 2], float& mx) {
+  using namespace bq::qd;
+  T h[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float gg = widen(narrow<T>(__uint_as_float(g[i]) * sg));
+    const float uu = widen(narrow<T>(__uint_as_float(u[i]) * su));
+    const T sl = narrow<T>(__fdiv_rn(gg, 1.0f + expf(-gg)));
+    h[i] = narrow<T>(widen(sl) * uu);
+    mx = nan_max(mx, fabsf(widen(h[i])));
+  }
+  const uint4* raw = reinterpret_cast<const uint4*>(h);
+#pragma unroll
+  for (int q = 0; q < (sizeof(T) == 4 ? 4 : 2); ++q) out[q] = raw[q];
+}
+
+// The epilogue of one warp for one tile: 32 rows x 256 accumulator columns.  SILU: the tile's
+// columns [0,128) are gate and [128,256) up of the same 128 output columns, and the output is
+// h = silu(gate) * up (128 columns); max |h| is folded into `mx`.
+template <int ES, bool SILU>
 __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Segment& seg,
                                                    const CUtensorMap* ymap, bool use_tma,
-                                                   uint32_t taddr, float scale, int m_row0, int n0,
-                                                   uint8_t* stage, uint32_t stage_addr, int lane,
-                                                   int& box_iter) {
+                                                   uint32_t taddr, float scale, float scale_up,
+                                                   int m_row0, int n0, uint8_t* box,
+                                                   uint32_t box_addr, int lane, int col_half,
+                                                   float& mx) {
   constexpr int kCols = 128 / ES;              // output columns per 128-byte piece
   constexpr int kPieces = ES == 4 ? 4 : 2;     // 16-byte pieces per 16 accumulator columns
-  for (int c = 0; c < kPairTile; c += kCols, ++box_iter) {
-    // pieces beyond this weight's rows are never stored (warp-uniform).  They must not take a
-    // box either: the wait below counts committed stores, one per box in use.
+  constexpr int kOutCols = SILU ? kPairTile / 2 : kPairTile;
+  const int c_end = (col_half + 1) * (kOutCols / 2);
+  for (int c = col_half * (kOutCols / 2); c < c_end; c += kCols) {
+    // pieces beyond this weight's rows are never stored (warp-uniform)
     if ((n0 + c) >= seg.n) break;
-    const int buf = box_iter & 1;
-    uint8_t* const box = stage + buf * kStoreBoxBytes;
-    // the TMA store that read this box two pieces ago must have finished reading it
-    if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    // the TMA store of the previous piece must have finished reading the box
+    if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < kCols; j += 16) {
       uint32_t r[16];
       tmem_ld16(taddr + c + j, r);          // warp-collective: no divergence before it
-      tmem_ld_wait();
       uint4 v[kPieces];
-      cast16<ES>(r, scale, p.out_dtype, v);
+      if constexpr (SILU) {
+        uint32_t up[16];
+        tmem_ld16(taddr + kPairTile / 2 + c + j, up);
+        tmem_ld_wait();
+        if constexpr (ES == 4) silu16<float>(r, up, scale, scale_up, v, mx);
+        else if (p.out_dtype == BQ_DTYPE_BF16) silu16<__nv_bfloat16>(r, up, scale, scale_up, v, mx);
+        else silu16<__half>(r, up, scale, scale_up, v, mx);
+      } else {
+        tmem_ld_wait();
+        cast16<ES>(r, scale, p.out_dtype, v);
+      }
 #pragma unroll
       for (int q = 0; q < kPieces; ++q) {
         const int piece = (j * ES) / 16 + q;                  // 0..7 along the 128-byte row
@@ -943,7 +978,7 @@ __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Se
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(ymap, stage_addr + buf * kStoreBoxBytes, n0 + c, m_row0);
+        tma_store_2d(ymap, box_addr, n0 + c, m_row0);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     } else {
@@ -993,6 +1028,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
   const int rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + kPairTile - 1) / kPairTile;
+  const bool silu = p.pair.on != 0;                       // gate/up tiles, h = silu(gate) * up out
+  const int n_step = silu ? kPairTile / 2 : kPairTile;    // output columns per tile
+  float* const s_amax = reinterpret_cast<float*>(base_ptr + kPairStages * kPairStageBytes + 512);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tm_x);
@@ -1003,7 +1041,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 8);    // four epilogue warps in each CTA of the pair
+      mbar_init(acc_empty(b), 2 * kPairEpiWarps);    // the epilogue warps of both CTAs of the pair
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -1028,15 +1066,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
         const int sg = find_segment(p, t);
         const int local = t - p.seg[sg].tile_begin;
         int m_idx, n_idx;
-        pair_tile_coords(local, m_tiles, (p.seg[sg].n + kPairTile - 1) / kPairTile, m_idx, n_idx);
+        pair_tile_coords(local, m_tiles, (p.seg[sg].n + n_step - 1) / n_step, m_idx, n_idx);
         const int m0 = m_idx * kPairTile + rank * kRowTile;
-        const int n0 = n_idx * kPairTile + rank * kRowTile;
+        // plain: this CTA's half of the tile's 256 weight rows; SiLU form: the leader loads 128
+        // gate rows, its peer the 128 up rows of the same output columns
+        const int n0 = silu ? n_idx * kRowTile : n_idx * kPairTile + rank * kRowTile;
+        const CUtensorMap* const w_map = silu ? &tm_w.w[rank] : &tm_w.w[sg];
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kPairStages, use = it / kPairStages;
           if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
           tma_load_2d_pair(a_tile(s), &tm_x, full_bar(s), kb * kBK, m0, pol);
-          tma_load_2d_pair(b_tile(s), &tm_w.w[sg], full_bar(s), kb * kBK, n0, pol);
+          tma_load_2d_pair(b_tile(s), w_map, full_bar(s), kb * kBK, n0, pol);
         }
       }
       if (!ok) *abort_flag = 1;
@@ -1074,10 +1115,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
     __syncwarp();
   } else {
-    const int quad = warp & 3;
-    int tile_iter = 0, box_iter = 0;
+    const int quad = warp & 3;                   // TMEM lanes [32 * quad, +32): rows of the tile
+    const int col_half = (warp - 2) >> 2;        // which half of the columns this warp stores
+    int tile_iter = 0;
     bool ok = true;
-    uint8_t* const stage = staging + quad * 2 * kStoreBoxBytes;
+    float h_max = 0.0f;                          // SiLU form: max |h| over everything this thread wrote
+    uint8_t* const stage = staging + (warp - 2) * kStoreBoxBytes;
     const uint32_t stage_addr = smem_u32(stage);
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty(0), 0);
     const uint32_t leader_acc_empty1 = map_to_cta(acc_empty(1), 0);
@@ -1087,20 +1130,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
       const Segment seg = p.seg[sg];
       const int local = t - seg.tile_begin;
       int m_idx, n_idx;
-      pair_tile_coords(local, m_tiles, (seg.n + kPairTile - 1) / kPairTile, m_idx, n_idx);
+      pair_tile_coords(local, m_tiles, (seg.n + n_step - 1) / n_step, m_idx, n_idx);
       const int m0 = m_idx * kPairTile + rank * kRowTile;
-      const int n0 = n_idx * kPairTile;
+      const int n0 = n_idx * n_step;
       if (!mbar_wait(acc_full(b), use_b & 1)) { ok = false; break; }
       tc_fence_after();
-      const float scale = __ldg(p.sx) * __ldg(seg.sw);
+      const float sx = __ldg(p.sx);
+      const float scale = sx * __ldg(seg.sw);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + b * kPairTile;
       const bool use_tma = seg.y_tma != 0;
-      if (p.out_dtype == BQ_DTYPE_F32)
-        pair_epilogue_rows<4>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, m0 + quad * 32, n0, stage,
-                              stage_addr, lane, box_iter);
-      else
-        pair_epilogue_rows<2>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, m0 + quad * 32, n0, stage,
-                              stage_addr, lane, box_iter);
+      if (silu) {
+        const float scale_up = sx * __ldg(p.pair.sw_up);
+        if (p.out_dtype == BQ_DTYPE_F32)
+          pair_epilogue_rows<4, true>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, scale_up,
+                                      m0 + quad * 32, n0, stage, stage_addr, lane, col_half, h_max);
+        else
+          pair_epilogue_rows<2, true>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, scale_up,
+                                      m0 + quad * 32, n0, stage, stage_addr, lane, col_half, h_max);
+      } else if (p.out_dtype == BQ_DTYPE_F32) {
+        pair_epilogue_rows<4, false>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
+                                     n0, stage, stage_addr, lane, col_half, h_max);
+      } else {
+        pair_epilogue_rows<2, false>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
+                                     n0, stage, stage_addr, lane, col_half, h_max);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(b == 0 ? leader_acc_empty0 : leader_acc_empty1);
@@ -1109,6 +1162,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
     if (!ok) *abort_flag = 1;
+    if (silu) {
+      // max |h| of the launch: warps -> CTA -> one atomicMax per CTA on the bit pattern (exact
+      // and order-free; NaN patterns sort on top); the CTA that arrives last turns the result into
+      // the scale of h and returns the scratch words to zero
+      using namespace bq::qd;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        h_max = nan_max(h_max, __shfl_xor_sync(0xffffffffu, h_max, off));
+      if (lane == 0) s_amax[warp - 2] = h_max;
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kPairEpiWarps) : "memory");      // the epilogue warps
+      if (warp == 2 && lane == 0) {
+        float w = s_amax[0];
+#pragma unroll
+        for (int i = 1; i < kPairEpiWarps; ++i) w = nan_max(w, s_amax[i]);
+        unsigned int* const words = p.pair.words;
+        atomicMax(&words[0], __float_as_uint(w));
+        __threadfence();
+        const unsigned int old = atomicAdd(&words[1], 1u);
+        if (old == gridDim.x - 1) {
+          __threadfence();
+          const unsigned int bits = atomicMax(&words[0], 0u);
+          p.pair.sh[0] = scale_from_amax(__uint_as_float(bits));
+          words[0] = 0u;
+          words[1] = 0u;
+          __threadfence();
+        }
+      }
+    }
   }
 
   tc_fence_before();
@@ -1468,7 +1549,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     const bool is_dense = dn != nullptr && dn->kind[i] != 0;
     if (!wq[i] || (!sw[i] && !is_dense) || N[i] <= 0) return kErrBadArg;
     if (N[i] % 16 || !aligned_to(wq[i], 16)) return kErrUnsupported;
-    if (pair == nullptr && push == nullptr && !(am != nullptr && !am->store_logits)) {   // forms that write y
+    if ((pair == nullptr || pair->prefill) && push == nullptr &&
+        !(am != nullptr && !am->store_logits)) {   // forms that write y
       if (!y[i]) return kErrBadArg;
       if (ldy[i] < N[i] || ldy[i] % 4 || !aligned_to(y[i], out_align)) return kErrUnsupported;
     }
@@ -1480,7 +1562,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     if (!dn->x || (dn->dtype != BQ_DTYPE_BF16 && dn->dtype != BQ_DTYPE_F16)) return kErrBadArg;
     if (!aligned_to(dn->x, 16)) return kErrUnsupported;
   }
-  if (pair && !stream_path) return kErrUnsupported;   // decode-regime form only
+  if (pair && stream_path == (pair->prefill != 0)) return kErrUnsupported;   // each form has its regime
   if (pair && (res || n_seg != 1)) return kErrBadArg;
   if (push) {
     if (!stream_path) return kErrUnsupported;
@@ -1525,14 +1607,14 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
 
   const bool pair_path = !stream_path;
   const int w_box_rows = kRowTile;
-  const int tile_n = pair_path ? kPairTile : kRowTile;
+  const int tile_n = pair_path ? ((pair && pair->prefill) ? kPairTile / 2 : kPairTile) : kRowTile;
   p.m_tiles = pair_path ? (int)((M + kPairTile - 1) / kPairTile) : (int)((M + kRowTile - 1) / kRowTile);
   OutMaps ymaps;
   memset(&ymaps, 0, sizeof(ymaps));
   int tiles = 0;
   for (int i = 0; i < n_seg; ++i) {
     p.seg[i].sw = sw[i];
-    const bool no_y = pair || push || (am != nullptr && !am->store_logits);
+    const bool no_y = (pair && !pair->prefill) || push || (am != nullptr && !am->store_logits);
     p.seg[i].y = no_y ? nullptr : y[i];
     p.seg[i].ldy = no_y ? 0 : ldy[i];
     p.seg[i].split_forced = split_forced;
@@ -1550,7 +1632,12 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
       p.seg[i].y_tma = aligned_to(y[i], 16) && (ldy[i] * es) % 16 == 0 &&
                        make_out_map(&ymaps.y[i], y[i], M, N[i], ldy[i], out_dtype) == kOk;
     }
-    if (pair) {
+    if (pair && pair->prefill) {
+      // two maps over the two weights, 128-row boxes: one CTA of a pair loads gate rows, the other
+      // the up rows of the same output columns
+      if (int rc = make_map(&maps.w[0], wq[0], N[0], K, kRowTile)) return rc;
+      if (int rc = make_map(&maps.w[1], pair->wq_up, N[0], K, kRowTile)) return rc;
+    } else if (pair) {
       // two maps over the two weights, 64-row boxes: the kernel puts a tile together from both
       if (int rc = make_map(&maps.w[0], wq[0], N[0] / 2, K, kRowTile / 2)) return rc;
       if (int rc = make_map(&maps.w[1], pair->wq_up, N[0] / 2, K, kRowTile / 2)) return rc;
@@ -1678,6 +1765,28 @@ extern "C" int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const
   const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight((int)I, k_blocks) : 1;
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
                      nullptr, nullptr, &pair, split);
+}
+
+extern "C" int bq_gate_up_silu_w8a8(const void* xq, const float* sx, const void* wq_gate,
+                                    const void* wq_up, const float* sw_gate, const float* sw_up,
+                                    int64_t M, int64_t I, int64_t K, int act_dtype, void* h_out,
+                                    int64_t ld_h, float* sh_out, void* ws, size_t ws_bytes,
+                                    void* stream) {
+  if (!wq_gate || !wq_up || !sw_gate || !sw_up || !h_out || !sh_out || I <= 0) return kErrBadArg;
+  if (I % 16 || !aligned_to(wq_up, 16)) return kErrUnsupported;
+  PairSilu pair;
+  memset(&pair, 0, sizeof(pair));
+  pair.prefill = 1;
+  pair.wq_up = wq_up;
+  pair.sw_up = sw_up;
+  pair.sh = sh_out;
+  const void* wqs[1] = {wq_gate};
+  const float* sws[1] = {sw_gate};
+  void* ys[1] = {h_out};
+  const int64_t Ns[1] = {I};
+  const int64_t ldys[1] = {ld_h};
+  return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
+                     nullptr, nullptr, &pair);
 }
 
 namespace {

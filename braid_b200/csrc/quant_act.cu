@@ -432,6 +432,22 @@ extern "C" int bq_silu_mul_cast(const void* gate, const void* up, int dtype, int
   return dispatch_phase<kSiluMul, kCastOnly>(dtype, p, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bq_cast_act(const void* x, int dtype, int64_t n, const float* scale, void* q_out,
+                           void* stream) {
+  if (x == nullptr || q_out == nullptr || scale == nullptr || n <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (!aligned_to(x, 16) || !aligned_to(q_out, 8)) return bq::kErrUnsupported;
+  if (n / kGroup >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = x;
+  p.q = static_cast<uint8_t*>(q_out);
+  p.scale = const_cast<float*>(scale);   // read only in this phase
+  p.n_groups = static_cast<unsigned int>(n / kGroup);
+  p.tail = static_cast<unsigned int>(n % kGroup);
+  p.groups_per_row = 1;
+  return dispatch_phase<kPlain, kCastOnly>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t rows,
                                      int64_t cols, int64_t ld_o, int64_t ld_gate, int64_t chunk,
                                      int64_t chunk_stride, void* q_out, float* scale_out, void* ws,

@@ -933,6 +933,50 @@ def gate_up_silu_quant(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: 
     return hq, sh
 
 
+def cast_act(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 codes of `x` under a scale decided elsewhere (a `[1, 1]` fp32 device tensor): the
+    cast half of `quantize_act`."""
+    _check_cuda(x, "cast_act")
+    code = _DTYPE_CODE.get(x.dtype)
+    if _quantizers_off() or code is None or not x.is_contiguous() or x.data_ptr() % 16 or not x.numel():
+        return (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    lib = _require_lib()
+    global _launches
+    _launches += 1
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    _lib.check(lib.bq_cast_act(x.data_ptr(), code, x.numel(), scale.data_ptr(), q.data_ptr(),
+                               _stream_ptr(x.device)), "cast_act")
+    return q
+
+
+def gate_up_silu(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
+                 act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor] | None:
+    """`h = F.silu(xq @ gate^T) * (xq @ up^T)` and the quantization scale of h in ONE launch at
+    prefill sizes (M > 256): gate and up never reach memory, SiLU*mul runs in the GEMM's epilogue
+    (braid/model/mlp.py:46-48).  Returns `(h [M, I], scale [1, 1])`, bit-identical to the separate
+    GEMMs, `F.silu(gate) * up` and `_act_scale(h)`; `None` when not applicable."""
+    M, K = xq.shape
+    code = _DTYPE_CODE.get(act_dtype)
+    if not _PAIR_MLP or _quantizers_off() or code is None or M <= 256:
+        return None
+    I = gate.data.shape[0]
+    if (up.data.shape != gate.data.shape or I % 16 or gate.data.shape[1] != K
+            or not gate.data.is_contiguous() or not up.data.is_contiguous()):
+        return None
+    lib = _require_lib()
+    h = torch.empty((M, I), dtype=act_dtype, device=xq.device)
+    sh = torch.empty((1, 1), dtype=torch.float32, device=xq.device)
+    if not xq.is_contiguous():
+        xq = xq.contiguous()
+    rc = lib.bq_gate_up_silu_w8a8(xq.data_ptr(), sx.data_ptr(), gate.data.data_ptr(), up.data.data_ptr(),
+                                  gate.scale.data_ptr(), up.scale.data_ptr(), M, I, K, code, h.data_ptr(),
+                                  I, sh.data_ptr(), _take_slot(xq.device), 16, _stream_ptr(xq.device))
+    if rc == _lib.BQ_ERR_UNSUPPORTED:
+        return None
+    _lib.check(rc, "gate_up_silu")
+    return h, sh
+
+
 # ---------------------------------------------------------------------------
 # column-parallel forms: the GEMM epilogue stores into every rank's gathered buffer
 # ---------------------------------------------------------------------------
@@ -999,8 +1043,10 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
     """The quantized branch of `MLP.forward` (braid/model/mlp.py:44-49) in 3 launches at decode
     sizes: quantize(x) -> gate and up as one GEMM (tiles put together from both weights) with
     SiLU*mul and the quantization of h in its epilogue -> down GEMM (with `residual` added in its epilogue).
-    Larger M, unpaired shapes or `set_paired_mlp(False)`: 4 launches (quantize -> grouped GEMM
-    writing gate|up into one `[M, 2I]` buffer -> SiLU*mul inside the quantizer of h -> down).
+    Larger M: 4 launches (quantize -> gate and up as one CTA-pair GEMM that writes h = silu(gate)*up
+    and its scale -> cast of h -> down).  Unpaired shapes or `set_paired_mlp(False)`: 4 launches
+    (quantize -> grouped GEMM writing gate|up into one `[M, 2I]` buffer -> SiLU*mul inside the
+    quantizer of h -> down).
     Either way the result is bit-identical to the reference's nine-plus-kernel sequence built
     from the same primitives.
     """
@@ -1017,6 +1063,14 @@ def mlp_forward(x: torch.Tensor, gate_proj: FP8Weight, up_proj: FP8Weight,
             y = fp8_matmul(paired[0], paired[1], down_proj, out_dtype=x.dtype, residual=res2)
             return y.reshape(*lead, down_proj.shape[0])
         pre = QuantizedActivation(xq, sx, x.shape, x.dtype)     # do not quantize twice
+    if _PAIR_MLP and M > 256 and x.device.type == "cuda":
+        xq, sx = (pre.q, pre.scale) if pre is not None else quantize_act(x2)
+        fused = gate_up_silu(xq, sx, gate_proj, up_proj, x.dtype)
+        if fused is not None:
+            h, sh = fused
+            y = fp8_matmul(cast_act(h, sh), sh, down_proj, out_dtype=x.dtype, residual=res2)
+            return y.reshape(*lead, down_proj.shape[0])
+        pre = QuantizedActivation(xq, sx, x.shape, x.dtype)
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     halves = (gu[:, :I], gu[:, I:])
     xq, sx = (pre.q, pre.scale) if pre is not None else quantize_act(x2)

@@ -277,6 +277,32 @@ int bq_lm_head_argmax(const void* xq, const void* wq, const float* sx, const flo
                       void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The first half of the quantized MLP at prefill sizes (M > 256), on the CTA-pair kernel: every
+ * 256-column MMA tile holds 128 gate rows and the 128 up rows of the same output columns (one
+ * CTA of the pair loads each, from the two weights where they lie), and the epilogue writes
+ *   h = T(T(silu(T(gate))) * T(up))      [M, I] of the activation type, row pitch ld_h
+ * instead of gate and up, together with the scale of h (max |h| over the launch, taken with
+ * one atomicMax per CTA; the CTA that finishes last publishes max(amax/448, 1e-12) to sh_out).
+ * bq_cast_act then turns h into codes under that scale.  h, scale and codes are bit-identical
+ * to bq_gemm_w8a8_grouped(gate, up) + bq_silu_mul_quant, with a third of their memory traffic
+ * and the SiLU arithmetic done once, inside the GEMM's otherwise idle epilogue warps.
+ *
+ * Replaces: braid/model/mlp.py:46-48 and the scale half of the `quantize_act` of :49.
+ *   ws   16 bytes, zero before the first call, self-resetting
+ * Returns BQ_ERR_UNSUPPORTED for M <= 256 (use bq_gate_up_silu_quant_w8a8).
+ */
+int bq_gate_up_silu_w8a8(const void* xq, const float* sx, const void* wq_gate, const void* wq_up,
+                         const float* sw_gate, const float* sw_up, int64_t M, int64_t I, int64_t K,
+                         int act_dtype, void* h_out, int64_t ld_h, float* sh_out, void* ws,
+                         size_t ws_bytes, void* stream);
+
+/*
+ * e4m3 codes of x under a scale decided elsewhere: q = e4m3(clamp(x / *scale, +-448)), the cast
+ * half of bq_quantize_act (braid/model/quant.py:229).  No scratch, no grid-wide wait.
+ */
+int bq_cast_act(const void* x, int dtype, int64_t n, const float* scale, void* q_out, void* stream);
+
+/*
  * The first half of the quantized MLP in ONE launch (decode regime, M <= 256):
  *   gate = Xq.Wg^T, up = Xq.Wu^T (each rounded to the activation type as bq_gemm_w8a8 would),
  *   h = T(T(silu(gate)) * up), then amax / scale / e4m3 codes of h

@@ -531,6 +531,34 @@ def test_paired_gate_up_epilogue_equals_the_separate_kernels(Q, dt, M, I, K):
     assert Q.device_status() == 0
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+@pytest.mark.parametrize("M,I,K", [(300, 1024, 512), (1000, 12288, 4096), (2048, 1536, 4096),
+                                   (4100, 272, 1040)],
+                         ids=["small", "9B", "shard_of_8", "ragged"])
+def test_prefill_gate_up_silu_equals_the_separate_kernels(Q, dt, M, I, K):
+    """M > 256: h = silu(gate) * up and its scale written by the CTA-pair GEMM's epilogue, then
+    `cast_act`, against the grouped GEMM + torch's SiLU*mul + the quantizer: h, scale and codes
+    bit for bit (three activation types, I off the tile grid, ragged M)."""
+    if dt is not torch.bfloat16 and (M, I) not in ((300, 1024), (4100, 272)):
+        pytest.skip("dtype variants on two shapes")
+    x = randn_cpu((M, K), seed=M + I, dtype=dt).cuda()
+    gate = Q.quantize_weight(randn_cpu((I, K), seed=1, scale=0.02).cuda())
+    up = Q.quantize_weight(randn_cpu((I, K), seed=2, scale=0.05).cuda())
+    xq, sx = Q.quantize_act(x)
+    g, u = Q.fp8_matmul_grouped(xq, sx, (gate, up), out_dtype=dt)
+    h_ref = F.silu(g) * u
+    hq_ref, sh_ref = Q.quantize_act(h_ref)
+    got = Q.gate_up_silu(xq, sx, gate, up, dt)
+    assert got is not None and Q.last_gemm_launch()["kernel"] == "pair"
+    h, sh = got
+    assert torch.equal(h, h_ref), f"{int((h != h_ref).sum())} of {h.numel()} h values differ"
+    assert torch.equal(sh, sh_ref), f"scale {sh.item():.9e} vs {sh_ref.item():.9e}"
+    assert torch.equal(Q.cast_act(h, sh).view(torch.uint8), hq_ref.view(torch.uint8))
+    h2, sh2 = Q.gate_up_silu(xq, sx, gate, up, dt)          # the scratch words were returned to zero
+    assert torch.equal(h2, h) and torch.equal(sh2, sh)
+    assert Q.device_status() == 0
+
+
 def test_paired_mlp_equals_the_four_launch_mlp_and_replays(Q):
     H, I = 4096, 12288
     mk = lambda n, k, s: Q.quantize_weight(randn_cpu((n, k), seed=s, scale=0.02).cuda())  # noqa: E731
