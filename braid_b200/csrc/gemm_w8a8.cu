@@ -8,7 +8,7 @@
 //
 // Two kernels, chosen by M:
 //
-//  * gemm_stream_kernel (M <= 256, the decode regime; HBM-bound, judged in GB/s).
+//  * gemm_stream_kernel (M <= 256, the decode regime; HBM-bound, measured in GB/s).
 //    Operands are swapped: 128 WEIGHT rows sit on the MMA M side and the (padded)
 //    batch on the MMA N side, so a tile streams 128 x K weight bytes whatever the
 //    batch is.  One CTA per (row tile, K slice); the K slices of a tile form a
@@ -18,7 +18,7 @@
 //    one activation (q/k/v, qkv/z, gate/up) go in one launch, each segment with
 //    its own scale.
 //
-//  * gemm_pair_kernel (M > 256, the prefill regime; tensor-bound, judged in
+//  * gemm_pair_kernel (M > 256, the prefill regime; tensor-bound, measured in
 //    TFLOP/s).  Persistent, warp-specialised CTA pairs (cta_group::2): one TMA
 //    producer warp, one MMA issuer warp, four epilogue warps; 256x256 output
 //    tiles; two 256-column accumulators in tensor memory so a tile's epilogue

@@ -118,11 +118,12 @@ class ProjectionSet:
         return total
 
     # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_stream_kernel launch at 128 rows,
-    # measured with ncu on a 2-layer stack (weights larger than L2), per launch shape; the ratio
-    # to the shape's algorithmic bytes carries over to other row counts only roughly, so other row
-    # counts use the mean ratio.
+    # measured with ncu on a 4-layer stack (weights larger than L2), per launch shape: every
+    # weight byte and the activation codes cross HBM once; the outputs are still in L2 when the
+    # kernel ends, so they do not show.  Other row counts use the mean measured/algorithmic ratio.
     MEASURED_TRAFFIC_M128 = {
-        ("qkv", "z"): 51.02e6, ("out",): 17.37e6, ("gate", "up"): 104.74e6,
+        ("qkv", "z"): 50.98e6, ("out",): 17.39e6, ("gate", "up"): 101.45e6, ("down",): 51.99e6,
+        ("q", "k", "v"): 42.57e6,
     }
 
     def gemm_measured_traffic_bytes(self) -> dict:
@@ -153,7 +154,7 @@ class ProjectionSet:
                     total += mean_ratio * alg
         n = 4 * len(self.layers)
         return {"bytes": total,
-                "source": f"ncu dram__bytes_read+write per launch shape at 128 rows on a 2-layer stack "
+                "source": f"ncu dram__bytes_read+write per launch shape at 128 rows on a 4-layer stack "
                           f"({covered} of {n} launches of this step have a measured shape; the others use "
                           f"the mean measured/algorithmic ratio {mean_ratio:.3f})"}
 
