@@ -91,7 +91,9 @@ int bq_quantize_act(const void* x, int dtype, int64_t n, void* q_out, float* sca
  *  - Limit: n <= BQ_STATIC_MAX_ELEMENTS, otherwise BQ_ERR_TOO_LARGE and nothing
  *    is launched.  Alignment rules as for bq_quantize_act.
  *  - The first call on each device looks up the array's device address (once,
- *    with that device current).  Make that first call before any stream capture.
+ *    with that device current).  Make that first call before any stream capture,
+ *    and from one thread: the lookup is cached without a lock, so two threads
+ *    must not make a device's first call at the same time.
  *  - All calls on a device share the one array: calls that may overlap on the
  *    GPU (different streams without ordering) race on it and give wrong scales.
  *    Each call clears the words that must start at zero, in stream order.
