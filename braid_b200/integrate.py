@@ -50,8 +50,9 @@ def adopt_weight(w) -> Q.FP8Weight:
 
 
 def fused_mlp_forward(self, x, residual=None):
-    """Replacement for `MLP.forward` (braid/model/mlp.py:34-49): quantized branch in 4 launches;
-    `residual`, if given, is added in the epilogue of the down projection."""
+    """Replacement for `MLP.forward` (braid/model/mlp.py:34-49): the quantized branch as
+    `quant.mlp_forward` runs it (3 launches at decode sizes, 4 at prefill sizes); `residual`, if
+    given, is added in the epilogue of the down projection."""
     import torch.nn.functional as F
     if not isinstance(self.gate_proj, Q.FP8Weight):
         y = F.linear(F.silu(F.linear(x, self.gate_proj)) * F.linear(x, self.up_proj), self.down_proj)
