@@ -426,14 +426,16 @@ __device__ __forceinline__ float silu_pair_rows(const EpilogueArgs& e, float sca
 
 // After the grid-wide scale is known: cast the parked h of this CTA's rows and write the codes.
 template <typename T>
-__device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const float* part, float sc,
+__device__ __forceinline__ void silu_pair_emit(const EpilogueArgs& e, const float* part, float scale,
                                                uint8_t* hq, long long ld_hq, int col0) {
   using namespace bq::qd;
+  const ScaleDiv sc(scale);
   const int hcol = (e.lane & 15) * 4 + (e.lane >= 16 ? 2 : 0);
   for (int m = e.m_begin + e.warp; m < e.m_end; m += kStreamWarps) {
     const T* hrow = reinterpret_cast<const T*>(part + m * kRowTile);
-    const float2 f = make_float2(quant_one(widen(hrow[hcol]), sc), quant_one(widen(hrow[hcol + 1]), sc));
-    const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+    float f[2] = {widen(hrow[hcol]), widen(hrow[hcol + 1])};
+    divide_group<2, true>(sc, f);   // the scale is that of these very values
+    const uint32_t pair = __nv_cvt_float2_to_fp8x2(make_float2(f[0], f[1]), __NV_SATFINITE, __NV_E4M3);
     *reinterpret_cast<uint16_t*>(hq + static_cast<long long>(m) * ld_hq + col0 + hcol) =
         static_cast<uint16_t>(pair & 0xFFFFu);
   }

@@ -76,11 +76,11 @@ __device__ __forceinline__ void store4(T* p, const Vec4<T>& v) {
 }
 
 template <typename T>
-__device__ __forceinline__ void emit4(const Vec4<T>& v, float sc, uint8_t* dst) {
-  const float2 lo = make_float2(quant_one(widen(v.v[0]), sc), quant_one(widen(v.v[1]), sc));
-  const float2 hi = make_float2(quant_one(widen(v.v[2]), sc), quant_one(widen(v.v[3]), sc));
-  const uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
-  const uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+__device__ __forceinline__ void emit4(const Vec4<T>& v, const ScaleDiv& sc, uint8_t* dst) {
+  float f[4] = {widen(v.v[0]), widen(v.v[1]), widen(v.v[2]), widen(v.v[3])};
+  divide_group<4, true>(sc, f);   // the scale is that of these very values
+  const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(f[0], f[1]), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(f[2], f[3]), __NV_SATFINITE, __NV_E4M3);
   *reinterpret_cast<uint32_t*>(dst) = (a & 0xFFFFu) | ((b & 0xFFFFu) << 16);
 }
 
@@ -165,12 +165,13 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_quant_kernel(const NormP
     }
   }
   const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+  const ScaleDiv dv(sc);
   if (blockIdx.x == 0 && t == 0) p.scale[0] = sc;
   uint8_t* qr = p.q + static_cast<long long>(row) * p.cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = t + i * kNormThreads;
-    if (v < n_vec) emit4(x[i], sc, qr + v * kVec);
+    if (v < n_vec) emit4(x[i], dv, qr + v * kVec);
   }
   grid_depart(static_cast<QuantWs*>(p.ws));
 }
@@ -250,12 +251,13 @@ __global__ void __launch_bounds__(kGatedWarps * 32) gated_rmsnorm_quant_kernel(c
     }
   }
   const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+  const ScaleDiv dv(sc);
   if (blockIdx.x == 0 && threadIdx.x == 0) p.scale[0] = sc;
   uint8_t* qr = p.q + static_cast<long long>(row) * p.heads * kHeadDim;
 #pragma unroll
   for (int i = 0; i < HPW; ++i) {
     const int head = warp + i * kGatedWarps;
-    if (head < p.heads) emit4(core[i], sc, qr + head * kHeadDim + lane * kVec);
+    if (head < p.heads) emit4(core[i], dv, qr + head * kHeadDim + lane * kVec);
   }
   grid_depart(static_cast<QuantWs*>(p.ws));
 }

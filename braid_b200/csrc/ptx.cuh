@@ -105,6 +105,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       : "memory");
 }
 
+// Untiled bulk copy of `bytes` contiguous bytes from global memory into this CTA's shared
+// memory, completion counted on an mbarrier.  Both addresses 16-byte aligned, `bytes` a
+// multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                             uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+
 // 2-D tiled store from this CTA's shared memory (bulk async-group completion); the part of the
 // box outside the tensor is not written.  x is the innermost coordinate: x * element size must
 // be a multiple of 16 bytes, and no coordinate may be negative.

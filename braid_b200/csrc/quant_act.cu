@@ -85,17 +85,18 @@ __global__ void __launch_bounds__(512, 1) quant_hold_kernel(const QParams p) {
     }
   }
   const float sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+  const ScaleDiv dv(sc);
   if (threadIdx.x == 0) BQ_STAMP(p, 4);
   if (tid == 0) p.scale[0] = sc;
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) {
     const unsigned int g = tid + static_cast<unsigned int>(i) * nthreads;
-    if (i < p.held && g < p.n_groups) emit8(held[i], sc, p.q + static_cast<size_t>(g) * kGroup);
+    if (i < p.held && g < p.n_groups) emit8<T, true>(held[i], dv, p.q + static_cast<size_t>(g) * kGroup);
   }
   if (owns_tail) {
     uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
     for (unsigned int i = 0; i < p.tail; ++i)
-      dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], sc), __NV_SATFINITE, __NV_E4M3);
+      dst[i] = __nv_cvt_float_to_fp8(quant_one(tail_v[i], dv), __NV_SATFINITE, __NV_E4M3);
   }
   grid_depart(static_cast<QuantWs*>(p.ws), p.wait_flag != nullptr ? p.wait_seen : nullptr, p.wait_count);
   if (threadIdx.x == 0) BQ_STAMP(p, 7);
@@ -156,24 +157,29 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     if (tid == 0) p.scale[0] = sc;
   }
   if constexpr (PHASE != kScaleOnly) {
-    // walk backwards: the groups read last in pass 1 are the likeliest still in L2
-    const long long last = (long long)p.n_groups - 1 - tid;
-    for (long long g0 = last; g0 >= 0; g0 -= (long long)nthreads * kUnroll) {
+    const ScaleDiv dv(sc);
+    // Every thread re-reads exactly the groups it read in pass 1 (the L2 keeps a line on
+    // the side of the chip whose SM asked for it, so the same SM finds it again), last
+    // iteration first: what pass 1 read last is the likeliest to be still there.
+    const unsigned int stride = nthreads * kUnroll;
+    long long g0 = -1;
+    if (tid < p.n_groups) g0 = (long long)tid + (long long)((p.n_groups - 1 - tid) / stride) * stride;
+    for (; g0 >= 0; g0 -= stride) {
       Pack8<T> a[kUnroll], b[MODE == kPlain ? 1 : kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const long long g = g0 - (long long)u * nthreads;
-        if (g >= 0) {
+        const long long g = g0 + (long long)u * nthreads;
+        if (g < (long long)p.n_groups) {
           if (coherent) load_raw<T, MODE, true>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
           else load_raw<T, MODE, false>(p, (unsigned int)g, a[u], b[MODE == kPlain ? 0 : u]);
         }
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const long long g = g0 - (long long)u * nthreads;
-        if (g >= 0) {
+        const long long g = g0 + (long long)u * nthreads;
+        if (g < (long long)p.n_groups) {
           apply_prologue<T, MODE>(a[u], b[MODE == kPlain ? 0 : u]);
-          emit8(a[u], sc, p.q + static_cast<size_t>(g) * kGroup);
+          emit8<T, PHASE == kBoth>(a[u], dv, p.q + static_cast<size_t>(g) * kGroup);
         }
       }
     }
@@ -181,12 +187,212 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
       const T* src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
       uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
       for (unsigned int i = 0; i < p.tail; ++i)
-        dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(coherent ? __ldcg(src + i) : src[i]), sc),
+        dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(coherent ? __ldcg(src + i) : src[i]), dv),
                                        __NV_SATFINITE, __NV_E4M3);
     }
   }
   if constexpr (PHASE != kCastOnly)
     grid_depart(static_cast<QuantWs*>(p.ws), coherent ? p.wait_seen : nullptr, p.wait_count);
+}
+
+// ---- plain quantizer at prefill sizes: bulk copies into a shared-memory ring --------------
+// The register-fed streaming kernel above keeps 64 bytes per thread in flight and computes
+// between its loads; at prefill sizes that is half of what HBM needs.  Here one producer lane
+// feeds a ring of kRingStages chunks with untiled bulk copies (bytes in flight cost no
+// registers: 2 CTAs x 96 KB per SM), and 512 consumer threads take 16 bytes of every chunk
+// each.  In the whole quantizer (kBoth) the ring is also a cache: when pass 1 ends, the last
+// kRingStages chunks of every CTA are still in shared memory, and pass 2 walks the CTA's
+// chunks backwards, so those are cast without touching memory again and the others are
+// re-fetched (from L2 while it still has them) in the order pass 1 read them last.
+constexpr int kRingThreads = 512;                  // consumers; one more warp produces
+constexpr int kRingChunk = kRingThreads * 16;      // bytes of input per chunk
+constexpr int kRingStages = 12;
+constexpr int kRingSmem = kRingStages * kRingChunk;
+
+template <typename T>
+__device__ __forceinline__ float unit_absmax(const uint4& raw, float m) {
+  if constexpr (sizeof(T) == 2) {
+    return absmax8(*reinterpret_cast<const Pack8<T>*>(&raw), m);
+  } else {
+    m = nan_max(m, fabsf(__uint_as_float(raw.x)));
+    m = nan_max(m, fabsf(__uint_as_float(raw.y)));
+    m = nan_max(m, fabsf(__uint_as_float(raw.z)));
+    return nan_max(m, fabsf(__uint_as_float(raw.w)));
+  }
+}
+
+// codes of the 16 bytes `raw` holds: 8 for a 16-bit type, 4 for fp32
+template <typename T, bool OWN_SCALE>
+__device__ __forceinline__ void unit_emit(const uint4& raw, const ScaleDiv& dv, uint8_t* dst) {
+  if constexpr (sizeof(T) == 2) {
+    emit8<T, OWN_SCALE>(*reinterpret_cast<const Pack8<T>*>(&raw), dv, dst);
+  } else {
+    float f[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
+                  __uint_as_float(raw.w)};
+    divide_group<4, OWN_SCALE>(dv, f);
+    const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(f[0], f[1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(f[2], f[3]), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint32_t*>(dst) = (a & 0xFFFFu) | ((b & 0xFFFFu) << 16);
+  }
+}
+
+template <typename T, int PHASE>
+__global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const QParams p) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  // [0] full / [1] empty of the forward pass, [2] full / [3] empty of the backward pass
+  __shared__ __align__(8) uint64_t bars[4][kRingStages];
+  __shared__ unsigned int s_failed;
+  bq::pdl_launch_dependents();
+  if (threadIdx.x == 0) { BQ_STAMP(p, 0); BQ_STAMP_META(p, 1); }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool producer = warp == kRingThreads / 32;
+  if (threadIdx.x == 0) {
+    s_failed = 0u;
+    for (int s = 0; s < kRingStages; ++s) {
+      bq::mbar_init(bq::smem_u32(&bars[0][s]), 1);
+      bq::mbar_init(bq::smem_u32(&bars[1][s]), kRingThreads / 32);
+      bq::mbar_init(bq::smem_u32(&bars[2][s]), 1);
+      bq::mbar_init(bq::smem_u32(&bars[3][s]), kRingThreads / 32);
+    }
+    bq::fence_mbar_init();
+  }
+  __syncthreads();
+  bq::pdl_wait_prior_grids();
+  if (threadIdx.x == 0) BQ_STAMP(p, 2);
+
+  const uint8_t* src = static_cast<const uint8_t*>(p.a);
+  const unsigned long long body = (unsigned long long)p.n_groups * kGroup * sizeof(T);   // bytes
+  const long long n_chunks = (long long)((body + kRingChunk - 1) / kRingChunk);
+  // this CTA's chunks: blockIdx.x, + gridDim.x, ...
+  const int count =
+      n_chunks > (long long)blockIdx.x ? (int)((n_chunks - 1 - blockIdx.x) / gridDim.x + 1) : 0;
+  auto chunk_offset = [&](int k) {
+    return ((unsigned long long)blockIdx.x + (unsigned long long)k * gridDim.x) * kRingChunk;
+  };
+  auto chunk_bytes = [&](int k) {
+    const unsigned long long left = body - chunk_offset(k);
+    return (uint32_t)(left < (unsigned long long)kRingChunk ? left : (unsigned long long)kRingChunk);
+  };
+  auto fail = [&]() { atomicExch(&s_failed, 1u); };
+  // what a later pass (or the cast launch that follows a scale launch) reads again stays in
+  // L2 as long as L2 likes; measured, the hint makes no difference at any size
+  const uint64_t policy = (PHASE == kCastOnly) ? bq::policy_evict_first() : bq::policy_evict_last();
+  // the elements after the last whole group belong to consumer thread 0 of CTA 0
+  const bool owns_tail = p.tail != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+  const T* tail_src = reinterpret_cast<const T*>(p.a) + static_cast<size_t>(p.n_groups) * kGroup;
+  constexpr int kPerUnit = 16 / (int)sizeof(T);   // elements (and code bytes) per 16 bytes of input
+
+  float sc;
+  // ---- forward pass: |x| max (kBoth, kScaleOnly) or the cast itself (kCastOnly) ----
+  if constexpr (PHASE == kCastOnly) sc = __ldcg(p.scale);
+  {
+    const ScaleDiv dv(PHASE == kCastOnly ? sc : 1.0f);
+    float m = 0.0f;
+    if (producer) {
+      if (lane == 0) {
+        for (int k = 0; k < count; ++k) {
+          const int s = k % kRingStages;
+          if (k >= kRingStages &&
+              !bq::mbar_wait(bq::smem_u32(&bars[1][s]), (uint32_t)((k / kRingStages - 1) & 1))) {
+            fail();
+            break;
+          }
+          const uint32_t bytes = chunk_bytes(k);
+          bq::mbar_expect_tx(bq::smem_u32(&bars[0][s]), bytes);
+          bq::bulk_load_1d(bq::smem_u32(ring + s * kRingChunk), src + chunk_offset(k), bytes,
+                           bq::smem_u32(&bars[0][s]), policy);
+        }
+      }
+    } else {
+      for (int k = 0; k < count; ++k) {
+        const int s = k % kRingStages;
+        if (!bq::mbar_wait(bq::smem_u32(&bars[0][s]), (uint32_t)((k / kRingStages) & 1))) {
+          fail();
+          break;
+        }
+        if (threadIdx.x * 16u < chunk_bytes(k)) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + threadIdx.x * 16);
+          if constexpr (PHASE == kCastOnly) {
+            unit_emit<T, false>(raw, dv, p.q + (chunk_offset(k) / 16 + threadIdx.x) * kPerUnit);
+          } else {
+            m = unit_absmax<T>(raw, m);
+          }
+        }
+        // hand the stage back when the producer will refill it (kBoth keeps the last ones)
+        if (PHASE != kBoth || k + kRingStages < count) {
+          __syncwarp();
+          if (lane == 0) bq::mbar_arrive(bq::smem_u32(&bars[1][s]));
+        }
+      }
+    }
+    if constexpr (PHASE == kCastOnly) {
+      if (owns_tail) {
+        uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
+        for (unsigned int i = 0; i < p.tail; ++i)
+          dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(tail_src[i]), dv), __NV_SATFINITE, __NV_E4M3);
+      }
+    } else {
+      if (owns_tail)
+        for (unsigned int i = 0; i < p.tail; ++i) m = nan_max(m, fabsf(widen(tail_src[i])));
+      if (threadIdx.x == 0) BQ_STAMP(p, 3);
+      sc = scale_from_amax(grid_amax(m, static_cast<QuantWs*>(p.ws)));
+      if (threadIdx.x == 0) BQ_STAMP(p, 4);
+      if (blockIdx.x == 0 && threadIdx.x == 0) p.scale[0] = sc;
+    }
+  }
+  // ---- backward pass of the whole quantizer: the ring's contents first, then re-fetches ----
+  if constexpr (PHASE == kBoth) {
+    const ScaleDiv dv(sc);
+    const int refetch = count - kRingStages;   // chunks [0, refetch) are no longer in the ring
+    if (producer) {
+      if (lane == 0 && s_failed == 0u) {
+        for (int k = refetch - 1; k >= 0; --k) {
+          const int s = k % kRingStages;
+          const uint32_t parity = (uint32_t)(((refetch - 1 - k) / kRingStages) & 1);
+          if (!bq::mbar_wait(bq::smem_u32(&bars[3][s]), parity)) { fail(); break; }
+          const uint32_t bytes = chunk_bytes(k);
+          bq::mbar_expect_tx(bq::smem_u32(&bars[2][s]), bytes);
+          bq::bulk_load_1d(bq::smem_u32(ring + s * kRingChunk), src + chunk_offset(k), bytes,
+                           bq::smem_u32(&bars[2][s]), bq::policy_evict_first());
+        }
+      }
+    } else if (s_failed == 0u) {
+      for (int k = count - 1; k >= 0; --k) {
+        const int s = k % kRingStages;
+        if (k < refetch) {
+          const uint32_t parity = (uint32_t)(((refetch - 1 - k) / kRingStages) & 1);
+          if (!bq::mbar_wait(bq::smem_u32(&bars[2][s]), parity)) { fail(); break; }
+        }
+        if (threadIdx.x * 16u < chunk_bytes(k)) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + threadIdx.x * 16);
+          unit_emit<T, true>(raw, dv, p.q + (chunk_offset(k) / 16 + threadIdx.x) * kPerUnit);
+        }
+        if (k >= kRingStages) {   // chunk k - kRingStages comes into this stage next
+          __syncwarp();
+          if (lane == 0) bq::mbar_arrive(bq::smem_u32(&bars[3][s]));
+        }
+      }
+    }
+    if (owns_tail) {
+      uint8_t* dst = p.q + static_cast<size_t>(p.n_groups) * kGroup;
+      for (unsigned int i = 0; i < p.tail; ++i)
+        dst[i] = __nv_cvt_float_to_fp8(quant_one(widen(tail_src[i]), dv), __NV_SATFINITE, __NV_E4M3);
+    }
+  }
+  // no bulk copy is in flight here unless a wait ran out: every issued copy was waited for by
+  // the consumers.  After a failed wait, give the copies a bounded time to land before the
+  // CTA's shared memory goes away.
+  __syncthreads();
+  if (s_failed != 0u) {
+    if (threadIdx.x == 0) {
+      atomicExch(&static_cast<QuantWs*>(p.ws)->status, (unsigned int)bq::kErrDeviceWait);
+      const long long t0 = clock64();
+      while (clock64() - t0 < 2000000LL) {}
+    }
+    __syncthreads();
+  }
+  if constexpr (PHASE != kCastOnly) grid_depart(static_cast<QuantWs*>(p.ws));
+  if (threadIdx.x == 0) BQ_STAMP(p, 7);
 }
 
 struct DeviceInfo {
@@ -208,17 +414,25 @@ int device_sms() {
 long long g_opt_quant_block = 0;   // 0 = heuristic
 long long g_opt_quant_held = 0;    // 0 = heuristic
 long long g_opt_quant_pdl = 1;     // programmatic dependent launch on by default
+long long g_opt_quant_ring = 1;    // plain mode at streaming sizes through the shared-memory ring
 
 template <typename Kernel>
-int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p_in, cudaStream_t stream) {
+int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p_in, cudaStream_t stream,
+                    size_t dynamic_smem = 0) {
   QParams p = p_in;
+  if (dynamic_smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic_smem) !=
+          cudaSuccess) {
+    (void)cudaGetLastError();
+    return bq::kErrLaunch;
+  }
 #ifdef BQ_PHASES
   p.phase_ring = bq::phase_ring_for_launch(&p.phase_seq);
 #endif
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3((unsigned)block, 1, 1);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = dynamic_smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -228,6 +442,22 @@ int launch_with_pdl(Kernel kernel, int grid, int block, const QParams& p_in, cud
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
   return bq::kOk;
+}
+
+// The ring kernel takes the plain mode of an input nobody is still writing (its bulk copies
+// are no coherent loads) that starts on a 16-byte boundary.
+template <int MODE>
+bool ring_applies(const QParams& p) {
+  return MODE == kPlain && p.wait_flag == nullptr && (reinterpret_cast<uintptr_t>(p.a) % 16) == 0;
+}
+
+template <typename T, int PHASE>
+int launch_ring(const QParams& p, int sms, cudaStream_t stream) {
+  const unsigned long long body = (unsigned long long)p.n_groups * kGroup * sizeof(T);
+  unsigned long long chunks = (body + kRingChunk - 1) / kRingChunk;
+  if (chunks < 1) chunks = 1;
+  const int grid = (int)(chunks < (unsigned long long)(2 * sms) ? chunks : (unsigned long long)(2 * sms));
+  return launch_with_pdl(quant_ring_kernel<T, PHASE>, grid, kRingThreads + 32, p, stream, kRingSmem);
 }
 
 template <typename T, int MODE>
@@ -262,6 +492,7 @@ int launch_quant(QParams p, cudaStream_t stream) {
     return launch_with_pdl(quant_hold_kernel<T, MODE, kMaxH>, grid, block, p, stream);
   }
   p.held = 0;
+  if (ring_applies<MODE>(p) && g_opt_quant_ring) return launch_ring<T, kBoth>(p, sms, stream);
   return launch_with_pdl(quant_stream_kernel<T, MODE, kBoth>, 2 * sms, 512, p, stream);
 }
 
@@ -285,6 +516,14 @@ int dispatch_phase(int dtype, const QParams& p, cudaStream_t stream) {
   unsigned long long want = ((unsigned long long)p.n_groups + 511ull) / 512ull;
   if (want < 1) want = 1;
   const int grid = (int)(want < (unsigned long long)(2 * sms) ? want : (unsigned long long)(2 * sms));
+  if (ring_applies<MODE>(p) && g_opt_quant_ring && want > (unsigned long long)(2 * sms)) {
+    switch (dtype) {
+      case BQ_DTYPE_F32: return launch_ring<float, PHASE>(p, sms, stream);
+      case BQ_DTYPE_BF16: return launch_ring<__nv_bfloat16, PHASE>(p, sms, stream);
+      case BQ_DTYPE_F16: return launch_ring<__half, PHASE>(p, sms, stream);
+      default: return bq::kErrBadArg;
+    }
+  }
   switch (dtype) {
     case BQ_DTYPE_F32:
       return launch_with_pdl(quant_stream_kernel<float, MODE, PHASE>, grid, 512, p, stream);
@@ -317,6 +556,7 @@ int bq::quant_set_option(const char* key, long long value) {
   if (eq(key, "quant_block")) { g_opt_quant_block = value; return kOk; }
   if (eq(key, "quant_held")) { g_opt_quant_held = value; return kOk; }
   if (eq(key, "quant_pdl")) { g_opt_quant_pdl = value ? 1 : 0; return kOk; }
+  if (eq(key, "quant_ring")) { g_opt_quant_ring = value ? 1 : 0; return kOk; }
   return kErrBadArg;
 }
 

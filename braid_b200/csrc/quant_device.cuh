@@ -1,8 +1,8 @@
 // Device-side building blocks of the FP8 activation quantizer, shared by the stand-alone
 // quantizer kernels (quant_act.cu, norm_quant.cu) and the paired gate/up epilogue (gemm_w8a8.cu).
 // The arithmetic is the reference's torch spelling as a CUDA device evaluates it
-// (braid/model/quant.py:108-115, :228-229): reciprocal-multiply scale, IEEE division,
-// comparison clamps (NaN survives), NaN-propagating max, round-to-nearest-even e4m3 cast; the
+// (braid/model/quant.py:108-115, :228-229): reciprocal-multiply scale, IEEE division, clamp to
+// +-448 (NaN survives), NaN-propagating max, round-to-nearest-even e4m3 cast; the
 // prologues keep the per-operation rounding of the separate torch kernels
 // (braid/model/mlp.py:48, braid/model/attention.py:215).
 #pragma once
@@ -11,6 +11,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <type_traits>
 
 namespace bq {
 namespace qd {
@@ -83,34 +84,98 @@ __device__ __forceinline__ Pack8<T> load8(const T* p) {
   return r;
 }
 
+// max(m, |v[0..7]|), NaN-propagating.  The 16-bit types take the maximum on packed pairs
+// (`abs` and `max.NaN` on two values per instruction; the maximum of 16-bit values is one of
+// them, so nothing is rounded) and widen once at the end.
 template <typename T>
 __device__ __forceinline__ float absmax8(const Pack8<T>& v, float m) {
+  if constexpr (sizeof(T) == 2) {
+    using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+    const T2* w = reinterpret_cast<const T2*>(&v);
+    const T2 m01 = __hmax2_nan(__habs2(w[0]), __habs2(w[1]));
+    const T2 m23 = __hmax2_nan(__habs2(w[2]), __habs2(w[3]));
+    const T2 mm = __hmax2_nan(m01, m23);
+    m = nan_max(m, widen(mm.x));
+    m = nan_max(m, widen(mm.y));
+  } else {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) m = nan_max(m, fabsf(widen(v.v[i])));
+    for (int i = 0; i < 8; ++i) m = nan_max(m, fabsf(widen(v.v[i])));
+  }
   return m;
 }
 
-__device__ __forceinline__ float quant_one(float x, float sc) {
-  float v = __fdiv_rn(x, sc);
-  // comparison clamps: both are false for NaN, which therefore falls through
-  v = (v < -kFp8Max) ? -kFp8Max : ((v > kFp8Max) ? kFp8Max : v);
-  return v;
+// x / sc for a divisor every element of the tensor shares, with the bits of the IEEE division
+// the reference spells (`x / scale`): the reciprocal is rounded once (`__frcp_rn`), and every
+// element takes a product and two residual corrections.  After the first correction the
+// quotient is within one unit in the last place, so the second one rounds correctly
+// (Markstein's division step: y = RN(1/b), q faithful, r = a - b*q exact, RN(q + r*y) =
+// RN(a/b)).  That holds while nothing leaves the normal range: the scale has to lie in
+// [2^-60, 2^60], a quotient that overflows or an operand that is not finite shows as a NaN and
+// takes the division instruction instead, and quotients too small for the corrections to be
+// exact are far below half of the smallest e4m3 step, where only the sign reaches the code
+// (hence the copysign, which also keeps -0).
+struct ScaleDiv {
+  float sc, inv;
+  bool fast;
+  __device__ __forceinline__ explicit ScaleDiv(float s) {
+    sc = s;
+    inv = __frcp_rn(s);
+    fast = s >= 0x1p-60f && s <= 0x1p60f;
+  }
+  // The quotient by the corrections alone; NaN where the division instruction has to decide.
+  __device__ __forceinline__ float corrected(float x) const {
+    float q = __fmul_rn(x, inv);
+    float r = __fmaf_rn(-q, sc, x);
+    q = __fmaf_rn(r, inv, q);
+    r = __fmaf_rn(-q, sc, x);
+    return copysignf(__fmaf_rn(r, inv, q), x);
+  }
+};
+
+// x[i] <- x[i] / sc for the N values of one group: one test for the whole group decides
+// between the corrected products and N division instructions.  OWN_SCALE says the scale was
+// taken from the very values being divided (sc = max|x| / 448, clamped from below): then a
+// scale inside the range means every x is finite and no quotient exceeds 448, and the test
+// for NaN among the results is left out.  What goes on to the saturating e4m3 conversion is
+// the bare quotient: the reference clamps to +-448 before its (non-saturating) cast,
+// `cvt.rn.satfinite` does the same clamp itself (finite values and infinities beyond the
+// range become +-448, NaN stays NaN).
+template <int N, bool OWN_SCALE = false>
+__device__ __forceinline__ void divide_group(const ScaleDiv& d, float (&x)[N]) {
+  float q[N];
+  bool ok = d.fast;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    q[i] = d.corrected(x[i]);
+    if constexpr (!OWN_SCALE) ok = ok && (q[i] == q[i]);
+  }
+  if (ok) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] = q[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] = __fdiv_rn(x[i], d.sc);
+  }
 }
 
-template <typename T>
-__device__ __forceinline__ void emit8(const Pack8<T>& v, float sc, uint8_t* dst) {
+__device__ __forceinline__ float quant_one(float x, const ScaleDiv& d) {
+  float v[1] = {x};
+  divide_group<1>(d, v);
+  return v[0];
+}
+
+template <typename T, bool OWN_SCALE = false>
+__device__ __forceinline__ void emit8(const Pack8<T>& v, const ScaleDiv& sc, uint8_t* dst) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = widen(v.v[i]);
+  divide_group<8, OWN_SCALE>(sc, f);
   uint32_t w[2];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int i = half * 4 + j * 2;
-      const float2 f = make_float2(quant_one(widen(v.v[i]), sc), quant_one(widen(v.v[i + 1]), sc));
-      const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
-      word |= (pair & 0xFFFFu) << (16 * j);
-    }
-    w[half] = word;
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[half * 4], f[half * 4 + 1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[half * 4 + 2], f[half * 4 + 3]), __NV_SATFINITE, __NV_E4M3);
+    w[half] = (lo & 0xFFFFu) | ((hi & 0xFFFFu) << 16);
   }
   *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
 }

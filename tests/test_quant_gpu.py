@@ -49,6 +49,35 @@ def test_ragged_small_and_streaming_sizes(Q, shape, dt):
     _assert_same(q, s, qr, sr, f"{dt} {shape}")
 
 
+@pytest.mark.parametrize("dt,n", [(torch.bfloat16, 4_850_000 + 4099), (torch.bfloat16, 20_000_003),
+                                  (torch.bfloat16, 296 * 12 * 4096 + 8), (torch.bfloat16, 296 * 13 * 4096),
+                                  (torch.float16, 7_777_777), (torch.float32, 2_500_001),
+                                  (torch.float32, 9_000_005)],
+                         ids=["bf16-resident", "bf16-refetch", "bf16-ring-full+1", "bf16-13-each",
+                              "fp16", "fp32-resident", "fp32-refetch"])
+def test_ragged_sizes_through_the_shared_memory_ring(Q, dt, n):
+    """Plain quantizer beyond the register-held regime: a ring of bulk copies per CTA.  Sizes
+    where every chunk of a CTA stays in the ring between the passes, where chunks are fetched
+    again, where the ring is exactly full, a short last chunk and a tail that is no whole group;
+    the cast half alone at the same sizes; and the register-fed streaming kernel on the same
+    input (option `quant_ring` off) gives the same bits."""
+    x = randn_cpu((n,), seed=n % 1000, dtype=dt, scale=1.7).cuda()
+    q, s = Q.quantize_act(x)
+    qr, sr = TS.quantize_act(x)
+    _assert_same(q, s, qr, sr, f"{dt} {n}")
+    qc = Q.cast_act(x, sr)
+    assert torch.equal(u8(qc).reshape(-1), u8(qr).reshape(-1))
+    try:
+        Q.set_option("quant_ring", 0)
+        q0, s0 = Q.quantize_act(x)
+        qc0 = Q.cast_act(x, sr)
+    finally:
+        Q.set_option("quant_ring", 1)
+    _assert_same(q0, s0, qr, sr, f"register-fed {dt} {n}")
+    assert torch.equal(u8(qc0).reshape(-1), u8(qr).reshape(-1))
+    assert Q.device_status() == 0
+
+
 @pytest.mark.parametrize("cols", [4096, 12288])
 def test_config_4_activations_on_the_streaming_kernel(Q, cols):
     """BASELINE config 4: 16 packed sequences (M ~ 8192 rows) of width 4096 (layer input) and
@@ -110,6 +139,68 @@ def test_every_bf16_value_through_the_cast(Q):
     qr, sr = TS.quantize_act(x)
     _assert_same(q, s, qr, sr, "all bf16")
     assert np.array_equal(codes_np(q), oracle.cast(to_np_f32(x), np.float32(s.item())))
+
+
+def _code_mismatches(q, want):
+    """Indices where two e4m3 code tensors differ; two NaN codes (0x7F, 0xFF) count as equal."""
+    a, b = u8(q).reshape(-1), u8(want).reshape(-1)
+    both_nan = ((a & 0x7F) == 0x7F) & ((b & 0x7F) == 0x7F)
+    return ((a != b) & ~both_nan).nonzero().reshape(-1)
+
+
+def _division_scales():
+    """Scales that stress a division done with one rounded reciprocal: random mantissas over the
+    exponents activations produce, mantissas of all ones and 1 + 1 ulp (where 1/scale rounds
+    worst), powers of two, the reference's floor 1e-12, both ends of the range the kernel takes
+    with the reciprocal, values beyond it (the division instruction), infinity."""
+    rng = np.random.default_rng(2024)
+    mant = rng.integers(0, 1 << 23, size=160, dtype=np.uint32)
+    expo = rng.integers(127 - 45, 127 + 20, size=160, dtype=np.uint32)
+    bits = list((expo << 23) | mant)
+    for e in (127 - 40, 127 - 7, 127, 127 + 5):
+        bits += [(e << 23) | 0x7FFFFF, (e << 23) | 1, (e << 23) | 0x7FFFFE, e << 23,
+                 (e << 23) | 0x400000, (e << 23) | 0x555555, (e << 23) | 0x2AAAAB]
+    vals = list(np.array(bits, dtype=np.uint32).view(np.float32))
+    vals += [np.float32(v) for v in (1e-12, 2.0 ** -60, np.nextafter(np.float32(2.0 ** -60), np.float32(0)),
+                                      2.0 ** 60, np.nextafter(np.float32(2.0 ** 60), np.float32(np.inf)),
+                                      1e-30, 3e35, 3.0, 1.0 / 3.0, np.inf)]
+    return vals
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_cast_under_a_shared_scale_is_the_ieee_division_for_every_16_bit_value(Q, dt):
+    """The cast divides by a scale all elements share through one rounded reciprocal and two
+    residual corrections; the codes must be those of the IEEE division the reference spells
+    (braid/model/quant.py:113) for every one of the 65536 bit patterns (NaN, infinities,
+    subnormals and -0 included) under every scale of the list."""
+    x = torch.arange(-32768, 32768, dtype=torch.int16).view(dt).cuda()
+    for sv in _division_scales():
+        scale = torch.full((1, 1), float(sv), dtype=torch.float32, device="cuda")
+        q = Q.cast_act(x, scale)
+        want = (x.float() / scale).reshape(-1).clamp(-Q.FP8_MAX, Q.FP8_MAX).to(Q.FP8)
+        bad = _code_mismatches(q, want)
+        assert bad.numel() == 0, (f"scale {float(sv)!r}: {bad.numel()} codes differ, first at bits "
+                                  f"{int(x.view(torch.int16)[bad[0]]) & 0xFFFF:#06x}")
+    # the oracle's cast agrees with the device's division on a sample of the same grid
+    sv = np.float32(0.0123456)
+    q = Q.cast_act(x, torch.full((1, 1), float(sv), dtype=torch.float32, device="cuda"))
+    fin = torch.isfinite(x.float()).cpu().numpy()
+    assert np.array_equal(codes_np(q)[fin], oracle.cast(to_np_f32(x.cpu()), sv)[fin])
+
+
+def test_cast_of_fp32_values_under_a_shared_scale_is_the_ieee_division(Q):
+    """fp32 activations: 2^22 random bit patterns per scale (any exponent, any mantissa)."""
+    g = torch.Generator(device="cuda").manual_seed(99)
+    bits = torch.randint(-2 ** 31, 2 ** 31 - 1, (1 << 22,), generator=g, device="cuda", dtype=torch.int64)
+    x = bits.to(torch.int32).view(torch.float32)
+    near = (torch.randn(1 << 22, generator=g, device="cuda") * 3.0)
+    for sv in _division_scales()[::5]:
+        scale = torch.full((1, 1), float(sv), dtype=torch.float32, device="cuda")
+        for t in (x, near * float(sv) if np.isfinite(sv) else near):
+            q = Q.cast_act(t, scale)
+            want = (t / scale).reshape(-1).clamp(-Q.FP8_MAX, Q.FP8_MAX).to(Q.FP8)
+            diff = _code_mismatches(q, want).numel()
+            assert diff == 0, f"scale {float(sv)!r}: {diff} codes differ"
 
 
 def test_golden_vectors_with_the_device_scale(Q, golden):
