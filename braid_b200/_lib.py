@@ -39,6 +39,8 @@ SIGNATURES = {
     "bq_silu_mul_cast": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "bq_sigmoid_gate_quant": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64,
                                      _vp, _vp, _vp, _sz, _vp]),
+    "bq_silu_mul": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "bq_sigmoid_mul": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "bq_rmsnorm_quant": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp,
                                 _vp, _sz, _vp]),
     "bq_gated_rmsnorm_quant": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,

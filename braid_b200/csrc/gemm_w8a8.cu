@@ -409,8 +409,8 @@ __device__ __forceinline__ float silu_pair_rows(const EpilogueArgs& e, float sca
         const float got1 = __shfl_xor_sync(0xffffffffu, up_half ? r1 : r3, 16);
         const float g0 = up_half ? got0 : r0, g1 = up_half ? got1 : r1;
         const float u0 = up_half ? r2 : got0, u1 = up_half ? r3 : got1;
-        const T s0 = narrow<T>(__fdiv_rn(g0, 1.0f + expf(-g0)));
-        const T s1 = narrow<T>(__fdiv_rn(g1, 1.0f + expf(-g1)));
+        const T s0 = silu_to<T>(g0);
+        const T s1 = silu_to<T>(g1);
         const T h0 = narrow<T>(widen(s0) * u0);
         const T h1 = narrow<T>(widen(s1) * u1);
         mx = nan_max(mx, fabsf(widen(h0)));
@@ -925,7 +925,7 @@ __device__ __forceinline__ void silu16(const uint32_t (&g)[16], const uint32_t (
   for (int i = 0; i < 16; ++i) {
     const float gg = widen(narrow<T>(__uint_as_float(g[i]) * sg));
     const float uu = widen(narrow<T>(__uint_as_float(u[i]) * su));
-    const T sl = narrow<T>(__fdiv_rn(gg, 1.0f + expf(-gg)));
+    const T sl = silu_to<T>(gg);
     h[i] = narrow<T>(widen(sl) * uu);
     mx = nan_max(mx, fabsf(widen(h[i])));
   }

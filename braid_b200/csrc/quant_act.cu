@@ -198,16 +198,14 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
 // ---- plain quantizer at prefill sizes: bulk copies into a shared-memory ring --------------
 // The register-fed streaming kernel above keeps 64 bytes per thread in flight and computes
 // between its loads; at prefill sizes that is half of what HBM needs.  Here one producer lane
-// feeds a ring of kRingStages chunks with untiled bulk copies (bytes in flight cost no
-// registers: 2 CTAs x 96 KB per SM), and 512 consumer threads take 16 bytes of every chunk
-// each.  In the whole quantizer (kBoth) the ring is also a cache: when pass 1 ends, the last
-// kRingStages chunks of every CTA are still in shared memory, and pass 2 walks the CTA's
+// feeds a ring of chunks with untiled bulk copies (bytes in flight cost no registers:
+// 2 CTAs x 96 KB per SM), and 512 consumer threads take one, two or four 16-byte units of
+// every chunk each.  In the whole quantizer (kBoth) the ring is also a cache: when pass 1 ends, the last
+// chunks of every CTA (96 KB) are still in shared memory, and pass 2 walks the CTA's
 // chunks backwards, so those are cast without touching memory again and the others are
 // re-fetched (from L2 while it still has them) in the order pass 1 read them last.
 constexpr int kRingThreads = 512;                  // consumers; one more warp produces
-constexpr int kRingChunk = kRingThreads * 16;      // bytes of input per chunk
-constexpr int kRingStages = 12;
-constexpr int kRingSmem = kRingStages * kRingChunk;
+constexpr int kRingSmem = 12 * kRingThreads * 16;  // 96 KB of ring per CTA, two CTAs per SM
 
 template <typename T>
 __device__ __forceinline__ float unit_absmax(const uint4& raw, float m) {
@@ -236,11 +234,17 @@ __device__ __forceinline__ void unit_emit(const uint4& raw, const ScaleDiv& dv, 
   }
 }
 
-template <typename T, int PHASE>
+// UNITS = 16-byte units of a chunk per consumer thread (1, 2 or 4): larger chunks spend fewer
+// instructions per element on barriers and addresses, smaller ones balance a short input over
+// the CTAs; the launcher picks the largest that leaves every CTA about three chunks.
+template <typename T, int PHASE, int UNITS>
 __global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const QParams p) {
+  constexpr int kRingUnits = UNITS;
+  constexpr int kRingChunk = kRingThreads * 16 * UNITS;      // bytes of input per chunk
+  constexpr int kRingStages = kRingSmem / kRingChunk;
   extern __shared__ __align__(128) uint8_t ring[];
   // [0] full / [1] empty of the forward pass, [2] full / [3] empty of the backward pass
-  __shared__ __align__(8) uint64_t bars[4][kRingStages];
+  __shared__ __align__(8) uint64_t bars[4][12];
   __shared__ unsigned int s_failed;
   bq::pdl_launch_dependents();
   if (threadIdx.x == 0) { BQ_STAMP(p, 0); BQ_STAMP_META(p, 1); }
@@ -310,12 +314,22 @@ __global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const 
           fail();
           break;
         }
-        if (threadIdx.x * 16u < chunk_bytes(k)) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + threadIdx.x * 16);
-          if constexpr (PHASE == kCastOnly) {
-            unit_emit<T, false>(raw, dv, p.q + (chunk_offset(k) / 16 + threadIdx.x) * kPerUnit);
-          } else {
-            m = unit_absmax<T>(raw, m);
+        const uint32_t have = chunk_bytes(k);
+        uint4 raw[kRingUnits];
+#pragma unroll
+        for (int u = 0; u < kRingUnits; ++u) {
+          const uint32_t unit = threadIdx.x + u * kRingThreads;
+          if (unit * 16u < have) raw[u] = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + unit * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kRingUnits; ++u) {
+          const uint32_t unit = threadIdx.x + u * kRingThreads;
+          if (unit * 16u < have) {
+            if constexpr (PHASE == kCastOnly) {
+              unit_emit<T, false>(raw[u], dv, p.q + (chunk_offset(k) / 16 + unit) * kPerUnit);
+            } else {
+              m = unit_absmax<T>(raw[u], m);
+            }
           }
         }
         // hand the stage back when the producer will refill it (kBoth keeps the last ones)
@@ -363,9 +377,18 @@ __global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const 
           const uint32_t parity = (uint32_t)(((refetch - 1 - k) / kRingStages) & 1);
           if (!bq::mbar_wait(bq::smem_u32(&bars[2][s]), parity)) { fail(); break; }
         }
-        if (threadIdx.x * 16u < chunk_bytes(k)) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + threadIdx.x * 16);
-          unit_emit<T, true>(raw, dv, p.q + (chunk_offset(k) / 16 + threadIdx.x) * kPerUnit);
+        const uint32_t have = chunk_bytes(k);
+        uint4 raw[kRingUnits];
+#pragma unroll
+        for (int u = 0; u < kRingUnits; ++u) {
+          const uint32_t unit = threadIdx.x + u * kRingThreads;
+          if (unit * 16u < have) raw[u] = *reinterpret_cast<const uint4*>(ring + s * kRingChunk + unit * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kRingUnits; ++u) {
+          const uint32_t unit = threadIdx.x + u * kRingThreads;
+          if (unit * 16u < have)
+            unit_emit<T, true>(raw[u], dv, p.q + (chunk_offset(k) / 16 + unit) * kPerUnit);
         }
         if (k >= kRingStages) {   // chunk k - kRingStages comes into this stage next
           __syncwarp();
@@ -393,6 +416,28 @@ __global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const 
   }
   if constexpr (PHASE != kCastOnly) grid_depart(static_cast<QuantWs*>(p.ws));
   if (threadIdx.x == 0) BQ_STAMP(p, 7);
+}
+
+// The prologues alone, unquantized: out[r, c] = the value the quantizer modes quantize
+// (`F.silu(gate) * up`, braid/model/mlp.py:48; `o * torch.sigmoid(gate)`,
+// braid/model/attention.py:215), contiguous [rows, cols] of T.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) prologue_dense_kernel(const QParams p, T* __restrict__ out) {
+  bq::pdl_launch_dependents();
+  bq::pdl_wait_prior_grids();
+  const unsigned int nthreads = gridDim.x * blockDim.x;
+  for (unsigned long long g = blockIdx.x * blockDim.x + threadIdx.x; g < p.n_groups; g += nthreads) {
+    Pack8<T> a, b;
+    load_raw<T, MODE, false>(p, (unsigned int)g, a, b);
+    apply_prologue<T, MODE>(a, b);
+    if constexpr (sizeof(T) == 4) {
+      float4* dst = reinterpret_cast<float4*>(out + g * kGroup);
+      dst[0] = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+      dst[1] = make_float4(a.v[4], a.v[5], a.v[6], a.v[7]);
+    } else {
+      *reinterpret_cast<uint4*>(out + g * kGroup) = *reinterpret_cast<const uint4*>(&a);
+    }
+  }
 }
 
 struct DeviceInfo {
@@ -454,10 +499,16 @@ bool ring_applies(const QParams& p) {
 template <typename T, int PHASE>
 int launch_ring(const QParams& p, int sms, cudaStream_t stream) {
   const unsigned long long body = (unsigned long long)p.n_groups * kGroup * sizeof(T);
-  unsigned long long chunks = (body + kRingChunk - 1) / kRingChunk;
+  const unsigned long long unit_chunk = (unsigned long long)kRingThreads * 16;
+  const unsigned long long ctas = 2ull * sms;
+  const int units = body >= 3 * ctas * 4 * unit_chunk ? 4 : (body >= 3 * ctas * 2 * unit_chunk ? 2 : 1);
+  unsigned long long chunks = (body + units * unit_chunk - 1) / (units * unit_chunk);
   if (chunks < 1) chunks = 1;
-  const int grid = (int)(chunks < (unsigned long long)(2 * sms) ? chunks : (unsigned long long)(2 * sms));
-  return launch_with_pdl(quant_ring_kernel<T, PHASE>, grid, kRingThreads + 32, p, stream, kRingSmem);
+  const int grid = (int)(chunks < ctas ? chunks : ctas);
+  const int block = kRingThreads + 32;
+  if (units == 4) return launch_with_pdl(quant_ring_kernel<T, PHASE, 4>, grid, block, p, stream, kRingSmem);
+  if (units == 2) return launch_with_pdl(quant_ring_kernel<T, PHASE, 2>, grid, block, p, stream, kRingSmem);
+  return launch_with_pdl(quant_ring_kernel<T, PHASE, 1>, grid, block, p, stream, kRingSmem);
 }
 
 template <typename T, int MODE>
@@ -714,6 +765,73 @@ extern "C" int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype,
   p.chunk = static_cast<unsigned int>(chunk);
   p.chunk_stride = chunk_stride;
   return dispatch_dtype<kSigmoidGate>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+template <int MODE>
+int launch_dense(int dtype, const QParams& p, void* out, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return bq::kErrLaunch;
+  unsigned long long want = ((unsigned long long)p.n_groups + 255ull) / 256ull;
+  const int grid = (int)(want < (unsigned long long)(8 * sms) ? want : (unsigned long long)(8 * sms));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_quant_pdl ? 1 : 0;
+  cudaError_t e;
+  switch (dtype) {
+    case BQ_DTYPE_F32:
+      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<float, MODE>, p, static_cast<float*>(out));
+      break;
+    case BQ_DTYPE_BF16:
+      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<__nv_bfloat16, MODE>, p,
+                             static_cast<__nv_bfloat16*>(out));
+      break;
+    case BQ_DTYPE_F16:
+      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<__half, MODE>, p, static_cast<__half*>(out));
+      break;
+    default: return bq::kErrBadArg;
+  }
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
+  return bq::kOk;
+}
+}  // namespace
+
+extern "C" int bq_silu_mul(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                           int64_t ld_gate, int64_t ld_up, void* h_out, void* stream) {
+  if (!h_out) return bq::kErrBadArg;
+  if (!aligned_to(h_out, 16)) return bq::kErrUnsupported;
+  QParams p{};
+  if (int rc = fill_silu_mul(&p, gate, up, dtype, rows, cols, ld_gate, ld_up)) return rc;
+  return launch_dense<kSiluMul>(dtype, p, h_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                              int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride,
+                              void* out, void* stream) {
+  if (!o || !gate || !out || rows <= 0 || cols <= 0 || chunk <= 0) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  const size_t es = elem_size(dtype);
+  if (cols % kGroup || chunk % kGroup || cols % chunk || ld_o < cols || (ld_o * es) % 16 ||
+      (ld_gate * es) % 16 || (chunk_stride * es) % 16 || !aligned_to(o, 16) ||
+      !aligned_to(gate, 16) || !aligned_to(out, 16))
+    return bq::kErrUnsupported;
+  if (rows * (cols / kGroup) >= 0x7fffffffLL) return bq::kErrTooLarge;
+  QParams p{};
+  p.a = o;
+  p.b = gate;
+  p.groups_per_row = static_cast<unsigned int>(cols / kGroup);
+  p.n_groups = static_cast<unsigned int>(rows * (cols / kGroup));
+  p.ld_a = ld_o;
+  p.ld_b = ld_gate;
+  p.chunk = static_cast<unsigned int>(chunk);
+  p.chunk_stride = chunk_stride;
+  return launch_dense<kSigmoidGate>(dtype, p, out, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------

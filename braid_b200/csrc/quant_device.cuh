@@ -185,6 +185,18 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
   return (raw < kEps) ? kEps : raw;   // NaN compares false and stays NaN
 }
 
+// x / (1 + exp(-x)) and 1 / (1 + exp(-x)) rounded to T as torch evaluates F.silu and
+// torch.sigmoid of a T tensor on a CUDA device: fp32, expf, an IEEE division, one rounding.
+// (Taking ex2/rcp approximations wherever the rounding to a 16-bit T hides them, with the exact
+// instructions for values near a rounding tie, passed the exhaustive test but measured slower:
+// the guard and the divergent exact path cost what the approximations saved.)
+template <typename T> __device__ __forceinline__ T silu_to(float x) {
+  return narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
+}
+template <typename T> __device__ __forceinline__ T sigmoid_to(float x) {
+  return narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-x)));
+}
+
 // Raw operands of one group: one 8-pack for the plain mode, two for the prologues.
 template <typename T, int MODE, bool COHERENT = false>
 __device__ __forceinline__ void load_raw(const QParams& p, unsigned int g, Pack8<T>& a, Pack8<T>& b) {
@@ -216,11 +228,11 @@ __device__ __forceinline__ void apply_prologue(Pack8<T>& a, const Pack8<T>& b) {
       if constexpr (MODE == kSiluMul) {
         // silu in fp32, rounded to T; product in fp32, rounded to T
         const float x = widen(a.v[i]);
-        const T sl = narrow<T>(__fdiv_rn(x, 1.0f + expf(-x)));
+        const T sl = silu_to<T>(x);
         a.v[i] = narrow<T>(widen(sl) * widen(b.v[i]));
       } else {
         const float gt = widen(b.v[i]);
-        const T sg = narrow<T>(__fdiv_rn(1.0f, 1.0f + expf(-gt)));
+        const T sg = sigmoid_to<T>(gt);
         a.v[i] = narrow<T>(widen(a.v[i]) * widen(sg));
       }
     }

@@ -447,6 +447,40 @@ def sigmoid_gate_quant(o: torch.Tensor, gate: torch.Tensor,
     return q.reshape(*o.shape[:-1], cols), scale
 
 
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """`F.silu(gate) * up` (braid/model/mlp.py:48) as one kernel, bit for bit: silu in fp32
+    rounded to the activation type, product in fp32 rounded again.  For the places that want the
+    product dense (an unquantized down projection); the quantized path never materialises it."""
+    code, cols, g2, u2 = _silu_mul_args(gate, up, "silu_mul")
+    if _quantizers_off():
+        return F.silu(gate) * up
+    rows = g2.shape[0]
+    h = torch.empty((rows, cols), dtype=gate.dtype, device=gate.device)
+    _lib.check(_require_lib().bq_silu_mul(g2.data_ptr(), u2.data_ptr(), code, rows, cols, g2.stride(0),
+                                          u2.stride(0), h.data_ptr(), _stream_ptr(gate.device)),
+               "silu_mul")
+    return h.reshape(*gate.shape[:-1], cols)
+
+
+def sigmoid_mul(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """`o * torch.sigmoid(gate)` (braid/model/attention.py:215) as one kernel, bit for bit;
+    `gate` dense and of `o`'s shape."""
+    _check_cuda(o, "sigmoid_mul")
+    code = _DTYPE_CODE.get(o.dtype)
+    if code is None or gate.dtype != o.dtype or gate.shape != o.shape:
+        raise ValueError("o and gate must share shape and one of fp32, bf16, fp16")
+    if _quantizers_off():
+        return o * torch.sigmoid(gate)
+    cols = o.shape[-1]
+    o2, g2 = _as_rows(o, cols), _as_rows(gate, cols)
+    rows = o2.shape[0]
+    out = torch.empty((rows, cols), dtype=o.dtype, device=o.device)
+    _lib.check(_require_lib().bq_sigmoid_mul(o2.data_ptr(), g2.data_ptr(), code, rows, cols, o2.stride(0),
+                                             g2.stride(0), cols, 0, out.data_ptr(),
+                                             _stream_ptr(o.device)), "sigmoid_mul")
+    return out.reshape(*o.shape[:-1], cols)
+
+
 # ---------------------------------------------------------------------------
 # norms fused into the quantizer of their consumer
 # ---------------------------------------------------------------------------

@@ -161,6 +161,22 @@ int bq_sigmoid_gate_quant(const void* o, const void* gate, int dtype, int64_t ro
                           void* q_out, float* scale_out, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The two prologues alone, unquantized, with the rounding the quantizer modes apply:
+ * bq_silu_mul writes h = T(T(silu(gate)) * up), bq_sigmoid_mul writes T(o * T(sigmoid(gate))),
+ * contiguous [rows, cols] of the input type, 16-byte aligned.  Arguments as in
+ * bq_silu_mul_quant / bq_sigmoid_gate_quant; no scratch.
+ *
+ * Replaces: the elementwise torch kernels of braid/model/mlp.py:48 (`F.silu(gate) * up`) and
+ * braid/model/attention.py:215 (`o * torch.sigmoid(gate)`) where the product is wanted dense
+ * (an unquantized down / o projection), bit for bit.
+ */
+int bq_silu_mul(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                int64_t ld_gate, int64_t ld_up, void* h_out, void* stream);
+int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                   int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride, void* out,
+                   void* stream);
+
+/*
  * RMSNorm fused into the quantizer: h = T(gamma * (rstd * x)), rstd = rsqrt(mean(x^2) + eps),
  * computed in fp32 from the fp32-widened input with ONE rounding to the activation type T,
  * then amax / scale / e4m3 codes of h as bq_quantize_act produces them.  The sum of squares

@@ -6,6 +6,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 import oracle
 from oracle import torch_spelling as TS
@@ -49,16 +50,17 @@ def test_ragged_small_and_streaming_sizes(Q, shape, dt):
     _assert_same(q, s, qr, sr, f"{dt} {shape}")
 
 
-@pytest.mark.parametrize("dt,n", [(torch.bfloat16, 4_850_000 + 4099), (torch.bfloat16, 20_000_003),
-                                  (torch.bfloat16, 296 * 12 * 4096 + 8), (torch.bfloat16, 296 * 13 * 4096),
-                                  (torch.float16, 7_777_777), (torch.float32, 2_500_001),
-                                  (torch.float32, 9_000_005)],
-                         ids=["bf16-resident", "bf16-refetch", "bf16-ring-full+1", "bf16-13-each",
-                              "fp16", "fp32-resident", "fp32-refetch"])
+@pytest.mark.parametrize("dt,n", [(torch.bfloat16, 4_850_000 + 4099), (torch.bfloat16, 9_000_001),
+                                  (torch.bfloat16, 20_000_003), (torch.bfloat16, 296 * 3 * 16384 + 8),
+                                  (torch.bfloat16, 296 * 4 * 16384), (torch.float16, 7_777_777),
+                                  (torch.float32, 2_500_001), (torch.float32, 9_000_005)],
+                         ids=["bf16-8KB-chunks", "bf16-16KB-chunks", "bf16-refetch", "bf16-ring-full+1",
+                              "bf16-4-each", "fp16", "fp32-resident", "fp32-refetch"])
 def test_ragged_sizes_through_the_shared_memory_ring(Q, dt, n):
-    """Plain quantizer beyond the register-held regime: a ring of bulk copies per CTA.  Sizes
-    where every chunk of a CTA stays in the ring between the passes, where chunks are fetched
-    again, where the ring is exactly full, a short last chunk and a tail that is no whole group;
+    """Plain quantizer beyond the register-held regime: a ring of bulk copies per CTA (96 KB;
+    chunks of 8, 16 or 32 KB by input size).  Sizes where every chunk of a CTA stays in the ring
+    between the passes, where chunks are fetched again, where the ring is exactly full (three
+    32 KB chunks per CTA on 148 SMs), a short last chunk and a tail that is no whole group;
     the cast half alone at the same sizes; and the register-fed streaming kernel on the same
     input (option `quant_ring` off) gives the same bits."""
     x = randn_cpu((n,), seed=n % 1000, dtype=dt, scale=1.7).cuda()
@@ -307,6 +309,38 @@ def test_sigmoid_gate_quant_dense_and_per_head_view(Q, dt):
     q2, s2 = Q.sigmoid_gate_quant(o, gate_v)
     _assert_same(q2, s2, qr, sr, "per-head view")
     assert q2.shape == o.shape
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_silu_and_sigmoid_of_every_16_bit_value(Q, dt):
+    """The prologues' silu and sigmoid, seen through the dense forms: the result has to be
+    torch's (`F.silu(gate) * up`, braid/model/mlp.py:48; `o * torch.sigmoid(gate)`,
+    braid/model/attention.py:215) for every one of the 65536 gate bit patterns, NaN and
+    infinities included, under several partners."""
+    gate = torch.arange(-32768, 32768, dtype=torch.int16).view(dt).cuda().reshape(64, 1024)
+    for partner in (1.0, -3.71875, 0.0009765625, 250.0):
+        other = torch.full_like(gate, partner)
+        for got, want in ((Q.silu_mul(gate, other), F.silu(gate) * other),
+                          (Q.sigmoid_mul(other, gate), other * torch.sigmoid(gate))):
+            a, b = got.view(torch.int16), want.view(torch.int16)
+            both_nan = torch.isnan(got) & torch.isnan(want)
+            bad = ((a != b) & ~both_nan).nonzero()
+            assert bad.numel() == 0, (f"{dt} partner {partner}: {bad.shape[0]} values differ, first at gate "
+                                      f"bits {int(gate.view(torch.int16)[tuple(bad[0])]) & 0xFFFF:#06x}")
+    # random partners: the second rounding sees every first-rounding outcome
+    g = torch.Generator(device="cuda").manual_seed(8)
+    up = (torch.randn(64, 1024, generator=g, device="cuda") * 2.0).to(dt)
+    assert torch.equal(Q.silu_mul(gate, up).view(torch.int16)[~torch.isnan(gate)],
+                       (F.silu(gate) * up).view(torch.int16)[~torch.isnan(gate)])
+
+
+def test_dense_prologues_in_fp32_and_on_column_blocks(Q):
+    x = randn_cpu((33, 2 * 512), seed=12, dtype=torch.float32, scale=3.0).cuda()
+    assert torch.equal(Q.silu_mul(x[:, :512], x[:, 512:]), F.silu(x[:, :512]) * x[:, 512:])
+    assert torch.equal(Q.sigmoid_mul(x[:, :512].contiguous(), x[:, 512:].contiguous()),
+                       x[:, :512] * torch.sigmoid(x[:, 512:]))
+    xb = x.to(torch.bfloat16)
+    assert torch.equal(Q.silu_mul(xb[:, :512], xb[:, 512:]), F.silu(xb[:, :512]) * xb[:, 512:])
 
 
 def test_prologues_against_the_golden_vectors(Q, golden):
