@@ -420,12 +420,13 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         y_nccl = fn().clone()
         del mlp
         # the same sharded MLP with the all-gathers folded into the GEMM epilogues (peer-mapped
-        # buffers over CUDA IPC, per-rank arrival counters, no collective): decode sizes only
-        if rows <= 256:
+        # buffers over CUDA IPC, per-rank arrival counters, no collective)
+        if True:
             try:
                 from braid_b200.parallel import FusedColumnParallelMLP
                 fmlp = FusedColumnParallelMLP.random_init(4096, 12288, torch.device("cuda"),
-                                                          dist.group.WORLD, seed=1)
+                                                          dist.group.WORLD, seed=1,
+                                                          rows_max=max(256, rows))
                 fmlp.connect()
                 y_fused = fmlp.forward(x).clone()
                 torch.cuda.synchronize()

@@ -124,6 +124,10 @@ struct PushParams {
   unsigned int* flag[kMaxPeers];  // one arrival counter per destination rank
   unsigned int* done;             // local: CTAs of this launch that have stored their share
   unsigned int expected;          // CTAs that store (the active ones)
+  // prefill SiLU form: where this rank's max |h| (float bits) goes on every rank, written by
+  // the last CTA before the arrivals; nullptr = not wanted
+  unsigned int* amax_dst[kMaxPeers];
+  unsigned int* amax_local;       // local running max of the launch (zero between launches)
 };
 
 struct GemmParams {
@@ -836,6 +840,35 @@ __global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, u
   __threadfence();
 }
 
+// The same wait, then the quantization scale of the gathered h from the ranks' max |h| words
+// (each written by its rank ahead of that rank's arrival): scale = max over ranks, turned into
+// the scale as the quantizer does it.  The maximum of the shards' maxima is the maximum of the
+// whole tensor, so this is the scale the unsharded quantizer computes, bit for bit.
+__global__ void wait_flag_scale_kernel(const unsigned int* flag, unsigned int* seen, unsigned int count,
+                                       unsigned int* status, const unsigned int* amax_slots, int n,
+                                       float* scale_out) {
+  const unsigned int target = *seen + count;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - target) >= 0) break;
+    if (clock64() - t0 > kSpinLimitCycles) {
+      atomicExch(status, (unsigned int)kErrDeviceWait);
+      break;
+    }
+  }
+  unsigned int best = 0u;
+  for (int i = 0; i < n; ++i) {
+    unsigned int b;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(b) : "l"(amax_slots + i) : "memory");
+    best = b > best ? b : best;      // |h| bit patterns order like the values, NaN on top
+  }
+  *scale_out = bq::qd::scale_from_amax(__uint_as_float(best));
+  *seen = target;
+  __threadfence();
+}
+
 // ---------------------------------------------------------------------------
 // Persistent tile kernel on CTA pairs (prefill regime, cta_group::2)
 // ---------------------------------------------------------------------------
@@ -994,10 +1027,21 @@ __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Se
         const int m = m_row0 + row;
         const uint4 v = *reinterpret_cast<const uint4*>(box + row * 128 + ((piece ^ (row & 7)) << 4));
         if (m < p.M && col < seg.n) {         // n is a multiple of 16: a piece is in or out as a whole
-          uint8_t* dst = static_cast<uint8_t*>(seg.y) + ((long long)m * seg.ldy + col) * ES;
           // rows are 8-byte aligned at least (checked by the host)
-          *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
-          *reinterpret_cast<uint2*>(dst + 8) = make_uint2(v.z, v.w);
+          if (p.push.n == 0) {
+            uint8_t* dst = static_cast<uint8_t*>(seg.y) + ((long long)m * seg.ldy + col) * ES;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+            *reinterpret_cast<uint2*>(dst + 8) = make_uint2(v.z, v.w);
+          } else {
+            // column-parallel form: the same piece into every rank's gathered buffer (plain
+            // stores through peer-mapped pointers, this rank's own buffer included)
+            const long long at = ((long long)m * p.push.ld + col) * ES;
+            for (int d = 0; d < p.push.n; ++d) {
+              uint8_t* dst = static_cast<uint8_t*>(p.push.dst[d]) + at;
+              *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+              *reinterpret_cast<uint2*>(dst + 8) = make_uint2(v.z, v.w);
+            }
+          }
         }
       }
       __syncwarp();
@@ -1164,7 +1208,47 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
     if (!ok) *abort_flag = 1;
-    if (silu) {
+    if (p.push.n > 0) {
+      // The stores of all epilogue threads are ordered before the elected thread's fence by the
+      // barrier (fences are cumulative); the fence orders them before this CTA's count; the
+      // last CTA sees every count, fences again and only then signals the ranks: every store of
+      // the launch happens before every arrival.
+      const bool want_amax = silu && p.push.amax_local != nullptr;
+      if (want_amax) {
+        using namespace bq::qd;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+          h_max = nan_max(h_max, __shfl_xor_sync(0xffffffffu, h_max, off));
+        if (lane == 0) s_amax[warp - 2] = h_max;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kPairEpiWarps) : "memory");
+      if (warp == 2 && lane == 0) {
+        if (want_amax) {
+          using namespace bq::qd;
+          float w = s_amax[0];
+#pragma unroll
+          for (int i = 1; i < kPairEpiWarps; ++i) w = nan_max(w, s_amax[i]);
+          // bit patterns of |h| order like the values, NaN on top: exact and order-free
+          atomicMax(p.push.amax_local, __float_as_uint(w));
+        }
+        __threadfence_system();
+        const unsigned int old = atomicAdd(p.push.done, 1u);
+        if (old == p.push.expected - 1u) {
+          *p.push.done = 0u;                     // ready for the next launch on this scratch
+          if (want_amax) {
+            // every CTA's max is in (its atomicMax precedes its count): hand this rank's
+            // max |h| to every rank, ahead of the arrival that tells them to look
+            const unsigned int bits = atomicExch(p.push.amax_local, 0u);
+            for (int d = 0; d < p.push.n; ++d)
+              if (p.push.amax_dst[d] != nullptr)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.push.amax_dst[d]), "r"(bits) : "memory");
+          }
+          __threadfence_system();
+          for (int d = 0; d < p.push.n; ++d)
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push.flag[d]) : "memory");
+        }
+      }
+    } else if (silu) {
       // max |h| of the launch: warps -> CTA -> one atomicMax per CTA on the bit pattern (exact
       // and order-free; NaN patterns sort on top); the CTA that arrives last turns the result into
       // the scale of h and returns the scratch words to zero
@@ -1471,6 +1555,7 @@ int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, const OutMaps& 
                 "pair kernel: pipeline + store boxes exceed the shared memory of an SM");
   int pairs = p.total_tiles < sms / 2 ? p.total_tiles : sms / 2;
   if (pairs < 1) pairs = 1;
+  if (p.push.n > 0) p.push.expected = (unsigned)(2 * pairs);   // every CTA has a tile and stores
   g_last_launch[0] = 2; g_last_launch[1] = 2 * pairs; g_last_launch[2] = 2;
   g_last_launch[3] = kPairStages; g_last_launch[4] = smem; g_last_launch[5] = kPairTile;
   cudaLaunchConfig_t cfg;
@@ -1567,8 +1652,11 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (pair && stream_path == (pair->prefill != 0)) return kErrUnsupported;   // each form has its regime
   if (pair && (res || n_seg != 1)) return kErrBadArg;
   if (push) {
-    if (!stream_path) return kErrUnsupported;
     if (res || n_seg != 1) return kErrBadArg;
+    // the prefill kernel stores 16-byte pieces as two 8-byte words
+    if (!stream_path)
+      for (int d = 0; d < push->n; ++d)
+        if (!aligned_to(push->dst[d], 8)) return kErrUnsupported;
   }
   if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
     if (!stream_path || ld_res == nullptr) return kErrUnsupported;
@@ -1605,6 +1693,8 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (push) {
     p.push = *push;
     p.push.done = static_cast<unsigned int*>(ws);   // first scratch word: zero between launches
+    // second scratch word: the launch's running max |h| where the ranks want it
+    p.push.amax_local = (push->amax_dst[0] != nullptr) ? static_cast<unsigned int*>(ws) + 1 : nullptr;
   }
 
   const bool pair_path = !stream_path;
@@ -1629,7 +1719,7 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
     const long long add = stream_path ? nt : nt * p.m_tiles;
     if (tiles + add > 0x3fffffffLL) return kErrTooLarge;
     tiles += (int)add;
-    if (pair_path) {
+    if (pair_path && !no_y) {
       const size_t es = out_dtype == BQ_DTYPE_F32 ? 4 : 2;
       p.seg[i].y_tma = aligned_to(y[i], 16) && (ldy[i] * es) % 16 == 0 &&
                        make_out_map(&ymaps.y[i], y[i], M, N[i], ldy[i], out_dtype) == kOk;
@@ -1793,7 +1883,7 @@ extern "C" int bq_gate_up_silu_w8a8(const void* xq, const float* sx, const void*
 
 namespace {
 int fill_push(PushParams* pp, int n_peers, void* const* dst, int64_t ld, void* const* flags,
-              int64_t width, size_t align) {
+              int64_t width, size_t align, void* const* amax_slots = nullptr) {
   if (n_peers < 1 || n_peers > kMaxPeers || !dst || !flags) return kErrBadArg;
   if (ld < width || ld % 4) return kErrUnsupported;
   memset(pp, 0, sizeof(*pp));
@@ -1804,6 +1894,11 @@ int fill_push(PushParams* pp, int n_peers, void* const* dst, int64_t ld, void* c
     if (!aligned_to(dst[i], align) || !aligned_to(flags[i], 4)) return kErrUnsupported;
     pp->dst[i] = dst[i];
     pp->flag[i] = static_cast<unsigned int*>(flags[i]);
+    if (amax_slots != nullptr) {
+      if (!amax_slots[i]) return kErrBadArg;
+      if (!aligned_to(amax_slots[i], 4)) return kErrUnsupported;
+      pp->amax_dst[i] = static_cast<unsigned int*>(amax_slots[i]);
+    }
   }
   return kOk;
 }
@@ -1830,11 +1925,16 @@ extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const 
                                          const float* sw_up, int64_t M,
                                          int64_t I, int64_t K, int act_dtype, int n_peers,
                                          void* const* h_dst, int64_t ld_h, void* const* flags,
-                                         void* ws, size_t ws_bytes, void* stream) {
+                                         void* const* amax_slots, void* ws, size_t ws_bytes,
+                                         void* stream) {
   if (!wq_gate || !wq_up || !sw_gate || !sw_up || I <= 0) return kErrBadArg;
   if (I % (kRowTile / 2) || !aligned_to(wq_up, 16)) return kErrUnsupported;
+  // the max |h| of the shard travels with the prefill form only (decode sizes re-quantize the
+  // gathered h in the kernel that waits for it)
+  if (amax_slots != nullptr && M <= g_opt_stream_max_m) amax_slots = nullptr;
   PushParams push;
-  if (int rc = fill_push(&push, n_peers, h_dst, ld_h, flags, I, act_dtype == BQ_DTYPE_F32 ? 8 : 4))
+  if (int rc = fill_push(&push, n_peers, h_dst, ld_h, flags, I, act_dtype == BQ_DTYPE_F32 ? 8 : 4,
+                         amax_slots))
     return rc;
   PairSilu pair;
   memset(&pair, 0, sizeof(pair));
@@ -1843,8 +1943,15 @@ extern "C" int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const 
   const void* wqs[1] = {wq_gate};
   const float* sws[1] = {sw_gate};
   void* ys[1] = {nullptr};
-  const int64_t Ns[1] = {2 * I};
   const int64_t ldys[1] = {0};
+  if (M > g_opt_stream_max_m) {
+    // prefill sizes: the CTA-pair kernel, SiLU*mul in its epilogue, h pieces to every rank
+    pair.prefill = 1;
+    const int64_t Ns[1] = {I};
+    return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
+                       nullptr, nullptr, &pair, 0, &push);
+  }
+  const int64_t Ns[1] = {2 * I};
   const int k_blocks = (int)((K + kBK - 1) / kBK);
   const int split = (K > 0 && K <= 0x7fffff00LL) ? split_for_weight(I, k_blocks) : 1;
   return run_grouped(xq, sx, M, K, 1, wqs, sws, ys, Ns, ldys, act_dtype, ws, ws_bytes, stream,
@@ -1858,6 +1965,22 @@ extern "C" int bq_wait_flag(const void* flag, void* seen, unsigned int count, vo
   wait_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned int*>(flag), static_cast<unsigned int*>(seen), count,
       static_cast<unsigned int*>(status_word));
+  if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
+  return kOk;
+}
+
+extern "C" int bq_wait_flag_scale(const void* flag, void* seen, unsigned int count, void* status_word,
+                                  const void* amax_slots, int n_slots, float* scale_out,
+                                  void* stream) {
+  if (!flag || !seen || !status_word || !amax_slots || !scale_out || count == 0) return kErrBadArg;
+  if (n_slots < 1 || n_slots > kMaxPeers) return kErrBadArg;
+  if (!aligned_to(flag, 4) || !aligned_to(seen, 4) || !aligned_to(status_word, 4) ||
+      !aligned_to(amax_slots, 4) || !aligned_to(scale_out, 4))
+    return kErrUnsupported;
+  wait_flag_scale_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned int*>(flag), static_cast<unsigned int*>(seen), count,
+      static_cast<unsigned int*>(status_word), static_cast<const unsigned int*>(amax_slots), n_slots,
+      scale_out);
   if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
   return kOk;
 }

@@ -86,13 +86,13 @@ class ColumnParallelMLP:
         self.down = W(down.data[hlo:hhi].contiguous(), down.scale, (hhi - hlo, I))
 
     @classmethod
-    def random_init(cls, hidden, inter, device, group=None, seed=0, ops=None):
+    def random_init(cls, hidden, inter, device, group=None, seed=0, ops=None, **kwargs):
         if ops is None:
             from . import quant as ops
         g = torch.Generator(device=device).manual_seed(seed)   # same weights on every rank
         mk = lambda n, k: ops.quantize_weight(  # noqa: E731
             (torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.bfloat16))
-        return cls(mk(inter, hidden), mk(inter, hidden), mk(hidden, inter), group, ops)
+        return cls(mk(inter, hidden), mk(inter, hidden), mk(hidden, inter), group, ops, **kwargs)
 
     def gather_bytes(self, rows: int) -> dict:
         """Bytes every rank ends up holding after each exchange (codes or bf16 for h, bf16 for y)."""
@@ -168,10 +168,13 @@ class PeerBuffers:
     """One rank's gathered buffers and counters, plus where the other ranks' copies are.
 
     `h` `[rows_max, I]` and `y` `[rows_max, H]` receive every rank's column slice; `sync` holds
-    the two arrival counters (h, y) that the other ranks increment.  The three live in ONE device
+    the two arrival counters (h, y) that the other ranks increment and, from byte 64, one word
+    per rank for that rank's max |h| (prefill sizes).  The three live in ONE device
     allocation made by the library (`bq_peer_alloc`), because it has to be exported to the other
     processes as a whole; `seen` and `status` are private to the rank.  `peers[r]` is rank r's
     (h, y, sync) device addresses as they are valid on THIS rank."""
+
+    AMAX_OFFSET = 64    # bytes into `sync`: one max |h| word per rank (up to 8)
 
     def __init__(self, rows_max: int, inter: int, hidden: int, dtype: torch.dtype, device, ops=None):
         import ctypes
@@ -244,7 +247,8 @@ class PeerBuffers:
 
 
 class FusedColumnParallelMLP(ColumnParallelMLP):
-    """`ColumnParallelMLP` with both all-gathers folded into the producing GEMMs (decode sizes).
+    """`ColumnParallelMLP` with both all-gathers folded into the producing GEMMs, at decode sizes
+    (the weight-streaming kernel) and at prefill sizes (the CTA-pair kernel) up to `rows_max` rows.
 
     gate/up shard: one paired GEMM whose epilogue forms this rank's slice of SiLU(gate)*up and
     stores it into every rank's `h` buffer; down shard: one GEMM whose epilogue stores its slice
@@ -291,18 +295,32 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         self.buffers.close(self.group)
 
     # -- the four phases (a test interleaves them over emulated ranks; forward() runs them in order)
+    # From this many rows on, the gate/up launch hands its shard's max |h| to every rank and the
+    # consumer is a one-thread wait that also forms the scale, then the cast pass; below it the
+    # quantizer of the gathered h waits in its own kernel (one launch fewer).
+    amax_from = 257
+
     def push_h(self, x2: torch.Tensor) -> None:
         ops, es = self.ops, torch.empty(0, dtype=self.dtype).element_size()
         xq, sx = ops.quantize_act(x2)
         col = self.i_ranges[self.rank][0]
+        amax = None
+        if x2.shape[0] >= self.amax_from:
+            amax = [s + PeerBuffers.AMAX_OFFSET + 4 * self.rank for _, _, s in self.buffers.peers]
         ops.gate_up_silu_push(xq, sx, self.gate, self.up, self.dtype,
                               [h + col * es for h, _, _ in self.buffers.peers], self.I,
-                              [s for _, _, s in self.buffers.peers])
+                              [s for _, _, s in self.buffers.peers], amax)
 
     def wait_h_push_y(self, M: int) -> None:
         ops, b, es = self.ops, self.buffers, torch.empty(0, dtype=self.dtype).element_size()
-        # the wait for every rank's h shard is inside the quantizer's kernel
-        hq, sh = ops.quantize_act_after(b.h[:M], b.sync[0:1], b.seen[0:1], self.count_h)
+        if M >= self.amax_from:
+            first = PeerBuffers.AMAX_OFFSET // 4
+            sh = ops.wait_flag_scale(b.sync[0:1], b.seen[0:1], self.count_h, b.status,
+                                     b.sync[first:first + self.world])
+            hq = ops.cast_act(b.h[:M], sh)
+        else:
+            # the wait for every rank's h shard is inside the quantizer's kernel
+            hq, sh = ops.quantize_act_after(b.h[:M], b.sync[0:1], b.seen[0:1], self.count_h)
         col = self.h_ranges[self.rank][0]
         ops.gemm_push(hq, sh, self.down, self.dtype, [y + col * es for _, y, _ in b.peers], self.H,
                       [s + 4 for _, _, s in b.peers])
@@ -315,18 +333,18 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """The MLP output `[..., H]`.
 
-        At decode sizes the result is a VIEW of this rank's gathered `y` buffer, which every
+        Up to `rows_max` rows the result is a VIEW of this rank's gathered `y` buffer, which every
         rank overwrites during the next call on this object: consume it (or copy it) on the
         launching stream before calling again.  `copy_out = True` returns a fresh tensor instead
-        (one small device copy).  Larger M takes the NCCL form, which always returns a fresh
+        (one device copy).  Larger M takes the NCCL form, which always returns a fresh
         tensor.  Ranks must be barriered, with their warm-up done, before the first call: a peer
         that is more than the wait bound (about half a second) late makes the bounded waits run
         out, which `last_status()` reports."""
         *lead, K = x.shape
         x2 = x.reshape(-1, K)
         M = x2.shape[0]
-        if M > self.rows_max or M > 256 or x.dtype != self.dtype or not self.buffers.peers:
-            return super().forward(x)                    # prefill sizes: the NCCL form
+        if M > self.rows_max or x.dtype != self.dtype or not self.buffers.peers:
+            return super().forward(x)                    # beyond the buffers: the NCCL form
         self.push_h(x2)
         self.wait_h_push_y(M)
         y = self.wait_y(M)

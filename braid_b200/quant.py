@@ -1042,9 +1042,11 @@ def gemm_push(xq: torch.Tensor, sx: torch.Tensor, w: FP8Weight, out_dtype: torch
 
 def gate_up_silu_push(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: FP8Weight,
                       act_dtype: torch.dtype, dst_ptrs: Sequence[int], ld: int,
-                      flag_ptrs: Sequence[int]) -> None:
+                      flag_ptrs: Sequence[int], amax_ptrs: Sequence[int] | None = None) -> None:
     """This rank's slice of `F.silu(xq @ gate^T) * (xq @ up^T)` in one launch over its gate and
-    up shards, stored into every rank's gathered `h` buffer, followed by the signals."""
+    up shards, stored into every rank's gathered `h` buffer, followed by the signals.  At prefill
+    sizes (M > 256) `amax_ptrs` (this rank's word on every rank) also receive the slice's
+    max |h| ahead of the signals, for `wait_flag_scale`."""
     _check_gemm_inputs(xq, sx)
     lib = _require_lib()
     M, K = xq.shape
@@ -1054,6 +1056,7 @@ def gate_up_silu_push(xq: torch.Tensor, sx: torch.Tensor, gate: FP8Weight, up: F
                                        up.data.data_ptr(), gate.scale.data_ptr(), up.scale.data_ptr(), M,
                                        gate.data.shape[0], K, _DTYPE_CODE[act_dtype], len(dst_ptrs),
                                        _ptr_array(dst_ptrs), ld, _ptr_array(flag_ptrs),
+                                       _ptr_array(amax_ptrs) if amax_ptrs is not None else None,
                                        _take_slot(xq.device), 16, _stream_ptr(xq.device))
     _lib.check(rc, "gate_up_silu_push")
 
@@ -1067,6 +1070,22 @@ def wait_flag(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.
     rc = lib.bq_wait_flag(flag.data_ptr(), seen.data_ptr(), count, status.data_ptr(),
                           _stream_ptr(flag.device))
     _lib.check(rc, "wait_flag")
+
+
+def wait_flag_scale(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.Tensor,
+                    amax_words: torch.Tensor) -> torch.Tensor:
+    """`wait_flag`, then the `[1, 1]` quantization scale of the gathered `h` from the ranks'
+    max |h| words (`amax_words`: one int32 per rank, written by the ranks' `gate_up_silu_push`
+    launches ahead of their signals) -- the scale `quantize_act` of the whole tensor returns."""
+    global _launches
+    lib = _require_lib()
+    _launches += 1
+    scale = torch.empty((1, 1), dtype=torch.float32, device=flag.device)
+    rc = lib.bq_wait_flag_scale(flag.data_ptr(), seen.data_ptr(), count, status.data_ptr(),
+                                amax_words.data_ptr(), amax_words.numel(), scale.data_ptr(),
+                                _stream_ptr(flag.device))
+    _lib.check(rc, "wait_flag_scale")
+    return scale
 
 
 # ---------------------------------------------------------------------------

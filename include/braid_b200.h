@@ -357,8 +357,9 @@ int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_g
  * rank with a system-scope release (the CTAs count themselves on the first word of `ws`, which
  * must be zero before the first call and is returned to zero).  A rank's buffer is complete when
  * its counter has advanced by the number of ranks; bq_wait_flag waits for exactly that (bounded)
- * in stream order.  Plain stores and counters only: no collective call, no multicast.  Decode
- * regime (M <= 256), up to 8 destinations.
+ * in stream order.  Plain stores and counters only: no collective call, no multicast.  Up to
+ * 8 destinations; M <= 256 runs the weight-streaming kernel, larger M the CTA-pair kernel
+ * (destinations then 8-byte aligned).
  */
 
 /*
@@ -391,13 +392,18 @@ int bq_gemm_w8a8_push(const void* xq, const void* wq, const float* sx, const flo
 /*
  * h shard = T(T(silu(gate)) * up) of this rank's gate and up shards (two [I, K] tensors as for
  * bq_gate_up_silu_quant_w8a8, I = columns of this rank) pushed to every rank.  The amax of h
- * spans all ranks' shards, so quantization is left to bq_quantize_act on the gathered buffer.
+ * spans all ranks' shards: at decode sizes quantization is left to bq_quantize_act_after on the
+ * gathered buffer; at prefill sizes (M > 256) the launch also hands this rank's max |h| (the
+ * bits of the float) to every rank -- `amax_slots[i]` = the word for THIS rank on rank i, or
+ * NULL for none -- written before the arrivals, so that bq_wait_flag_scale + bq_cast_act
+ * replace the two-pass quantizer of the gathered tensor.  `ws`: 16 bytes as for the other GEMMs
+ * (the first two words are used and returned to zero).
  */
 int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_gate,
                               const void* wq_up, const float* sw_gate, const float* sw_up,
                               int64_t M, int64_t I,
                               int64_t K, int act_dtype, int n_peers, void* const* h_dst,
-                              int64_t ld_h, void* const* flags,
+                              int64_t ld_h, void* const* flags, void* const* amax_slots,
                               void* ws, size_t ws_bytes, void* stream);
 
 /*
@@ -406,6 +412,15 @@ int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_ga
  * *seen.  `flag` is this rank's arrival counter, `seen` a device word owned by this rank.
  */
 int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word, void* stream);
+
+/*
+ * bq_wait_flag, then *scale_out = the quantization scale of the gathered h: the maximum of the
+ * `n_slots` max |h| words the ranks' bq_gate_up_silu_push_w8a8 launches wrote (`amax_slots`,
+ * on this rank), turned into a scale as bq_quantize_act does.  The maximum of the shards'
+ * maxima is the maximum of the whole tensor: the scale of the unsharded quantizer, bit for bit.
+ */
+int bq_wait_flag_scale(const void* flag, void* seen, unsigned int count, void* status_word,
+                       const void* amax_slots, int n_slots, float* scale_out, void* stream);
 
 /*
  * bq_quantize_act on a gathered buffer, with the wait of bq_wait_flag folded into the kernel:

@@ -42,11 +42,13 @@ def _sharded_reference(Q, ranks, x):
     return h, torch.cat([Q.fp8_matmul(hq, sh, r.down, out_dtype=x.dtype) for r in ranks], dim=1)
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("world,M", [(w, m) for w in (2, 4, 8) for m in (1, 16, 128)]
+                         + [(2, 300), (4, 1000), (8, 700)])
 def test_fused_exchange_equals_the_gathered_spelling(Q, world, M):
+    """Decode sizes go through the weight-streaming kernel's push epilogues, M > 256 through the
+    CTA-pair kernel's (ragged row counts: clipped last tiles)."""
     weights = _weights(Q)
-    ranks = _emulated(Q, world, weights)
+    ranks = _emulated(Q, world, weights, rows_max=max(256, M))
     for call in range(3):                                   # buffers and counters are reused
         x = randn_cpu((M, H), seed=10 * M + call).cuda()
         for r in ranks:

@@ -36,7 +36,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     dev = torch.device("cuda", rank)
     Q.warm_fused(True)
     hidden, inter = 4096, 12288
-    mlp = FusedColumnParallelMLP.random_init(hidden, inter, dev, dist.group.WORLD, seed=1)
+    mlp = FusedColumnParallelMLP.random_init(hidden, inter, dev, dist.group.WORLD, seed=1, rows_max=1024)
     mlp.connect()
     # every rank can rebuild every shard (same seed): the unfused, gathered spelling, locally
     g = torch.Generator(device=dev).manual_seed(1)
@@ -44,7 +44,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     full = (mk(inter, hidden), mk(inter, hidden), mk(hidden, inter))
     shards = [FusedColumnParallelMLP(*full, ops=Q, world=world, rank=r) for r in range(world)]
     ok = True
-    for call, M in enumerate((1, 16, 128, 128)):
+    # decode sizes (weight-streaming kernel) and prefill sizes (CTA-pair kernel), buffers reused
+    for call, M in enumerate((1, 16, 128, 128, 300, 1000, 1000, 64)):
         gx = torch.Generator(device=dev).manual_seed(100 + call)      # same x on every rank
         x = torch.randn(M, hidden, generator=gx, device=dev).to(torch.bfloat16)
         y = mlp.forward(x).clone()
