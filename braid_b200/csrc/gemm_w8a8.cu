@@ -1035,12 +1035,12 @@ __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Se
           } else {
             // column-parallel form: the same piece into every rank's gathered buffer (plain
             // stores through peer-mapped pointers, this rank's own buffer included)
+            // 16-byte stores (destinations and row pitch are 16-byte aligned, checked by the
+            // host): 8 lanes write one whole 128-byte line, which is what the link moves well --
+            // halves of 32-byte sectors, as the 8-byte stores above produce, reached 0.3 TB/s
             const long long at = ((long long)m * p.push.ld + col) * ES;
-            for (int d = 0; d < p.push.n; ++d) {
-              uint8_t* dst = static_cast<uint8_t*>(p.push.dst[d]) + at;
-              *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
-              *reinterpret_cast<uint2*>(dst + 8) = make_uint2(v.z, v.w);
-            }
+            for (int d = 0; d < p.push.n; ++d)
+              *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.push.dst[d]) + at) = v;
           }
         }
       }
@@ -1653,10 +1653,13 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   if (pair && (res || n_seg != 1)) return kErrBadArg;
   if (push) {
     if (res || n_seg != 1) return kErrBadArg;
-    // the prefill kernel stores 16-byte pieces as two 8-byte words
-    if (!stream_path)
+    // the prefill kernel stores 16-byte pieces
+    if (!stream_path) {
+      const long long es = out_dtype == BQ_DTYPE_F32 ? 4 : 2;
+      if ((push->ld * es) % 16) return kErrUnsupported;
       for (int d = 0; d < push->n; ++d)
-        if (!aligned_to(push->dst[d], 8)) return kErrUnsupported;
+        if (!aligned_to(push->dst[d], 16)) return kErrUnsupported;
+    }
   }
   if (res != nullptr) {   // the residual epilogue exists in the weight-streaming kernel only
     if (!stream_path || ld_res == nullptr) return kErrUnsupported;

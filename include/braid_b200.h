@@ -359,7 +359,7 @@ int bq_gate_up_silu_quant_w8a8(const void* xq, const float* sx, const void* wq_g
  * its counter has advanced by the number of ranks; bq_wait_flag waits for exactly that (bounded)
  * in stream order.  Plain stores and counters only: no collective call, no multicast.  Up to
  * 8 destinations; M <= 256 runs the weight-streaming kernel, larger M the CTA-pair kernel
- * (destinations then 8-byte aligned).
+ * (destinations and their row pitch then 16-byte aligned).
  */
 
 /*
