@@ -62,7 +62,12 @@ SIGNATURES = {
                                          ctypes.POINTER(_vp), _i64, ctypes.POINTER(_vp),
                                          ctypes.POINTER(_vp), _vp, _sz, _vp]),
     "bq_wait_flag": (_int, [_vp, _vp, ctypes.c_uint, _vp, _vp]),
-    "bq_wait_flag_scale": (_int, [_vp, _vp, ctypes.c_uint, _vp, _vp, _int, _vp, _vp]),
+    "bq_wait_flag_scale": (_int, [_vp, _vp, ctypes.c_uint, _vp, _vp, _int, _int, _vp, _vp]),
+    "bq_word_push": (_int, [_vp, _int, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp]),
+    "bq_cast_act_push": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _int, ctypes.POINTER(_vp), _i64,
+                                ctypes.POINTER(_vp), _vp, _sz, _vp]),
+    "bq_rows_push": (_int, [_vp, _int, _i64, _i64, _i64, _int, ctypes.POINTER(_vp), _i64,
+                            ctypes.POINTER(_vp), _vp, _sz, _vp]),
     "bq_quantize_act_after": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _vp, ctypes.c_uint, _vp, _sz, _vp]),
     "bq_gemm_w8a8_grouped": (_int, [_vp, _vp, _i64, _i64, _int,
                                     ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),

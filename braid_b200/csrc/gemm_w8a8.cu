@@ -846,7 +846,7 @@ __global__ void wait_flag_kernel(const unsigned int* flag, unsigned int* seen, u
 // whole tensor, so this is the scale the unsharded quantizer computes, bit for bit.
 __global__ void wait_flag_scale_kernel(const unsigned int* flag, unsigned int* seen, unsigned int count,
                                        unsigned int* status, const unsigned int* amax_slots, int n,
-                                       float* scale_out) {
+                                       int slots_hold_scales, float* scale_out) {
   const unsigned int target = *seen + count;
   const long long t0 = clock64();
   for (;;) {
@@ -864,7 +864,9 @@ __global__ void wait_flag_scale_kernel(const unsigned int* flag, unsigned int* s
     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(b) : "l"(amax_slots + i) : "memory");
     best = b > best ? b : best;      // |h| bit patterns order like the values, NaN on top
   }
-  *scale_out = bq::qd::scale_from_amax(__uint_as_float(best));
+  // the scale is a monotone function of the amax (and its lower clamp commutes with max), so
+  // the maximum of the ranks' scales is the scale of the maximum
+  *scale_out = slots_hold_scales ? __uint_as_float(best) : bq::qd::scale_from_amax(__uint_as_float(best));
   *seen = target;
   __threadfence();
 }
@@ -1013,7 +1015,11 @@ __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Se
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(ymap, box_addr, n0 + c, m_row0);
+        // column-parallel form: the same box into every rank's gathered buffer (ymap[d] then
+        // describes rank d's buffer at this rank's columns; peers' buffers are reached through
+        // peer-mapped addresses by plain, non-multicast bulk stores)
+        const int n_dst = p.push.n > 0 ? p.push.n : 1;
+        for (int d = 0; d < n_dst; ++d) tma_store_2d(ymap + d, box_addr, n0 + c, m_row0);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     } else {
@@ -1188,24 +1194,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
       if (silu) {
         const float scale_up = sx * __ldg(p.pair.sw_up);
         if (p.out_dtype == BQ_DTYPE_F32)
-          pair_epilogue_rows<4, true>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, scale_up,
+          pair_epilogue_rows<4, true>(p, seg, &tm_y.y[p.push.n > 0 ? 0 : sg], use_tma, taddr, scale, scale_up,
                                       m0 + quad * 32, n0, stage, stage_addr, lane, col_half, h_max);
         else
-          pair_epilogue_rows<2, true>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, scale_up,
+          pair_epilogue_rows<2, true>(p, seg, &tm_y.y[p.push.n > 0 ? 0 : sg], use_tma, taddr, scale, scale_up,
                                       m0 + quad * 32, n0, stage, stage_addr, lane, col_half, h_max);
       } else if (p.out_dtype == BQ_DTYPE_F32) {
-        pair_epilogue_rows<4, false>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
+        pair_epilogue_rows<4, false>(p, seg, &tm_y.y[p.push.n > 0 ? 0 : sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
                                      n0, stage, stage_addr, lane, col_half, h_max);
       } else {
-        pair_epilogue_rows<2, false>(p, seg, &tm_y.y[sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
+        pair_epilogue_rows<2, false>(p, seg, &tm_y.y[p.push.n > 0 ? 0 : sg], use_tma, taddr, scale, 0.0f, m0 + quad * 32,
                                      n0, stage, stage_addr, lane, col_half, h_max);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(b == 0 ? leader_acc_empty0 : leader_acc_empty1);
     }
-    // the boxes must stay valid until the last stores have read them
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // the boxes must stay valid until the last stores have read them; for the column-parallel
+    // form the wait also means the stores have been written, before anybody is told to look
+    if (lane == 0) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (p.push.n > 0) asm volatile("fence.proxy.async;" ::: "memory");
+    }
     __syncwarp();
     if (!ok) *abort_flag = 1;
     if (p.push.n > 0) {
@@ -1355,6 +1365,7 @@ int device_sms() {
 }
 
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
+long long g_opt_push_tma = 1;   // prefill push epilogue: bulk tensor stores (0: 16-byte plain stores)
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_b_stages = 0;   // activation ring depth: 0 = heuristic, -1 = as deep as the weight ring
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
@@ -1588,6 +1599,7 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_stages") == 0) { g_opt_stages = value; return kOk; }
   if (strcmp(key, "decode_b_stages") == 0) { g_opt_b_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
+  if (strcmp(key, "push_tma") == 0) { g_opt_push_tma = value ? 1 : 0; return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
@@ -1726,6 +1738,13 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
       const size_t es = out_dtype == BQ_DTYPE_F32 ? 4 : 2;
       p.seg[i].y_tma = aligned_to(y[i], 16) && (ldy[i] * es) % 16 == 0 &&
                        make_out_map(&ymaps.y[i], y[i], M, N[i], ldy[i], out_dtype) == kOk;
+    }
+    if (pair_path && push && g_opt_push_tma) {
+      // one map per destination rank over its [M, N shard] window (n_seg is 1 for a push)
+      bool ok = true;
+      for (int d = 0; d < push->n && ok; ++d)
+        ok = make_out_map(&ymaps.y[d], push->dst[d], M, N[i], push->ld, out_dtype) == kOk;
+      p.seg[i].y_tma = ok ? 1 : 0;
     }
     if (pair && pair->prefill) {
       // two maps over the two weights, 128-row boxes: one CTA of a pair loads gate rows, the other
@@ -1972,9 +1991,38 @@ extern "C" int bq_wait_flag(const void* flag, void* seen, unsigned int count, vo
   return kOk;
 }
 
+// One thread: the 4-byte word at `word` (a scale, a max) into `dst_words[i]` on every rank, then
+// one arrival on every rank's counter, the word first (system-scope release on the counters).
+__global__ void word_push_kernel(const unsigned int* word, int n, PushParams dst) {
+  const unsigned int v = __ldcg(word);
+  for (int d = 0; d < n; ++d)
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst.amax_dst[d]), "r"(v) : "memory");
+  __threadfence_system();
+  for (int d = 0; d < n; ++d)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(dst.flag[d]) : "memory");
+}
+
+extern "C" int bq_word_push(const void* word, int n_peers, void* const* dst_words, void* const* flags,
+                            void* stream) {
+  if (!word || !dst_words || !flags || n_peers < 1 || n_peers > kMaxPeers) return kErrBadArg;
+  if (!aligned_to(word, 4)) return kErrUnsupported;
+  PushParams pp;
+  memset(&pp, 0, sizeof(pp));
+  for (int i = 0; i < n_peers; ++i) {
+    if (!dst_words[i] || !flags[i]) return kErrBadArg;
+    if (!aligned_to(dst_words[i], 4) || !aligned_to(flags[i], 4)) return kErrUnsupported;
+    pp.amax_dst[i] = static_cast<unsigned int*>(dst_words[i]);
+    pp.flag[i] = static_cast<unsigned int*>(flags[i]);
+  }
+  word_push_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(word),
+                                                                   n_peers, pp);
+  if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
+  return kOk;
+}
+
 extern "C" int bq_wait_flag_scale(const void* flag, void* seen, unsigned int count, void* status_word,
-                                  const void* amax_slots, int n_slots, float* scale_out,
-                                  void* stream) {
+                                  const void* amax_slots, int n_slots, int slots_hold_scales,
+                                  float* scale_out, void* stream) {
   if (!flag || !seen || !status_word || !amax_slots || !scale_out || count == 0) return kErrBadArg;
   if (n_slots < 1 || n_slots > kMaxPeers) return kErrBadArg;
   if (!aligned_to(flag, 4) || !aligned_to(seen, 4) || !aligned_to(status_word, 4) ||
@@ -1983,7 +2031,7 @@ extern "C" int bq_wait_flag_scale(const void* flag, void* seen, unsigned int cou
   wait_flag_scale_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned int*>(flag), static_cast<unsigned int*>(seen), count,
       static_cast<unsigned int*>(status_word), static_cast<const unsigned int*>(amax_slots), n_slots,
-      scale_out);
+      slots_hold_scales, scale_out);
   if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
   return kOk;
 }

@@ -29,6 +29,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/braid_b200.h"
 #include "ptx.cuh"
@@ -440,6 +441,70 @@ __global__ void __launch_bounds__(256) prologue_dense_kernel(const QParams p, T*
   }
 }
 
+// ---- column-parallel form: one rank's [rows, cols] block to every rank ----------------------
+// Elementwise: every thread takes 8 values of a row of this rank's block and stores them --
+// as e4m3 codes under a given scale (CAST) or unchanged -- at the same row and column of every
+// rank's gathered buffer (plain stores through peer-mapped pointers, this rank's own buffer
+// included; the pointers already carry this rank's column offset).  A warp writes 256 (codes) or
+// 512 contiguous bytes of a row per destination, which the links move at their copy rate; the
+// 128-byte pieces a GEMM epilogue scatters over rows do not.  The CTAs count themselves on a
+// local word and the last one adds 1 to every rank's arrival counter with a system-scope
+// release, as the GEMM push epilogues do.
+struct RowPush {
+  const void* src;
+  long long ld_src;               // elements
+  int rows, groups_per_row;       // groups of 8 columns
+  const float* scale;             // CAST: device scalar
+  int n;
+  void* dst[8];
+  long long ld_dst;               // elements of the destination (bytes for codes)
+  unsigned int* flag[8];
+  unsigned int* done;             // local, zero between launches
+};
+
+template <typename T, bool CAST>
+__global__ void __launch_bounds__(256) row_push_kernel(const RowPush p) {
+  bq::pdl_launch_dependents();
+  bq::pdl_wait_prior_grids();
+  float sc = 1.0f;
+  if constexpr (CAST) sc = __ldcg(p.scale);
+  const ScaleDiv dv(sc);
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* src = reinterpret_cast<const T*>(p.src) + (long long)row * p.ld_src;
+    for (int g = threadIdx.x; g < p.groups_per_row; g += blockDim.x) {
+      const Pack8<T> v = load8<T, false>(src + g * kGroup);
+      const long long at = (long long)row * p.ld_dst + g * kGroup;
+      if constexpr (CAST) {
+        const uint2 c = codes8<T, false>(v, dv);
+        for (int d = 0; d < p.n; ++d) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst[d]) + at) = c;
+      } else if constexpr (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(&v);
+        for (int d = 0; d < p.n; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.dst[d]) + at) = raw;
+      } else {
+        const float4 lo = make_float4(v.v[0], v.v[1], v.v[2], v.v[3]);
+        const float4 hi = make_float4(v.v[4], v.v[5], v.v[6], v.v[7]);
+        for (int d = 0; d < p.n; ++d) {
+          float4* q = reinterpret_cast<float4*>(static_cast<T*>(p.dst[d]) + at);
+          q[0] = lo;
+          q[1] = hi;
+        }
+      }
+    }
+  }
+  // every store of the launch happens before every arrival (see the GEMM push epilogue)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int old = atomicAdd(p.done, 1u);
+    if (old == gridDim.x - 1u) {
+      *p.done = 0u;
+      __threadfence_system();
+      for (int d = 0; d < p.n; ++d)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.flag[d]) : "memory");
+    }
+  }
+}
+
 struct DeviceInfo {
   int sms = 0;
 };
@@ -832,6 +897,83 @@ extern "C" int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_
   p.chunk = static_cast<unsigned int>(chunk);
   p.chunk_stride = chunk_stride;
   return launch_dense<kSigmoidGate>(dtype, p, out, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+template <bool CAST>
+int launch_row_push(int dtype, const RowPush& p, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return bq::kErrLaunch;
+  const int grid = p.rows < 8 * sms ? p.rows : 8 * sms;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_quant_pdl ? 1 : 0;
+  cudaError_t e;
+  switch (dtype) {
+    case BQ_DTYPE_F32: e = cudaLaunchKernelEx(&cfg, row_push_kernel<float, CAST>, p); break;
+    case BQ_DTYPE_BF16: e = cudaLaunchKernelEx(&cfg, row_push_kernel<__nv_bfloat16, CAST>, p); break;
+    case BQ_DTYPE_F16: e = cudaLaunchKernelEx(&cfg, row_push_kernel<__half, CAST>, p); break;
+    default: return bq::kErrBadArg;
+  }
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
+  return bq::kOk;
+}
+
+int fill_row_push(RowPush* p, const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                  int n_peers, void* const* dst, int64_t ld_dst, void* const* flags, void* ws,
+                  size_t ws_bytes, size_t out_elem) {
+  if (!x || !dst || !flags || rows <= 0 || cols <= 0 || n_peers < 1 || n_peers > 8) return bq::kErrBadArg;
+  if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  const size_t es = elem_size(dtype);
+  if (cols % kGroup || ld_x < cols || (ld_x * es) % 16 || !aligned_to(x, 16) || ld_dst < cols ||
+      (ld_dst * out_elem) % (8 * out_elem > 16 ? 16 : 8 * out_elem))
+    return bq::kErrUnsupported;
+  if (rows > 0x7fffffffLL || cols > 0x7fffffffLL) return bq::kErrTooLarge;
+  memset(p, 0, sizeof(*p));
+  p->src = x;
+  p->ld_src = ld_x;
+  p->rows = (int)rows;
+  p->groups_per_row = (int)(cols / kGroup);
+  p->n = n_peers;
+  p->ld_dst = ld_dst;
+  p->done = static_cast<unsigned int*>(ws);
+  for (int i = 0; i < n_peers; ++i) {
+    if (!dst[i] || !flags[i]) return bq::kErrBadArg;
+    if (!aligned_to(dst[i], 8 * out_elem > 16 ? 16 : 8 * out_elem) || !aligned_to(flags[i], 4))
+      return bq::kErrUnsupported;
+    p->dst[i] = dst[i];
+    p->flag[i] = static_cast<unsigned int*>(flags[i]);
+  }
+  return bq::kOk;
+}
+}  // namespace
+
+extern "C" int bq_cast_act_push(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                                const float* scale, int n_peers, void* const* q_dst, int64_t ld_q,
+                                void* const* flags, void* ws, size_t ws_bytes, void* stream) {
+  if (!scale) return bq::kErrBadArg;
+  RowPush p;
+  if (int rc = fill_row_push(&p, x, dtype, rows, cols, ld_x, n_peers, q_dst, ld_q, flags, ws, ws_bytes, 1))
+    return rc;
+  p.scale = scale;
+  return launch_row_push<true>(dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bq_rows_push(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                            int n_peers, void* const* dst, int64_t ld_dst, void* const* flags,
+                            void* ws, size_t ws_bytes, void* stream) {
+  RowPush p;
+  if (int rc = fill_row_push(&p, x, dtype, rows, cols, ld_x, n_peers, dst, ld_dst, flags, ws, ws_bytes,
+                             elem_size(dtype)))
+    return rc;
+  return launch_row_push<false>(dtype, p, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------

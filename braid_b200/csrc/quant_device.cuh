@@ -164,8 +164,9 @@ __device__ __forceinline__ float quant_one(float x, const ScaleDiv& d) {
   return v[0];
 }
 
+// the 8 e4m3 codes of one group, as two 32-bit words
 template <typename T, bool OWN_SCALE = false>
-__device__ __forceinline__ void emit8(const Pack8<T>& v, const ScaleDiv& sc, uint8_t* dst) {
+__device__ __forceinline__ uint2 codes8(const Pack8<T>& v, const ScaleDiv& sc) {
   float f[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) f[i] = widen(v.v[i]);
@@ -177,7 +178,12 @@ __device__ __forceinline__ void emit8(const Pack8<T>& v, const ScaleDiv& sc, uin
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[half * 4 + 2], f[half * 4 + 3]), __NV_SATFINITE, __NV_E4M3);
     w[half] = (lo & 0xFFFFu) | ((hi & 0xFFFFu) << 16);
   }
-  *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+  return make_uint2(w[0], w[1]);
+}
+
+template <typename T, bool OWN_SCALE = false>
+__device__ __forceinline__ void emit8(const Pack8<T>& v, const ScaleDiv& sc, uint8_t* dst) {
+  *reinterpret_cast<uint2*>(dst) = codes8<T, OWN_SCALE>(v, sc);
 }
 
 __device__ __forceinline__ float scale_from_amax(float amax) {

@@ -167,9 +167,10 @@ def _align(n: int, a: int = 256) -> int:
 class PeerBuffers:
     """One rank's gathered buffers and counters, plus where the other ranks' copies are.
 
-    `h` `[rows_max, I]` and `y` `[rows_max, H]` receive every rank's column slice; `sync` holds
-    the two arrival counters (h, y) that the other ranks increment and, from byte 64, one word
-    per rank for that rank's max |h| (prefill sizes).  The three live in ONE device
+    `h` `[rows_max, I]` and `y` `[rows_max, H]` receive every rank's column slice (`hq`, the
+    e4m3 codes of h that prefill sizes exchange instead, shares h's bytes); `sync` holds the
+    arrival counters the other ranks increment (word 0: h or the shard scales, 1: y, 2: codes)
+    and, from byte 64, one word per rank for that rank's shard scale or max |h|.  The three live in ONE device
     allocation made by the library (`bq_peer_alloc`), because it has to be exported to the other
     processes as a whole; `seen` and `status` are private to the rank.  `peers[r]` is rank r's
     (h, y, sync) device addresses as they are valid on THIS rank."""
@@ -194,9 +195,11 @@ class PeerBuffers:
         raw = torch.as_tensor(_DeviceBlock(self.base, self.nbytes), device=self.device)
         self._raw = raw
         self.h = raw[self.off_h:self.off_h + rows_max * inter * es].view(dtype).view(rows_max, inter)
+        # the gathered e4m3 codes of h (prefill sizes exchange codes, not values) share h's bytes
+        self.hq = raw[self.off_h:self.off_h + rows_max * inter].view(rows_max, inter)
         self.y = raw[self.off_y:self.off_y + rows_max * hidden * es].view(dtype).view(rows_max, hidden)
         self.sync = raw[self.off_sync:self.off_sync + 256].view(torch.int32)
-        self.seen = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.seen = torch.zeros(3, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.peers: list[tuple[int, int, int]] = []
         self._opened: list[int] = []
@@ -240,7 +243,7 @@ class PeerBuffers:
             if group is not None:
                 dist.barrier(group=group)
             if self.base:
-                self.h = self.y = self.sync = self._raw = None
+                self.h = self.hq = self.y = self.sync = self._raw = None
                 self._lib.bq_peer_free(self.base)
                 self.base = 0
         self.peers = []
@@ -294,27 +297,65 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
     def close(self) -> None:
         self.buffers.close(self.group)
 
-    # -- the four phases (a test interleaves them over emulated ranks; forward() runs them in order)
-    # From this many rows on, the gate/up launch hands its shard's max |h| to every rank and the
-    # consumer is a one-thread wait that also forms the scale, then the cast pass; below it the
-    # quantizer of the gathered h waits in its own kernel (one launch fewer).
+    # -- the phases (a test interleaves them over emulated ranks; forward() runs them in order)
+    # Prefill sizes (from `codes_from` rows on) exchange h as e4m3 CODES: the gate/up GEMM keeps
+    # its shard of h local and returns the shard's scale; the scales go round as 4-byte words;
+    # a one-thread kernel waits for them and takes their maximum (the scale of the whole h); an
+    # elementwise kernel casts the shard and stores the codes into every rank's buffer, a warp
+    # writing 256 contiguous bytes per rank.  Half the bytes of the bf16 exchange and whole
+    # lines on the links.  `prefill_form = "epilogue"` selects the other spelling: bf16 pieces
+    # pushed from the GEMM's epilogue (overlapped with the GEMM, but 128-byte pieces scattered
+    # over rows move at about two thirds of the links' copy rate) and the shard's max |h| ahead
+    # of the arrivals.  Decode sizes: bf16 from the epilogue, the quantizer of the gathered h
+    # waits in its own kernel (fewest launches).
     amax_from = 257
+    prefill_form = "codes"
+    _codes = False
+    _h_local = None
+    _sh = None
+
+    def _slot_ptrs(self):
+        return [s + PeerBuffers.AMAX_OFFSET + 4 * self.rank for _, _, s in self.buffers.peers]
 
     def push_h(self, x2: torch.Tensor) -> None:
         ops, es = self.ops, torch.empty(0, dtype=self.dtype).element_size()
         xq, sx = ops.quantize_act(x2)
         col = self.i_ranges[self.rank][0]
-        amax = None
-        if x2.shape[0] >= self.amax_from:
-            amax = [s + PeerBuffers.AMAX_OFFSET + 4 * self.rank for _, _, s in self.buffers.peers]
+        prefill = x2.shape[0] >= self.amax_from
+        self._codes = False
+        if prefill and self.prefill_form == "codes":
+            got = ops.gate_up_silu(xq, sx, self.gate, self.up, self.dtype)
+            if got is not None:
+                self._h_local, sh_local = got
+                self._codes = True
+                ops.word_push(sh_local, self._slot_ptrs(), [s for _, _, s in self.buffers.peers])
+                return
         ops.gate_up_silu_push(xq, sx, self.gate, self.up, self.dtype,
                               [h + col * es for h, _, _ in self.buffers.peers], self.I,
-                              [s for _, _, s in self.buffers.peers], amax)
+                              [s for _, _, s in self.buffers.peers],
+                              self._slot_ptrs() if prefill else None)
+
+    def push_codes(self, M: int) -> None:
+        """Codes form only: wait for every rank's shard scale, cast this rank's shard under their
+        maximum and store the codes into every rank's buffer."""
+        if not (M >= self.amax_from and self._codes):
+            return
+        ops, b = self.ops, self.buffers
+        first = PeerBuffers.AMAX_OFFSET // 4
+        self._sh = ops.wait_flag_scale(b.sync[0:1], b.seen[0:1], self.count_h, b.status,
+                                       b.sync[first:first + self.world], words_are_scales=True)
+        col = self.i_ranges[self.rank][0]
+        ops.cast_act_push(self._h_local, self._sh, [h + col for h, _, _ in b.peers], self.I,
+                          [s + 8 for _, _, s in b.peers])
+        self._h_local = None
 
     def wait_h_push_y(self, M: int) -> None:
         ops, b, es = self.ops, self.buffers, torch.empty(0, dtype=self.dtype).element_size()
-        if M >= self.amax_from:
-            first = PeerBuffers.AMAX_OFFSET // 4
+        first = PeerBuffers.AMAX_OFFSET // 4
+        if M >= self.amax_from and self._codes:
+            ops.wait_flag(b.sync[2:3], b.seen[2:3], self.world, b.status)
+            hq, sh = b.hq[:M].view(ops.FP8), self._sh
+        elif M >= self.amax_from:
             sh = ops.wait_flag_scale(b.sync[0:1], b.seen[0:1], self.count_h, b.status,
                                      b.sync[first:first + self.world])
             hq = ops.cast_act(b.h[:M], sh)
@@ -346,6 +387,7 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         if M > self.rows_max or x.dtype != self.dtype or not self.buffers.peers:
             return super().forward(x)                    # beyond the buffers: the NCCL form
         self.push_h(x2)
+        self.push_codes(M)
         self.wait_h_push_y(M)
         y = self.wait_y(M)
         if self.copy_out:

@@ -1073,19 +1073,55 @@ def wait_flag(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.
 
 
 def wait_flag_scale(flag: torch.Tensor, seen: torch.Tensor, count: int, status: torch.Tensor,
-                    amax_words: torch.Tensor) -> torch.Tensor:
+                    words: torch.Tensor, words_are_scales: bool = False) -> torch.Tensor:
     """`wait_flag`, then the `[1, 1]` quantization scale of the gathered `h` from the ranks'
-    max |h| words (`amax_words`: one int32 per rank, written by the ranks' `gate_up_silu_push`
-    launches ahead of their signals) -- the scale `quantize_act` of the whole tensor returns."""
+    words (one int32 per rank): max |h| of each shard (written by `gate_up_silu_push` ahead of
+    its signals) or, with `words_are_scales`, each shard's scale (`word_push`) -- either way the
+    scale `quantize_act` of the whole tensor returns."""
     global _launches
     lib = _require_lib()
     _launches += 1
     scale = torch.empty((1, 1), dtype=torch.float32, device=flag.device)
     rc = lib.bq_wait_flag_scale(flag.data_ptr(), seen.data_ptr(), count, status.data_ptr(),
-                                amax_words.data_ptr(), amax_words.numel(), scale.data_ptr(),
-                                _stream_ptr(flag.device))
+                                words.data_ptr(), words.numel(), 1 if words_are_scales else 0,
+                                scale.data_ptr(), _stream_ptr(flag.device))
     _lib.check(rc, "wait_flag_scale")
     return scale
+
+
+def word_push(word: torch.Tensor, dst_ptrs: Sequence[int], flag_ptrs: Sequence[int]) -> None:
+    """The 4-byte `word` (a `[1, 1]` scale) into every rank's slot for this rank, then one
+    arrival on every rank's counter."""
+    global _launches
+    _launches += 1
+    rc = _require_lib().bq_word_push(word.data_ptr(), len(dst_ptrs), _ptr_array(dst_ptrs),
+                                     _ptr_array(flag_ptrs), _stream_ptr(word.device))
+    _lib.check(rc, "word_push")
+
+
+def cast_act_push(x: torch.Tensor, scale: torch.Tensor, dst_ptrs: Sequence[int], ld: int,
+                  flag_ptrs: Sequence[int]) -> None:
+    """e4m3 codes of this rank's `[M, n]` block under `scale`, stored at the same rows of every
+    rank's gathered code buffer (`dst_ptrs`: device addresses of this rank's first column, row
+    pitch `ld` bytes), then one arrival per rank."""
+    _check_cuda(x, "cast_act_push")
+    M, n = x.shape
+    rc = _require_lib().bq_cast_act_push(x.data_ptr(), _DTYPE_CODE[x.dtype], M, n, x.stride(0),
+                                         scale.data_ptr(), len(dst_ptrs), _ptr_array(dst_ptrs), ld,
+                                         _ptr_array(flag_ptrs), _take_slot(x.device), 16,
+                                         _stream_ptr(x.device))
+    _lib.check(rc, "cast_act_push")
+
+
+def rows_push(x: torch.Tensor, dst_ptrs: Sequence[int], ld: int, flag_ptrs: Sequence[int]) -> None:
+    """This rank's `[M, n]` block, unchanged, to the same rows of every rank's gathered buffer
+    (row pitch `ld` elements), then one arrival per rank."""
+    _check_cuda(x, "rows_push")
+    M, n = x.shape
+    rc = _require_lib().bq_rows_push(x.data_ptr(), _DTYPE_CODE[x.dtype], M, n, x.stride(0),
+                                     len(dst_ptrs), _ptr_array(dst_ptrs), ld, _ptr_array(flag_ptrs),
+                                     _take_slot(x.device), 16, _stream_ptr(x.device))
+    _lib.check(rc, "rows_push")
 
 
 # ---------------------------------------------------------------------------

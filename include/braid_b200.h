@@ -414,13 +414,42 @@ int bq_gate_up_silu_push_w8a8(const void* xq, const float* sx, const void* wq_ga
 int bq_wait_flag(const void* flag, void* seen, unsigned int count, void* status_word, void* stream);
 
 /*
- * bq_wait_flag, then *scale_out = the quantization scale of the gathered h: the maximum of the
- * `n_slots` max |h| words the ranks' bq_gate_up_silu_push_w8a8 launches wrote (`amax_slots`,
- * on this rank), turned into a scale as bq_quantize_act does.  The maximum of the shards'
- * maxima is the maximum of the whole tensor: the scale of the unsharded quantizer, bit for bit.
+ * bq_wait_flag, then *scale_out = the quantization scale of the gathered h from the `n_slots`
+ * words the ranks wrote on this rank (`amax_slots`): either max |h| of each rank's shard
+ * (bq_gate_up_silu_push_w8a8; slots_hold_scales = 0: the maximum is turned into a scale as
+ * bq_quantize_act does) or each shard's scale (bq_word_push of the scale bq_gate_up_silu_w8a8
+ * returned; slots_hold_scales = 1: the maximum IS the scale, the scale being a monotone function
+ * of the amax).  The maximum over the shards is the maximum over the tensor: the scale of the
+ * unsharded quantizer, bit for bit.
  */
 int bq_wait_flag_scale(const void* flag, void* seen, unsigned int count, void* status_word,
-                       const void* amax_slots, int n_slots, float* scale_out, void* stream);
+                       const void* amax_slots, int n_slots, int slots_hold_scales, float* scale_out,
+                       void* stream);
+
+/*
+ * One-thread kernel: the 4-byte word at `word` into `dst_words[i]` on every rank (peer-mapped
+ * pointers, this rank's own included), then one arrival on every rank's counter `flags[i]`.
+ */
+int bq_word_push(const void* word, int n_peers, void* const* dst_words, void* const* flags,
+                 void* stream);
+
+/*
+ * One rank's [rows, cols] block to every rank of the node, elementwise, by plain stores through
+ * peer-mapped pointers (`dst[i]` already offset to this rank's first column in rank i's
+ * gathered buffer, row pitch ld_dst), then one arrival per rank (`flags[i]`), counted as in the
+ * GEMM push forms on the first word of `ws` (16 bytes, zero between launches).
+ * bq_cast_act_push stores the e4m3 codes of the block under `*scale` (bq_cast_act's
+ * arithmetic): a warp writes 256 contiguous bytes of a row per destination, which NVLink moves
+ * at its copy rate -- the way a column-parallel MLP exchanges h as codes once the shards'
+ * scales have been combined (bq_word_push + bq_wait_flag_scale).  bq_rows_push stores the
+ * block unchanged.  cols a multiple of 8; x and its pitch 16-byte aligned.
+ */
+int bq_cast_act_push(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                     const float* scale, int n_peers, void* const* q_dst, int64_t ld_q,
+                     void* const* flags, void* ws, size_t ws_bytes, void* stream);
+int bq_rows_push(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x, int n_peers,
+                 void* const* dst, int64_t ld_dst, void* const* flags, void* ws, size_t ws_bytes,
+                 void* stream);
 
 /*
  * bq_quantize_act on a gathered buffer, with the wait of bq_wait_flag folded into the kernel:

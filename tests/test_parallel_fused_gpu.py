@@ -42,23 +42,34 @@ def _sharded_reference(Q, ranks, x):
     return h, torch.cat([Q.fp8_matmul(hq, sh, r.down, out_dtype=x.dtype) for r in ranks], dim=1)
 
 
-@pytest.mark.parametrize("world,M", [(w, m) for w in (2, 4, 8) for m in (1, 16, 128)]
-                         + [(2, 300), (4, 1000), (8, 700)])
-def test_fused_exchange_equals_the_gathered_spelling(Q, world, M):
-    """Decode sizes go through the weight-streaming kernel's push epilogues, M > 256 through the
-    CTA-pair kernel's (ragged row counts: clipped last tiles)."""
+@pytest.mark.parametrize("world,M,form", [(w, m, "codes") for w in (2, 4, 8) for m in (1, 16, 128)]
+                         + [(2, 300, "codes"), (4, 1000, "codes"), (8, 700, "codes"),
+                            (2, 300, "epilogue"), (4, 1000, "epilogue"), (8, 700, "epilogue")])
+def test_fused_exchange_equals_the_gathered_spelling(Q, world, M, form):
+    """Decode sizes go through the weight-streaming kernel's push epilogues.  M > 256 (ragged row
+    counts: clipped last tiles) either exchange e4m3 codes -- shard scales as words, their
+    maximum, an elementwise cast-and-store kernel -- or push bf16 pieces from the CTA-pair
+    kernel's epilogue with the shard's max |h| ahead of the arrivals."""
     weights = _weights(Q)
     ranks = _emulated(Q, world, weights, rows_max=max(256, M))
+    for r in ranks:
+        r.prefill_form = form
     for call in range(3):                                   # buffers and counters are reused
         x = randn_cpu((M, H), seed=10 * M + call).cuda()
         for r in ranks:
             r.push_h(x)
         for r in ranks:
+            r.push_codes(M)
+        for r in ranks:
             r.wait_h_push_y(M)
         outs = [r.wait_y(M).clone() for r in ranks]
         h_ref, y_ref = _sharded_reference(Q, ranks, x)
+        hq_ref = Q.quantize_act(h_ref)[0].view(torch.uint8)
         for r, y in zip(ranks, outs):
-            assert torch.equal(r.buffers.h[:M], h_ref), f"rank {r.rank}: gathered h differs (call {call})"
+            if M >= r.amax_from and r.prefill_form == "codes":   # prefill sizes exchange codes
+                assert torch.equal(r.buffers.hq[:M], hq_ref), f"rank {r.rank}: gathered codes differ (call {call})"
+            else:
+                assert torch.equal(r.buffers.h[:M], h_ref), f"rank {r.rank}: gathered h differs (call {call})"
             assert torch.equal(y, y_ref), f"rank {r.rank}: gathered y differs (call {call})"
             assert int(r.buffers.status.item()) == 0
         # against the unsharded MLP: same codes and scales, GEMM sums within the bf16 tolerance
