@@ -400,7 +400,8 @@ def column_parallel_block(dist, rows_list, steps, warmup):
     out = {}
     for rows in rows_list:
         mlp = ColumnParallelMLP.random_init(4096, 12288, torch.device("cuda"), dist.group.WORLD, seed=1)
-        x = torch.randn(rows, 4096, device="cuda").to(torch.bfloat16)
+        gx = torch.Generator(device="cuda").manual_seed(7)       # the same activation on every rank
+        x = torch.randn(rows, 4096, generator=gx, device="cuda").to(torch.bfloat16)
         fn = lambda: mlp.forward(x)  # noqa: E731
         # one CUDA graph per rank holding the kernels AND the two NCCL all-gathers, replayed like
         # the decode step; eager launches if the collective cannot be captured here
@@ -421,7 +422,7 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         del mlp
         # the same sharded MLP with the all-gathers folded into the GEMM epilogues (peer-mapped
         # buffers over CUDA IPC, per-rank arrival counters, no collective)
-        if True:
+        if True:   # decode sizes and prefill sizes alike
             try:
                 from braid_b200.parallel import FusedColumnParallelMLP
                 fmlp = FusedColumnParallelMLP.random_init(4096, 12288, torch.device("cuda"),
@@ -436,9 +437,14 @@ def column_parallel_block(dist, rows_list, steps, warmup):
                 entry["fused"] = {"ms_per_call": msf / steps,
                                   "equals_nccl_form": bool(torch.equal(y_fused, y_nccl)),
                                   "wait_status": int(fmlp.buffers.status.item()),
-                                  "launches_per_call": 4,
-                                  "what": "GEMM epilogues store into every rank's gathered buffer "
-                                          "through peer pointers; arrival waits in the consumer / a one-thread kernel; no NCCL"}
+                                  "launches_per_call": 4 if rows <= 256 else 8,
+                                  "what": ("GEMM epilogues store into every rank's gathered buffer "
+                                           "through peer pointers; arrival waits in the consumer / a "
+                                           "one-thread kernel; no NCCL") if rows <= 256 else
+                                          ("h exchanged as e4m3 codes: shard scales as 4-byte words, "
+                                           "their maximum, an elementwise cast-and-store kernel into "
+                                           "every rank's buffer; y from the down GEMM's epilogue; peer "
+                                           "pointers, arrival counters, bounded waits; no NCCL")}
                 del gf
                 fmlp.close()
                 del fmlp
@@ -454,6 +460,9 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         del g1
         entry["single_gpu_ms_per_call"] = ms1 / steps
         entry["speedup_vs_single_gpu"] = ms1 / ms
+        # prefill sizes: the sharded result equals the unsharded one bit for bit (same codes, same
+        # scale, and the prefill GEMM sums K in one order whatever rows of the weight it is given)
+        entry["equals_single_gpu"] = bool(torch.equal(y_nccl, Q.mlp_forward(x, wg, wu, wd)))
         if "fused" in entry and "ms_per_call" in entry["fused"]:
             entry["fused"]["speedup_vs_single_gpu"] = (ms1 / steps) / entry["fused"]["ms_per_call"]
             entry["fused"]["speedup_vs_nccl_form"] = (ms / steps) / entry["fused"]["ms_per_call"]

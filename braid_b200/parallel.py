@@ -10,7 +10,13 @@ the benchmark configuration defines:
     (max is exact).  Rank r computes its slice of SiLU(gate)*up, the bf16 slices are all-gathered
     (NCCL over NVLink) into the full `[M, I]` intermediate, every rank quantizes that (identical
     scale on all ranks and identical to the single-GPU value), computes its slice of the down
-    projection, and the bf16 output slices are all-gathered into `[M, H]`.
+    projection, and the bf16 output slices are all-gathered into `[M, H]`.  Two forms:
+    `ColumnParallelMLP` exchanges through NCCL (bf16 at decode sizes; from 257 rows on e4m3
+    codes under the MAX-reduced scale, half the bytes); `FusedColumnParallelMLP` uses no
+    collective at all -- every rank's buffers are mapped into every other rank's process and
+    the kernels store into them directly (GEMM epilogues at decode sizes; at prefill sizes the
+    shard scales travel as 4-byte words and an elementwise kernel stores the codes of the local
+    shard into every rank's buffer), with per-rank arrival counters and bounded waits.
 
 Weight shards keep the per-tensor scale of the WHOLE weight, so scales and FP8 codes equal the
 single-GPU ones; a GEMM output can differ from the single-GPU one in its last bit because the K
