@@ -43,6 +43,8 @@ SIGNATURES = {
     "bq_sigmoid_mul": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "bq_rmsnorm_quant": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp,
                                 _vp, _sz, _vp]),
+    "bq_rmsnorm_scale": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp,
+                                _vp, _sz, _vp]),
     "bq_gated_rmsnorm_quant": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,
                                       _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),

@@ -177,6 +177,100 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_quant_kernel(const NormP
 }
 
 // ---------------------------------------------------------------------------------------------
+// plain RMSNorm at prefill sizes: more rows than one co-resident grid has CTAs.  Every CTA loops
+// over rows (row arithmetic exactly as above), writes the normalised activation h, and keeps the
+// running max |h|; nobody waits for anybody: each CTA folds its max into one word with an
+// atomicMax and counts itself, and the CTA that counts last turns the word into the scale and
+// returns the scratch to zero.  The codes are then one cast pass over h under that scale
+// (bq_cast_act), in stream order.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_scale_kernel(const NormParams p) {
+  bq::pdl_launch_dependents();
+  __shared__ float s_red[4];
+  __shared__ float s_max[4];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int n_vec = p.cols / kVec;
+  float g[VPT][kVec];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = t + i * kNormThreads;
+    if (v < n_vec) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(p.gamma) + v);
+      g[i][0] = f.x; g[i][1] = f.y; g[i][2] = f.z; g[i][3] = f.w;
+    }
+  }
+  bq::pdl_wait_prior_grids();
+  float m = 0.0f;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* xr = reinterpret_cast<const T*>(p.x) + static_cast<long long>(row) * p.ld_x;
+    Vec4<T> x[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = t + i * kNormThreads;
+      if (v < n_vec) x[i] = load4(xr + v * kVec);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = t + i * kNormThreads;
+      if (v < n_vec) {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          const float f = widen(x[i].v[j]);
+          s = __fmaf_rn(f, f, s);
+        }
+      }
+    }
+    s = warp_tree_sum(s);
+    if (lane == 0 && warp >= 2) s_red[warp - 2] = s;
+    __syncthreads();
+    if (lane == 0 && warp < 2) s = __fadd_rn(s, s_red[warp]);
+    __syncthreads();
+    if (lane == 0 && warp == 1) s_red[0] = s;
+    __syncthreads();
+    if (t == 0) s_red[1] = __fdiv_rn(__fadd_rn(s, s_red[0]), static_cast<float>(p.cols));
+    __syncthreads();
+    const float rstd = rsqrtf(__fadd_rn(s_red[1], p.eps));
+    T* hr = reinterpret_cast<T*>(p.h_out) + static_cast<long long>(row) * p.ld_h;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = t + i * kNormThreads;
+      if (v < n_vec) {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          const float y = __fmul_rn(g[i][j], __fmul_rn(rstd, widen(x[i].v[j])));
+          x[i].v[j] = narrow<T>(y);
+          m = nan_max(m, fabsf(widen(x[i].v[j])));
+        }
+        store4(hr + v * kVec, x[i]);
+      }
+    }
+    __syncthreads();   // s_red is written again by the next row
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if (lane == 0) s_max[warp] = m;
+  __syncthreads();
+  if (t == 0) {
+    float w = s_max[0];
+    for (int i = 1; i < kNormThreads / 32; ++i) w = nan_max(w, s_max[i]);
+    QuantWs* ws = static_cast<QuantWs*>(p.ws);
+    // |h| >= 0 or NaN with the sign cleared: bit patterns order like the values, NaN on top
+    atomicMax(&ws->amax_bits, __float_as_uint(w));
+    __threadfence();
+    const unsigned int old = atomicAdd(&ws->arrive, 1u);
+    if (old == gridDim.x - 1) {
+      __threadfence();
+      const unsigned int bits = atomicExch(&ws->amax_bits, 0u);
+      p.scale[0] = scale_from_amax(__uint_as_float(bits));
+      ws->arrive = 0u;
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // gated RMSNorm (per 128-wide head) -> quantize.  One CTA per token row, one warp per head
 // (warps loop when there are more heads than warps); a lane owns one 4-element vector of a head.
 // ---------------------------------------------------------------------------------------------
@@ -315,6 +409,62 @@ inline size_t elem_size(int dtype) { return dtype == BQ_DTYPE_F32 ? 4 : 2; }
 inline bool known_dtype(int d) { return d == BQ_DTYPE_F32 || d == BQ_DTYPE_BF16 || d == BQ_DTYPE_F16; }
 
 }  // namespace
+
+namespace {
+template <typename T>
+int launch_rmsnorm_scale(const NormParams& p, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return bq::kErrLaunch;
+  }
+  const int per_thread = (p.cols / kVec + kNormThreads - 1) / kNormThreads;
+  const int grid = p.rows < 8 * sms ? p.rows : 8 * sms;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kNormThreads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (per_thread <= 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 2>, p);
+  else if (per_thread <= 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 4>, p);
+  else if (per_thread <= 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 8>, p);
+  else if (per_thread <= 16) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 16>, p);
+  else return bq::kErrUnsupported;
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
+  return bq::kOk;
+}
+}  // namespace
+
+extern "C" int bq_rmsnorm_scale(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                                const float* gamma, float eps, void* h_out, int64_t ld_h,
+                                float* scale_out, void* ws, size_t ws_bytes, void* stream) {
+  if (!x || !gamma || !h_out || !scale_out || rows <= 0 || cols <= 0) return bq::kErrBadArg;
+  if (!known_dtype(dtype)) return bq::kErrBadArg;
+  if (ws == nullptr || ws_bytes < sizeof(QuantWs) || !aligned_to(ws, 16)) return bq::kErrWorkspace;
+  const size_t es = elem_size(dtype);
+  const size_t vec_bytes = kVec * es;
+  if (cols % kVec || ld_x < cols || (ld_x * es) % vec_bytes || !aligned_to(x, vec_bytes) ||
+      !aligned_to(gamma, 16) || ld_h < cols || (ld_h * es) % vec_bytes || !aligned_to(h_out, vec_bytes))
+    return bq::kErrUnsupported;
+  if (rows > 0x7fffffffLL || cols > 0x7fffffffLL) return bq::kErrTooLarge;
+  NormParams p{};
+  p.x = x; p.gamma = gamma; p.h_out = h_out;
+  p.scale = scale_out; p.ws = ws;
+  p.rows = static_cast<int>(rows); p.cols = static_cast<int>(cols);
+  p.ld_x = ld_x; p.ld_h = ld_h; p.eps = eps;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case BQ_DTYPE_F32: return launch_rmsnorm_scale<float>(p, s);
+    case BQ_DTYPE_BF16: return launch_rmsnorm_scale<__nv_bfloat16>(p, s);
+    default: return launch_rmsnorm_scale<__half>(p, s);
+  }
+}
 
 extern "C" int bq_rmsnorm_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
                                 const float* gamma, float eps, void* h_out, int64_t ld_h, void* q_out,

@@ -541,8 +541,9 @@ def torch_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, gamma: torch.Tenso
 def rms_norm_quant(x: torch.Tensor, gamma: torch.Tensor, eps: float,
                    keep_dense: bool = False) -> QuantizedActivation:
     """`quantize_act(rms_norm(x, gamma, eps))` in one launch (braid/model/layer.py:49,59 feeding
-    `project` / the MLP).  Bit-identical to the two steps; inputs the kernel does not take (more
-    rows than fit on the device at once, odd strides) run the two steps."""
+    `project` / the MLP).  Bit-identical to the two steps.  More rows than fit on the device at
+    once (prefill) take two launches: the norm with rows looped per CTA, which also leaves the
+    scale, and the cast pass; inputs with odd strides run the two torch-spelled steps."""
     _check_cuda(x, "rms_norm_quant")
     K = x.shape[-1]
     code = _DTYPE_CODE.get(x.dtype)
@@ -564,6 +565,21 @@ def rms_norm_quant(x: torch.Tensor, gamma: torch.Tensor, eps: float,
             _lib.check(rc, "rms_norm_quant")
             return QuantizedActivation(q, scale, x.shape, x.dtype,
                                        h.reshape(x.shape) if keep_dense else None)
+        if rc == _lib.BQ_ERR_TOO_LARGE:
+            global _launches
+            _launches -= 1            # the refused call launched nothing
+            # prefill: more rows than CTAs can wait for one another -- rows looped per CTA, h and
+            # its scale from one launch with no grid-wide wait, then the cast pass
+            if h is None:
+                h = torch.empty((rows, K), dtype=x.dtype, device=x.device)
+            rc = lib.bq_rmsnorm_scale(x2.data_ptr(), code, rows, K, x2.stride(0), gamma.data_ptr(),
+                                      float(eps), h.data_ptr(), K, scale.data_ptr(),
+                                      _take_slot(x.device), 16, _stream_ptr(x.device))
+            if rc != _lib.BQ_ERR_UNSUPPORTED:
+                _lib.check(rc, "rms_norm_scale")
+                q = cast_act(h, scale)
+                return QuantizedActivation(q, scale, x.shape, x.dtype,
+                                           h.reshape(x.shape) if keep_dense else None)
     h = torch_rms_norm(x, gamma, eps)
     q, scale = quantize_act(h.reshape(-1, K))
     return QuantizedActivation(q, scale, x.shape, x.dtype, h if keep_dense else None)

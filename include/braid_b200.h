@@ -200,6 +200,17 @@ int bq_rmsnorm_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
                      float* scale_out, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * The same norm for more rows than one co-resident grid has CTAs (prefill): every CTA loops
+ * over rows, writes the normalised activation h_out (required here) and the grid leaves the
+ * quantization scale of h in *scale_out without anybody waiting for anybody (one atomicMax and
+ * one count per CTA; the CTA that counts last publishes).  bq_cast_act(h_out, scale_out) in
+ * stream order then gives the codes: the two calls equal bq_rmsnorm_quant bit for bit.
+ */
+int bq_rmsnorm_scale(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                     const float* gamma, float eps, void* h_out, int64_t ld_h, float* scale_out,
+                     void* ws, size_t ws_bytes, void* stream);
+
+/*
  * Gated RMSNorm of the GDN readout fused into the quantizer of out_proj's input:
  *   core = T(y);  xn = T(rstd * core) per 128-wide head;  h = T((gamma * xn) * silu(float(z)))
  * with the fp32 arithmetic and the three roundings of the reference's spelling, then amax /

@@ -80,6 +80,31 @@ def test_rms_norm_quant_strided_rows_leading_dims_and_fallback(Q):
     _same(qa, ref, "4096 rows")
 
 
+@pytest.mark.parametrize("dt,shape", [(torch.bfloat16, (8192, 4096)), (torch.bfloat16, (2500, 2560)),
+                                      (torch.float32, (3000, 4096)), (torch.float16, (4100, 512))],
+                         ids=["bf16-8192x4096", "bf16-2500x2560", "fp32-3000x4096", "fp16-4100x512"])
+def test_rms_norm_quant_at_prefill_sizes(Q, dt, shape):
+    """More rows than one co-resident grid has CTAs: the norm loops rows per CTA and leaves h and
+    its scale without a grid-wide wait (`bq_rmsnorm_scale`), the cast pass writes the codes;
+    bit-identical to the torch spelling, with and without the dense output, NaN included."""
+    x = randn_cpu(shape, seed=shape[0], dtype=dt, scale=3.0).cuda()
+    x[::5] *= 9.0
+    gamma = _gamma(shape[1], 2, spread=0.3)
+    ref = TS.rms_norm(x, gamma, EPS)
+    calls = Q.launch_count()
+    qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
+    assert Q.launch_count() - calls == 2        # the norm (which also leaves the scale), the cast
+    assert torch.equal(qa.dense, ref)
+    _same(qa, ref, f"{dt} {shape}")
+    qb = Q.rms_norm_quant(x, gamma, EPS)
+    assert qb.dense is None and torch.equal(u8(qb.q), u8(qa.q)) and torch.equal(qb.scale, qa.scale)
+    x[shape[0] // 2, 7] = float("nan")
+    qa = Q.rms_norm_quant(x, gamma, EPS, keep_dense=True)
+    ref = TS.rms_norm(x, gamma, EPS)
+    assert torch.isnan(qa.scale).all() and torch.equal(torch.isnan(qa.dense), torch.isnan(ref))
+    assert Q.device_status() == 0
+
+
 def test_rms_norm_quant_degenerate_values(Q):
     gamma = _gamma(4096, 5)
     zeros = torch.zeros(4, 4096, dtype=torch.bfloat16, device="cuda")
