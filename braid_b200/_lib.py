@@ -47,6 +47,8 @@ SIGNATURES = {
                                 _vp, _sz, _vp]),
     "bq_gated_rmsnorm_quant": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,
                                       _i64, _vp, _vp, _vp, _sz, _vp]),
+    "bq_gated_rmsnorm_scale": (_int, [_vp, _int, _i64, _vp, _int, _i64, _vp, ctypes.c_float, _i64, _i64,
+                                      _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
     "bq_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "bq_gemm_w8a8": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "bq_gemm_w8a8_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _int, _i64, _i64, _i64, _i64,

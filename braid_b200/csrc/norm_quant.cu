@@ -278,6 +278,8 @@ struct GatedParams {
   const void* y;       // scan output, fp32 or the activation type
   const void* z;       // gate, the activation type
   const float* gamma;  // [128]
+  void* h_out;         // looped form: the gated, normalised activation [rows, heads * 128]
+  long long ld_h;
   uint8_t* q;
   float* scale;
   void* ws;
@@ -410,6 +412,77 @@ inline bool known_dtype(int d) { return d == BQ_DTYPE_F32 || d == BQ_DTYPE_BF16 
 
 }  // namespace
 
+// The gated norm for more rows than one co-resident grid has CTAs (prefill): a warp owns one
+// head of one row at a time (head arithmetic exactly as above; no CTA-wide step in it), the
+// warps of the grid stride over all (row, head) pairs, write the gated activation and fold
+// max |h| into one word as rmsnorm_scale_kernel does; the cast pass follows in stream order.
+template <typename T, bool Y_F32>
+__global__ void __launch_bounds__(kGatedWarps * 32) gated_rmsnorm_scale_kernel(const GatedParams p) {
+  bq::pdl_launch_dependents();
+  __shared__ float s_max[kGatedWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float4 gm = __ldg(reinterpret_cast<const float4*>(p.gamma) + lane);
+  const float gmv[kVec] = {gm.x, gm.y, gm.z, gm.w};
+  bq::pdl_wait_prior_grids();
+  const long long units = static_cast<long long>(p.rows) * p.heads;
+  const long long stride = static_cast<long long>(gridDim.x) * kGatedWarps;
+  float m = 0.0f;
+  for (long long u = static_cast<long long>(blockIdx.x) * kGatedWarps + warp; u < units; u += stride) {
+    const long long row = u / p.heads;
+    const int head = static_cast<int>(u - row * p.heads);
+    const long long off = static_cast<long long>(head) * kHeadDim + lane * kVec;
+    Vec4<T> core;
+    if constexpr (Y_F32) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(
+          reinterpret_cast<const float*>(p.y) + row * p.ld_y + off));
+      core.v[0] = narrow<T>(f.x); core.v[1] = narrow<T>(f.y);
+      core.v[2] = narrow<T>(f.z); core.v[3] = narrow<T>(f.w);
+    } else {
+      core = load4(reinterpret_cast<const T*>(p.y) + row * p.ld_y + off);
+    }
+    const Vec4<T> gate = load4(reinterpret_cast<const T*>(p.z) + row * p.ld_z + off);
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      const float f = widen(core.v[j]);
+      s = __fmaf_rn(f, f, s);
+    }
+    s = warp_tree_sum(s);
+    s = __shfl_sync(0xffffffffu, s, 0);
+    const float sigma2 = __fdiv_rn(s, static_cast<float>(kHeadDim));
+    const float rstd = rsqrtf(__fadd_rn(sigma2, p.eps));
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      const T xn = narrow<T>(__fmul_rn(rstd, widen(core.v[j])));
+      const float zf = widen(gate.v[j]);
+      const float silu = __fdiv_rn(zf, 1.0f + expf(-zf));
+      const float h = __fmul_rn(__fmul_rn(gmv[j], widen(xn)), silu);
+      core.v[j] = narrow<T>(h);
+      m = nan_max(m, fabsf(widen(core.v[j])));
+    }
+    store4(reinterpret_cast<T*>(p.h_out) + row * p.ld_h + off, core);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if (lane == 0) s_max[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float w = s_max[0];
+    for (int i = 1; i < kGatedWarps; ++i) w = nan_max(w, s_max[i]);
+    QuantWs* ws = static_cast<QuantWs*>(p.ws);
+    atomicMax(&ws->amax_bits, __float_as_uint(w));
+    __threadfence();
+    const unsigned int old = atomicAdd(&ws->arrive, 1u);
+    if (old == gridDim.x - 1) {
+      __threadfence();
+      const unsigned int bits = atomicExch(&ws->amax_bits, 0u);
+      p.scale[0] = scale_from_amax(__uint_as_float(bits));
+      ws->arrive = 0u;
+      __threadfence();
+    }
+  }
+}
+
 namespace {
 template <typename T>
 int launch_rmsnorm_scale(const NormParams& p, cudaStream_t stream) {
@@ -522,4 +595,57 @@ extern "C" int bq_gated_rmsnorm_quant(const void* y, int y_dtype, int64_t ld_y, 
     default:
       return yf32 ? launch_gated<__half, true>(p, s) : launch_gated<__half, false>(p, s);
   }
+}
+
+extern "C" int bq_gated_rmsnorm_scale(const void* y, int y_dtype, int64_t ld_y, const void* z, int dtype,
+                                      int64_t ld_z, const float* gamma, float eps, int64_t rows,
+                                      int64_t heads, int64_t head_dim, void* h_out, int64_t ld_h,
+                                      float* scale_out, void* ws, size_t ws_bytes, void* stream) {
+  if (!y || !z || !gamma || !h_out || !scale_out || rows <= 0 || heads <= 0) return bq::kErrBadArg;
+  if (!known_dtype(dtype) || (y_dtype != dtype && y_dtype != BQ_DTYPE_F32)) return bq::kErrBadArg;
+  if (ws == nullptr || ws_bytes < sizeof(QuantWs) || !aligned_to(ws, 16)) return bq::kErrWorkspace;
+  if (head_dim != kHeadDim) return bq::kErrUnsupported;
+  const size_t es = elem_size(dtype), ys = elem_size(y_dtype);
+  const int64_t width = heads * head_dim;
+  if (ld_y < width || ld_z < width || ld_h < width || (ld_y * ys) % (kVec * ys) ||
+      (ld_z * es) % (kVec * es) || (ld_h * es) % (kVec * es) || !aligned_to(y, kVec * ys) ||
+      !aligned_to(z, kVec * es) || !aligned_to(h_out, kVec * es) || !aligned_to(gamma, 16))
+    return bq::kErrUnsupported;
+  if (rows > 0x7fffffffLL || heads > 0x7fffLL) return bq::kErrTooLarge;
+  GatedParams p{};
+  p.y = y; p.z = z; p.gamma = gamma; p.h_out = h_out; p.ld_h = ld_h;
+  p.scale = scale_out; p.ws = ws;
+  p.rows = static_cast<int>(rows); p.heads = static_cast<int>(heads);
+  p.ld_y = ld_y; p.ld_z = ld_z; p.eps = eps;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return bq::kErrLaunch;
+  }
+  const long long want = (rows * heads + kGatedWarps - 1) / kGatedWarps;
+  const int grid = static_cast<int>(want < 8LL * sms ? want : 8LL * sms);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kGatedWarps * 32, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const bool yf32 = (y_dtype == BQ_DTYPE_F32) && (dtype != BQ_DTYPE_F32);
+  cudaError_t e;
+  switch (dtype) {
+    case BQ_DTYPE_F32: e = cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<float, false>, p); break;
+    case BQ_DTYPE_BF16:
+      e = yf32 ? cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__nv_bfloat16, true>, p)
+               : cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__nv_bfloat16, false>, p);
+      break;
+    default:
+      e = yf32 ? cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__half, true>, p)
+               : cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__half, false>, p);
+  }
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
+  return bq::kOk;
 }

@@ -615,6 +615,19 @@ def gated_rms_norm_quant(y: torch.Tensor, z: torch.Tensor, gamma: torch.Tensor, 
         if rc not in (_lib.BQ_ERR_TOO_LARGE, _lib.BQ_ERR_UNSUPPORTED):
             _lib.check(rc, "gated_rms_norm_quant")
             return QuantizedActivation(q, scale, (*lead, width), z.dtype)
+        if rc == _lib.BQ_ERR_TOO_LARGE:
+            global _launches
+            _launches -= 1            # the refused call launched nothing
+            # prefill: warps stride over all (row, head) pairs, the gated activation and its
+            # scale from one launch with no grid-wide wait, then the cast pass
+            core = torch.empty((rows, width), dtype=z.dtype, device=z.device)
+            rc = lib.bq_gated_rmsnorm_scale(y2.data_ptr(), ycode, y2.stride(0), z2.data_ptr(), code,
+                                            z2.stride(0), gamma.data_ptr(), float(eps), rows, heads,
+                                            head_dim, core.data_ptr(), width, scale.data_ptr(),
+                                            _take_slot(z.device), 16, _stream_ptr(z.device))
+            if rc != _lib.BQ_ERR_UNSUPPORTED:
+                _lib.check(rc, "gated_rms_norm_scale")
+                return QuantizedActivation(cast_act(core, scale), scale, (*lead, width), z.dtype)
     core = torch_rms_norm_gated(y2.to(z.dtype).reshape(-1, head_dim), z2.reshape(-1, head_dim),
                                 gamma, eps).reshape(rows, width)
     q, scale = quantize_act(core)

@@ -232,6 +232,17 @@ int bq_gated_rmsnorm_quant(const void* y, int y_dtype, int64_t ld_y, const void*
                            size_t ws_bytes, void* stream);
 
 /*
+ * The gated norm for more rows than one co-resident grid has CTAs (prefill): writes the gated,
+ * normalised activation h_out [rows, heads*head_dim] and leaves its quantization scale in
+ * *scale_out with no grid-wide wait; bq_cast_act(h_out, scale_out) then gives the codes.  The
+ * two calls equal bq_gated_rmsnorm_quant bit for bit.  Any number of heads.
+ */
+int bq_gated_rmsnorm_scale(const void* y, int y_dtype, int64_t ld_y, const void* z, int dtype,
+                           int64_t ld_z, const float* gamma, float eps, int64_t rows, int64_t heads,
+                           int64_t head_dim, void* h_out, int64_t ld_h, float* scale_out, void* ws,
+                           size_t ws_bytes, void* stream);
+
+/*
  * Bytes of scratch the GEMM entry points need: 16 (the sticky status word and
  * the counters of the paired / push epilogues).  Split-K partial sums travel
  * through distributed shared memory and never reach global memory.  Zero the

@@ -159,6 +159,24 @@ def test_gated_rms_norm_quant_many_rows_and_nan(Q):
     assert int((u8(qa.q) != u8(qr)).sum()) == 0
 
 
+@pytest.mark.parametrize("ydt,rows,heads", [(torch.float32, 8192, 32), (torch.bfloat16, 3000, 32),
+                                            (torch.float32, 2500, 16)],
+                         ids=["f32-scan-8192x32", "bf16-3000x32", "f32-scan-2500x16"])
+def test_gated_rms_norm_quant_at_prefill_sizes(Q, ydt, rows, heads):
+    """More rows than one co-resident grid has CTAs: warps stride over all (row, head) pairs
+    (`bq_gated_rmsnorm_scale`), then the cast pass; bit-identical to the torch spelling."""
+    width = heads * 128
+    y = randn_cpu((rows, heads, 128), seed=rows, dtype=ydt, scale=2.0).cuda()
+    z = randn_cpu((rows, width), seed=rows + 1, scale=1.5).cuda()
+    gamma = _gamma(128, 3, spread=0.3)
+    ref = TS.rms_norm_gated(y.to(z.dtype).reshape(-1, 128), z.reshape(-1, 128), gamma, EPS).reshape(rows, width)
+    calls = Q.launch_count()
+    qa = Q.gated_rms_norm_quant(y, z, gamma, EPS, 128)
+    assert Q.launch_count() - calls == 2
+    _same(qa, ref, f"{ydt} {rows}x{heads}")
+    assert Q.device_status() == 0
+
+
 def test_consumers_take_the_quantized_activation(Q):
     """`project`, `linear` and the MLP on a pre-quantized activation equal the reference order of
     operations (norm, then the consumer quantizes) bit for bit, bf16 weights in the mix included."""
