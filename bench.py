@@ -462,7 +462,8 @@ def column_parallel_block(dist, rows_list, steps, warmup):
         entry["speedup_vs_single_gpu"] = ms1 / ms
         # prefill sizes: the sharded result equals the unsharded one bit for bit (same codes, same
         # scale, and the prefill GEMM sums K in one order whatever rows of the weight it is given)
-        entry["equals_single_gpu"] = bool(torch.equal(y_nccl, Q.mlp_forward(x, wg, wu, wd)))
+        if rows > 256:
+            entry["equals_single_gpu"] = bool(torch.equal(y_nccl, Q.mlp_forward(x, wg, wu, wd)))
         entry["best"] = {"form": "nccl", "ms_per_call": ms / steps, "speedup_vs_single_gpu": ms1 / ms}
         if "fused" in entry and "ms_per_call" in entry["fused"]:
             entry["fused"]["speedup_vs_single_gpu"] = (ms1 / steps) / entry["fused"]["ms_per_call"]

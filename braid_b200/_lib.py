@@ -41,6 +41,9 @@ SIGNATURES = {
                                      _vp, _vp, _vp, _sz, _vp]),
     "bq_silu_mul": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp]),
     "bq_sigmoid_mul": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "bq_silu_mul_dense_scale": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "bq_sigmoid_mul_dense_scale": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
+                                          _vp, _sz, _vp]),
     "bq_rmsnorm_quant": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp,
                                 _vp, _sz, _vp]),
     "bq_rmsnorm_scale": (_int, [_vp, _int, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp,

@@ -426,17 +426,42 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256) prologue_dense_kernel(const QParams p, T* __restrict__ out) {
   bq::pdl_launch_dependents();
   bq::pdl_wait_prior_grids();
+  __shared__ float s_max[8];
   const unsigned int nthreads = gridDim.x * blockDim.x;
+  float m = 0.0f;
   for (unsigned long long g = blockIdx.x * blockDim.x + threadIdx.x; g < p.n_groups; g += nthreads) {
     Pack8<T> a, b;
     load_raw<T, MODE, false>(p, (unsigned int)g, a, b);
     apply_prologue<T, MODE>(a, b);
+    m = absmax8(a, m);
     if constexpr (sizeof(T) == 4) {
       float4* dst = reinterpret_cast<float4*>(out + g * kGroup);
       dst[0] = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
       dst[1] = make_float4(a.v[4], a.v[5], a.v[6], a.v[7]);
     } else {
       *reinterpret_cast<uint4*>(out + g * kGroup) = *reinterpret_cast<const uint4*>(&a);
+    }
+  }
+  // with a scale asked for: every CTA folds its max into one word and counts itself, the CTA
+  // that counts last publishes the scale and returns the scratch to zero; nobody waits
+  if (p.scale == nullptr) return;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float w = s_max[0];
+    for (unsigned int i = 1; i < blockDim.x / 32; ++i) w = nan_max(w, s_max[i]);
+    QuantWs* ws = static_cast<QuantWs*>(p.ws);
+    atomicMax(&ws->amax_bits, __float_as_uint(w));
+    __threadfence();
+    const unsigned int old = atomicAdd(&ws->arrive, 1u);
+    if (old == gridDim.x - 1) {
+      __threadfence();
+      const unsigned int bits = atomicExch(&ws->amax_bits, 0u);
+      p.scale[0] = scale_from_amax(__uint_as_float(bits));
+      ws->arrive = 0u;
+      __threadfence();
     }
   }
 }
@@ -876,9 +901,46 @@ extern "C" int bq_silu_mul(const void* gate, const void* up, int dtype, int64_t 
   return launch_dense<kSiluMul>(dtype, p, h_out, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bq_silu_mul_dense_scale(const void* gate, const void* up, int dtype, int64_t rows,
+                                       int64_t cols, int64_t ld_gate, int64_t ld_up, void* h_out,
+                                       float* scale_out, void* ws, size_t ws_bytes, void* stream) {
+  if (!h_out || !scale_out) return bq::kErrBadArg;
+  if (!aligned_to(h_out, 16)) return bq::kErrUnsupported;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  QParams p{};
+  if (int rc = fill_silu_mul(&p, gate, up, dtype, rows, cols, ld_gate, ld_up)) return rc;
+  p.scale = scale_out;
+  p.ws = ws;
+  return launch_dense<kSiluMul>(dtype, p, h_out, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+int sigmoid_mul_common(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                       int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride, void* out,
+                       float* scale_out, void* ws, void* stream);
+}
+
+extern "C" int bq_sigmoid_mul_dense_scale(const void* o, const void* gate, int dtype, int64_t rows,
+                                          int64_t cols, int64_t ld_o, int64_t ld_gate, int64_t chunk,
+                                          int64_t chunk_stride, void* out, float* scale_out, void* ws,
+                                          size_t ws_bytes, void* stream) {
+  if (!scale_out) return bq::kErrBadArg;
+  if (int rc = check_ws(ws, ws_bytes)) return rc;
+  return sigmoid_mul_common(o, gate, dtype, rows, cols, ld_o, ld_gate, chunk, chunk_stride, out,
+                            scale_out, ws, stream);
+}
+
 extern "C" int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
                               int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride,
                               void* out, void* stream) {
+  return sigmoid_mul_common(o, gate, dtype, rows, cols, ld_o, ld_gate, chunk, chunk_stride, out,
+                            nullptr, nullptr, stream);
+}
+
+namespace {
+int sigmoid_mul_common(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                       int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride, void* out,
+                       float* scale_out, void* ws, void* stream) {
   if (!o || !gate || !out || rows <= 0 || cols <= 0 || chunk <= 0) return bq::kErrBadArg;
   if (dtype != BQ_DTYPE_F32 && dtype != BQ_DTYPE_BF16 && dtype != BQ_DTYPE_F16) return bq::kErrBadArg;
   const size_t es = elem_size(dtype);
@@ -896,8 +958,11 @@ extern "C" int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_
   p.ld_b = ld_gate;
   p.chunk = static_cast<unsigned int>(chunk);
   p.chunk_stride = chunk_stride;
+  p.scale = scale_out;
+  p.ws = ws;
   return launch_dense<kSigmoidGate>(dtype, p, out, static_cast<cudaStream_t>(stream));
 }
+}  // namespace
 
 namespace {
 template <bool CAST>

@@ -130,6 +130,9 @@ _LOCK = threading.Lock()
 # take slots round-robin so that launches in flight on different streams do not
 # share barrier words.
 _SLOTS = 256
+# From this many elements on (beyond what the one-launch prologue quantizers hold in registers)
+# the SiLU*mul and sigmoid-gate quantizers run as two launches: product + scale, then the cast.
+_TWO_LAUNCH_FROM = 1 << 22
 _SLOT_BYTES = 64
 _scratch: dict[int, torch.Tensor] = {}
 _next_slot: dict[int, int] = {}
@@ -345,8 +348,17 @@ def silu_mul_quant(gate: torch.Tensor, up: torch.Tensor) -> tuple[torch.Tensor, 
     cols = gate.shape[-1]
     g2, u2 = _as_rows(gate, cols), _as_rows(up, cols)
     rows = g2.shape[0]
-    q = torch.empty((rows, cols), dtype=FP8, device=gate.device)
     scale = torch.empty((1, 1), dtype=torch.float32, device=gate.device)
+    if rows * cols >= _TWO_LAUNCH_FROM:
+        # prefill sizes: the product and its scale in one launch (no grid-wide wait), then the
+        # cast pass -- the one-launch form would evaluate silu twice over its two passes
+        h = torch.empty((rows, cols), dtype=gate.dtype, device=gate.device)
+        rc = lib.bq_silu_mul_dense_scale(g2.data_ptr(), u2.data_ptr(), code, rows, cols, g2.stride(0),
+                                         u2.stride(0), h.data_ptr(), scale.data_ptr(),
+                                         _take_slot(gate.device), 16, _stream_ptr(gate.device))
+        _lib.check(rc, "silu_mul_dense_scale")
+        return cast_act(h, scale).reshape(*gate.shape[:-1], cols), scale
+    q = torch.empty((rows, cols), dtype=FP8, device=gate.device)
     rc = lib.bq_silu_mul_quant(g2.data_ptr(), u2.data_ptr(), code, rows, cols,
                                g2.stride(0), u2.stride(0), q.data_ptr(), scale.data_ptr(),
                                _take_slot(gate.device), 16, _stream_ptr(gate.device))
@@ -437,8 +449,17 @@ def sigmoid_gate_quant(o: torch.Tensor, gate: torch.Tensor,
         g2 = _as_rows(gate, cols)
         ld_gate, chunk, chunk_stride, gptr = g2.stride(0), cols, 0, g2.data_ptr()
         keep = g2
-    q = torch.empty((rows, cols), dtype=FP8, device=o.device)
     scale = torch.empty((1, 1), dtype=torch.float32, device=o.device)
+    if rows * cols >= _TWO_LAUNCH_FROM:
+        # prefill sizes: product and scale in one launch, then the cast pass (see silu_mul_quant)
+        h = torch.empty((rows, cols), dtype=o.dtype, device=o.device)
+        rc = lib.bq_sigmoid_mul_dense_scale(o2.data_ptr(), gptr, code, rows, cols, o2.stride(0), ld_gate,
+                                            chunk, chunk_stride, h.data_ptr(), scale.data_ptr(),
+                                            _take_slot(o.device), 16, _stream_ptr(o.device))
+        del keep
+        _lib.check(rc, "sigmoid_mul_dense_scale")
+        return cast_act(h, scale).reshape(*o.shape[:-1], cols), scale
+    q = torch.empty((rows, cols), dtype=FP8, device=o.device)
     rc = lib.bq_sigmoid_gate_quant(o2.data_ptr(), gptr, code, rows, cols, o2.stride(0), ld_gate,
                                    chunk, chunk_stride, q.data_ptr(), scale.data_ptr(),
                                    _take_slot(o.device), 16, _stream_ptr(o.device))

@@ -177,6 +177,20 @@ int bq_sigmoid_mul(const void* o, const void* gate, int dtype, int64_t rows, int
                    void* stream);
 
 /*
+ * The same two products together with the quantization scale of the result (one atomicMax and
+ * one count per CTA on `ws`, 16 bytes as for bq_quantize_act; the CTA that counts last writes
+ * *scale_out; no grid-wide wait): the first of two launches that replace bq_silu_mul_quant /
+ * bq_sigmoid_gate_quant at prefill sizes, where their two passes would evaluate the prologue
+ * twice -- bq_cast_act(out, scale_out) is the second.  Same bits as the one-launch forms.
+ */
+int bq_silu_mul_dense_scale(const void* gate, const void* up, int dtype, int64_t rows, int64_t cols,
+                            int64_t ld_gate, int64_t ld_up, void* h_out, float* scale_out, void* ws,
+                            size_t ws_bytes, void* stream);
+int bq_sigmoid_mul_dense_scale(const void* o, const void* gate, int dtype, int64_t rows, int64_t cols,
+                               int64_t ld_o, int64_t ld_gate, int64_t chunk, int64_t chunk_stride,
+                               void* out, float* scale_out, void* ws, size_t ws_bytes, void* stream);
+
+/*
  * RMSNorm fused into the quantizer: h = T(gamma * (rstd * x)), rstd = rsqrt(mean(x^2) + eps),
  * computed in fp32 from the fp32-widened input with ONE rounding to the activation type T,
  * then amax / scale / e4m3 codes of h as bq_quantize_act produces them.  The sum of squares

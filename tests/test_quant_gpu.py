@@ -334,6 +334,33 @@ def test_silu_and_sigmoid_of_every_16_bit_value(Q, dt):
                        (F.silu(gate) * up).view(torch.int16)[~torch.isnan(gate)])
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_prologue_quantizers_at_prefill_sizes_take_two_launches(Q, dt):
+    """From 2^22 elements on, SiLU*mul and the sigmoid gate run as product + scale (no grid-wide
+    wait) followed by the cast pass; same bits as the torch spelling, column blocks and the
+    per-head gate view read in place, NaN carried."""
+    M, I = 2100, 2048
+    gu = randn_cpu((M, 2 * I), seed=51, dtype=dt, scale=2.0).cuda()
+    calls = Q.launch_count()
+    q, s = Q.silu_mul_quant(gu[:, :I], gu[:, I:])
+    assert Q.launch_count() - calls == 2
+    qr, sr = TS.quantize_act(TS.silu_mul(gu[:, :I].contiguous(), gu[:, I:].contiguous()))
+    _assert_same(q, s, qr, sr, f"silu two-launch {dt}")
+    B, T, H, D = 2, 1100, 16, 128
+    qg = randn_cpu((B, T, H * 2 * D), seed=52, dtype=dt, scale=2.0).cuda()
+    o = randn_cpu((B, T, H * D), seed=53, dtype=dt).cuda()
+    _, gate_v = qg.view(B, T, H, 2 * D).chunk(2, dim=-1)
+    qr, sr = TS.quantize_act(TS.sigmoid_gate(o, gate_v.reshape(B, T, H * D)))
+    calls = Q.launch_count()
+    q2, s2 = Q.sigmoid_gate_quant(o, gate_v)
+    assert Q.launch_count() - calls == 2
+    _assert_same(q2, s2, qr, sr, f"sigmoid two-launch {dt}")
+    o[1, 7, 3] = float("nan")
+    q3, s3 = Q.sigmoid_gate_quant(o, gate_v)
+    assert torch.isnan(s3).all()
+    assert Q.device_status() == 0
+
+
 def test_dense_prologues_in_fp32_and_on_column_blocks(Q):
     x = randn_cpu((33, 2 * 512), seed=12, dtype=torch.float32, scale=3.0).cuda()
     assert torch.equal(Q.silu_mul(x[:, :512], x[:, 512:]), F.silu(x[:, :512]) * x[:, 512:])
