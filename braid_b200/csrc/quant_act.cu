@@ -479,6 +479,7 @@ struct RowPush {
   const void* src;
   long long ld_src;               // elements
   int rows, groups_per_row;       // groups of 8 columns
+  int wide;                       // CAST: destinations allow 16-byte stores of two groups
   const float* scale;             // CAST: device scalar
   int n;
   void* dst[8];
@@ -496,6 +497,19 @@ __global__ void __launch_bounds__(256) row_push_kernel(const RowPush p) {
   const ScaleDiv dv(sc);
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const T* src = reinterpret_cast<const T*>(p.src) + (long long)row * p.ld_src;
+    if (CAST && p.wide) {
+      // two groups per thread, one 16-byte store per destination: a warp writes 512 contiguous
+      // bytes of the row on every rank
+      for (int g = 2 * threadIdx.x; g < p.groups_per_row; g += 2 * blockDim.x) {
+        const Pack8<T> v0 = load8<T, false>(src + g * kGroup);
+        const Pack8<T> v1 = load8<T, false>(src + (g + 1) * kGroup);
+        const uint2 c0 = codes8<T, false>(v0, dv), c1 = codes8<T, false>(v1, dv);
+        const uint4 c = make_uint4(c0.x, c0.y, c1.x, c1.y);
+        const long long at = (long long)row * p.ld_dst + g * kGroup;
+        for (int d = 0; d < p.n; ++d) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst[d]) + at) = c;
+      }
+      continue;
+    }
     for (int g = threadIdx.x; g < p.groups_per_row; g += blockDim.x) {
       const Pack8<T> v = load8<T, false>(src + g * kGroup);
       const long long at = (long long)row * p.ld_dst + g * kGroup;
@@ -1028,6 +1042,9 @@ extern "C" int bq_cast_act_push(const void* x, int dtype, int64_t rows, int64_t 
   if (int rc = fill_row_push(&p, x, dtype, rows, cols, ld_x, n_peers, q_dst, ld_q, flags, ws, ws_bytes, 1))
     return rc;
   p.scale = scale;
+  p.wide = (cols % 16 == 0 && ld_q % 16 == 0) ? 1 : 0;
+  for (int i = 0; i < n_peers; ++i)
+    if (!aligned_to(q_dst[i], 16)) p.wide = 0;
   return launch_row_push<true>(dtype, p, static_cast<cudaStream_t>(stream));
 }
 

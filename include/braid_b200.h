@@ -552,6 +552,8 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
  * bq_set_option("stream_max_m", v)      largest M the weight-streaming kernel takes (<= 256)
  * bq_set_option("gemm_pdl" | "quant_pdl", 0/1)  programmatic dependent launch
  * bq_set_option("quant_block" | "quant_held", v) quantizer launch shape overrides
+ * bq_set_option("quant_ring", 0/1)      plain quantizer at prefill sizes through the shared-memory ring (default 1)
+ * bq_set_option("push_tma", 0/1)        prefill push epilogue by bulk tensor stores (default 1) or 16-byte plain stores
  * Returns BQ_ERR_BAD_ARG for an unknown key.
  */
 int bq_set_option(const char* key, int64_t value);
