@@ -1991,15 +1991,17 @@ extern "C" int bq_wait_flag(const void* flag, void* seen, unsigned int count, vo
   return kOk;
 }
 
-// One thread: the 4-byte word at `word` (a scale, a max) into `dst_words[i]` on every rank, then
-// one arrival on every rank's counter, the word first (system-scope release on the counters).
+// One warp, lane d for rank d: the 4-byte word at `word` (a scale, a max) into `dst_words[d]`,
+// then one arrival on that rank's counter, the word first (system-scope release on the
+// counter).  One lane per rank so that the round trips to the ranks run side by side (a single
+// thread walking four ranks took 12 us).
 __global__ void word_push_kernel(const unsigned int* word, int n, PushParams dst) {
+  const int d = threadIdx.x;
+  if (d >= n) return;
   const unsigned int v = __ldcg(word);
-  for (int d = 0; d < n; ++d)
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst.amax_dst[d]), "r"(v) : "memory");
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst.amax_dst[d]), "r"(v) : "memory");
   __threadfence_system();
-  for (int d = 0; d < n; ++d)
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(dst.flag[d]) : "memory");
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(dst.flag[d]) : "memory");
 }
 
 extern "C" int bq_word_push(const void* word, int n_peers, void* const* dst_words, void* const* flags,
@@ -2014,7 +2016,7 @@ extern "C" int bq_word_push(const void* word, int n_peers, void* const* dst_word
     pp.amax_dst[i] = static_cast<unsigned int*>(dst_words[i]);
     pp.flag[i] = static_cast<unsigned int*>(flags[i]);
   }
-  word_push_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(word),
+  word_push_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(word),
                                                                    n_peers, pp);
   if (cudaGetLastError() != cudaSuccess) return kErrLaunch;
   return kOk;

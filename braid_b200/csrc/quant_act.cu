@@ -532,14 +532,23 @@ __global__ void __launch_bounds__(256) row_push_kernel(const RowPush p) {
   }
   // every store of the launch happens before every arrival (see the GEMM push epilogue)
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned int old = atomicAdd(p.done, 1u);
-    if (old == gridDim.x - 1u) {
-      *p.done = 0u;
+  if (threadIdx.x < 32) {
+    unsigned int last = 0u;
+    if (threadIdx.x == 0) {
       __threadfence_system();
-      for (int d = 0; d < p.n; ++d)
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.flag[d]) : "memory");
+      const unsigned int old = atomicAdd(p.done, 1u);
+      if (old == gridDim.x - 1u) {
+        *p.done = 0u;
+        __threadfence_system();
+        last = 1u;
+      }
+    }
+    // lane d signals rank d: the round trips run side by side; lane 0's fences come first
+    last = __shfl_sync(0xffffffffu, last, 0);
+    __syncwarp();
+    if (last != 0u && (int)threadIdx.x < p.n) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.flag[threadIdx.x]) : "memory");
     }
   }
 }

@@ -463,8 +463,9 @@ int bq_wait_flag_scale(const void* flag, void* seen, unsigned int count, void* s
                        void* stream);
 
 /*
- * One-thread kernel: the 4-byte word at `word` into `dst_words[i]` on every rank (peer-mapped
- * pointers, this rank's own included), then one arrival on every rank's counter `flags[i]`.
+ * One-warp kernel (a lane per rank): the 4-byte word at `word` into `dst_words[i]` on every rank
+ * (peer-mapped pointers, this rank's own included), then one arrival on that rank's counter
+ * `flags[i]`.
  */
 int bq_word_push(const void* word, int n_peers, void* const* dst_words, void* const* flags,
                  void* stream);
