@@ -81,6 +81,32 @@ def test_fused_exchange_equals_the_gathered_spelling(Q, world, M, form):
         r.buffers.close()
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_block_pushes_store_the_same_rows_on_every_rank_and_signal(Q, dt):
+    """`rows_push` (block unchanged) and `cast_act_push` (its e4m3 codes) with three destinations
+    in this process: every destination gets the block at the column offset its pointer carries,
+    nothing else is touched, and every counter advances by one per launch."""
+    M, n, width = 300, 1024, 4096
+    x = randn_cpu((M, 2 * n), seed=3, dtype=dt, scale=2.0).cuda()[:, :n]      # strided rows
+    flags = torch.zeros(3, dtype=torch.int32, device="cuda")
+    dst = [torch.full((M, width), -7.0, dtype=dt, device="cuda") for _ in range(3)]
+    col, es = 512, x.element_size()
+    Q.rows_push(x, [d.data_ptr() + col * es for d in dst], width, [flags[i:i + 1].data_ptr() for i in range(3)])
+    for d in dst:
+        assert torch.equal(d[:, col:col + n], x)
+        assert bool((d[:, :col] == -7.0).all()) and bool((d[:, col + n:] == -7.0).all())
+    scale = Q.quantize_act(x.contiguous())[1]
+    want = Q.cast_act(x.contiguous(), scale).view(torch.uint8)
+    qd = [torch.full((M, width), 9, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    Q.cast_act_push(x, scale, [d.data_ptr() + col for d in qd], width,
+                    [flags[i:i + 1].data_ptr() for i in range(3)])
+    for d in qd:
+        assert torch.equal(d[:, col:col + n], want)
+        assert bool((d[:, :col] == 9).all()) and bool((d[:, col + n:] == 9).all())
+    assert flags.tolist() == [2, 2, 2]
+    assert Q.device_status() == 0
+
+
 def test_a_wait_that_nothing_satisfies_runs_out_and_reports(Q):
     """A counter no rank increments: the wait kernel gives up after its cycle limit (well under
     a second), raises the status word, and the context stays usable."""
