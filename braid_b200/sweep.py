@@ -332,8 +332,83 @@ def phase_tables(args, dev, peaks):
     return out
 
 
+def column_parallel_kernels(rows: int = 4096) -> None:
+    """The codes form of `FusedColumnParallelMLP` kernel by kernel, every kernel back to back
+    with itself on all ranks at once (max over ranks, CUDA events), and the whole forward from
+    one graph.  Run under torchrun, one process per GPU:
+        python -m torch.distributed.run --nproc-per-node N bench.py --sweep --only column_parallel --rows 4096
+    Rank 0 prints one JSON line."""
+    import torch.distributed as dist
+    from .parallel import FusedColumnParallelMLP
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    Q.warm_fused(True)
+    mlp = FusedColumnParallelMLP.random_init(4096, 12288, dev, dist.group.WORLD, seed=1, rows_max=max(256, rows))
+    mlp.connect()
+    rank, b = mlp.rank, mlp.buffers
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(rows, 4096, generator=g, device=dev).to(torch.bfloat16)
+    xq, sx = Q.quantize_act(x)
+
+    def timed(fn, n=10):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        c.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(c) * 1e3 / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    spare = [s + 32 for _, _, s in b.peers]        # counters nobody waits on
+    col, hcol = mlp.i_ranges[rank][0], mlp.h_ranges[rank][0]
+    h_local, sh = Q.gate_up_silu(xq, sx, mlp.gate, mlp.up, x.dtype)
+    hq = b.hq[:rows].view(Q.FP8)
+    Q.cast_act_push(h_local, sh, [h + col for h, _, _ in b.peers], mlp.I, spare)
+    torch.cuda.synchronize()
+    dist.barrier()
+    y_local = Q.fp8_matmul(hq, sh, mlp.down, out_dtype=x.dtype)
+    out = {"ranks": mlp.world, "rows": rows, "us": {
+        "quantize x": timed(lambda: Q.quantize_act(x)),
+        "gate/up + SiLU*mul of the shard (local)": timed(lambda: Q.gate_up_silu(xq, sx, mlp.gate, mlp.up, x.dtype)),
+        "shard scale word to every rank": timed(lambda: Q.word_push(sh, mlp._slot_ptrs(), spare)),
+        "cast of the shard (local)": timed(lambda: Q.cast_act(h_local, sh)),
+        "cast + codes to every rank": timed(lambda: Q.cast_act_push(
+            h_local, sh, [h + col for h, _, _ in b.peers], mlp.I, spare)),
+        "down shard (local)": timed(lambda: Q.fp8_matmul(hq, sh, mlp.down, out_dtype=x.dtype)),
+        "down shard, y to every rank from the epilogue": timed(lambda: Q.gemm_push(
+            hq, sh, mlp.down, mlp.dtype, [y + hcol * 2 for _, y, _ in b.peers], mlp.H, spare)),
+        "y block to every rank (separate kernel)": timed(lambda: Q.rows_push(
+            y_local, [y + hcol * 2 for _, y, _ in b.peers], mlp.H, spare)),
+    }}
+    mlp.forward(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        mlp.forward(x)
+    out["us"]["whole forward, one graph"] = timed(graph.replay, n=20)
+    out["wait_status"] = mlp.last_status()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    mlp.close()
+    dist.destroy_process_group()
+
+
 def main(args):
     import bench   # peaks reader lives with the benchmark
+    if getattr(args, "only", None) == "column_parallel":
+        column_parallel_kernels(args.rows if args.rows > 256 else 4096)
+        return
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     Q.warm_fused(True)
