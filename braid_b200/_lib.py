@@ -31,6 +31,7 @@ _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_s
 SIGNATURES = {
     "bq_version": (_int, []),
     "bq_status_string": (ctypes.c_char_p, [_int]),
+    "bq_scratchless_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "bq_quant_workspace_bytes": (_sz, []),
     "bq_quantize_act": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _sz, _vp]),
     "bq_quantize_act_static": (_int, [_vp, _int, _i64, _vp, _vp, _vp]),

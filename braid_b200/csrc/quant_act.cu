@@ -196,6 +196,11 @@ __global__ void __launch_bounds__(512, 2) quant_stream_kernel(const QParams p) {
     grid_depart(static_cast<QuantWs*>(p.ws), coherent ? p.wait_seen : nullptr, p.wait_count);
 }
 
+// Sticky status of the launches that run without scratch from the caller (the cast half alone):
+// a bounded wait that ran out there has no status word of the caller's to raise, so it raises
+// this one; bq_scratchless_status() reads and clears it.
+__device__ unsigned int g_scratchless_status = 0u;
+
 // ---- plain quantizer at prefill sizes: bulk copies into a shared-memory ring --------------
 // The register-fed streaming kernel above keeps 64 bytes per thread in flight and computes
 // between its loads; at prefill sizes that is half of what HBM needs.  Here one producer lane
@@ -409,7 +414,11 @@ __global__ void __launch_bounds__(kRingThreads + 32, 2) quant_ring_kernel(const 
   __syncthreads();
   if (s_failed != 0u) {
     if (threadIdx.x == 0) {
-      atomicExch(&static_cast<QuantWs*>(p.ws)->status, (unsigned int)bq::kErrDeviceWait);
+      // the cast half alone runs without scratch: it raises the library's own sticky word
+      if (p.ws != nullptr)
+        atomicExch(&static_cast<QuantWs*>(p.ws)->status, (unsigned int)bq::kErrDeviceWait);
+      else
+        atomicExch(&g_scratchless_status, (unsigned int)bq::kErrDeviceWait);
       const long long t0 = clock64();
       while (clock64() - t0 < 2000000LL) {}
     }
@@ -722,6 +731,20 @@ int bq::quant_set_option(const char* key, long long value) {
   if (eq(key, "quant_pdl")) { g_opt_quant_pdl = value ? 1 : 0; return kOk; }
   if (eq(key, "quant_ring")) { g_opt_quant_ring = value ? 1 : 0; return kOk; }
   return kErrBadArg;
+}
+
+extern "C" int bq_scratchless_status(int* status_out) {
+  if (status_out == nullptr) return bq::kErrBadArg;
+  unsigned int v = 0u;
+  if (cudaDeviceSynchronize() != cudaSuccess ||
+      cudaMemcpyFromSymbol(&v, g_scratchless_status, sizeof(v)) != cudaSuccess)
+    return bq::kErrLaunch;
+  if (v != 0u) {
+    const unsigned int zero = 0u;
+    if (cudaMemcpyToSymbol(g_scratchless_status, &zero, sizeof(zero)) != cudaSuccess) return bq::kErrLaunch;
+  }
+  *status_out = static_cast<int>(v);
+  return bq::kOk;
 }
 
 extern "C" size_t bq_quant_workspace_bytes(void) { return sizeof(QuantWs); }

@@ -251,7 +251,11 @@ def device_status(device: torch.device | int | None = None) -> int:
     bad = int(words.max().item())
     if bad:
         words.zero_()
-    return bad
+    # launches that take no scratch (the cast pass) raise a word inside the library
+    own = ctypes.c_int(0)
+    with torch.cuda.device(idx):
+        _lib.check(_require_lib().bq_scratchless_status(ctypes.byref(own)), "scratchless_status")
+    return bad or int(own.value)
 
 
 def set_option(key: str, value: int) -> None:

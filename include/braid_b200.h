@@ -44,6 +44,13 @@ extern "C" {
 /* Library version (major*100 + minor). */
 int bq_version(void);
 
+/*
+ * Synchronises the current device and returns, through *status_out, the sticky status of the
+ * launches that take no scratch from the caller (bq_cast_act): 0, or BQ_ERR_DEVICE_WAIT when a
+ * bounded wait of such a launch ran out since the last call; clears it.  Never during capture.
+ */
+int bq_scratchless_status(int* status_out);
+
 /* Human-readable text for a status code; never NULL. */
 const char* bq_status_string(int status);
 
