@@ -104,7 +104,31 @@ def test_argument_validation_returns_before_any_cuda_call(lib):
     assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 1, 8, 60, 32, 64, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
     assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 7, 8, 64, 32, 64, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
     assert lib.bq_gemm_w8a8(16, 16, 16, 16, 16, 1, 8, 64, 32, 64, None, 0, None) == _lib.BQ_ERR_WORKSPACE
+    # the prefill-size and column-parallel entry points: every check precedes any CUDA call
+    assert lib.bq_cast_act(None, 1, 8, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_cast_act(24, 1, 8, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_rmsnorm_scale(16, 1, 4, 64, 64, 16, 1e-6, None, 64, 16, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_rmsnorm_scale(16, 1, 4, 64, 64, 16, 1e-6, 16, 64, 16, None, 0, None) == _lib.BQ_ERR_WORKSPACE
+    assert lib.bq_rmsnorm_scale(16, 1, 4, 62, 64, 16, 1e-6, 16, 64, 16, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_gated_rmsnorm_scale(16, 0, 256, 16, 1, 256, 16, 1e-6, 4, 2, 64, 16, 256, 16, 16, 16,
+                                      None) == _lib.BQ_ERR_UNSUPPORTED          # head_dim must be 128
+    assert lib.bq_silu_mul_dense_scale(16, 16, 1, 4, 16, 16, 16, None, 16, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_silu_mul(16, 16, 1, 4, 12, 12, 12, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_sigmoid_mul(16, 16, 1, 4, 16, 16, 16, 0, 0, 16, None) == _lib.BQ_ERR_BAD_ARG
+    ptrs = (ctypes.c_void_p * 2)(16, 32)
+    bad = (ctypes.c_void_p * 2)(16, None)
+    assert lib.bq_word_push(None, 2, ptrs, ptrs, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_word_push(16, 9, ptrs, ptrs, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_word_push(16, 2, bad, ptrs, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_wait_flag_scale(16, 16, 0, 16, 16, 2, 0, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_wait_flag_scale(16, 16, 2, 16, 16, 9, 0, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_cast_act_push(16, 1, 4, 16, 16, None, 2, ptrs, 64, ptrs, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_cast_act_push(16, 1, 4, 12, 16, 16, 2, ptrs, 64, ptrs, 16, 16, None) == _lib.BQ_ERR_UNSUPPORTED
+    assert lib.bq_rows_push(16, 1, 4, 16, 16, 2, bad, 64, ptrs, 16, 16, None) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_rows_push(16, 1, 4, 16, 16, 2, ptrs, 64, ptrs, None, 0, None) == _lib.BQ_ERR_WORKSPACE
+    assert lib.bq_scratchless_status(None) == _lib.BQ_ERR_BAD_ARG
     assert lib.bq_set_option(b"no_such_option", 1) == _lib.BQ_ERR_BAD_ARG
+    assert lib.bq_set_option(b"quant_ring", 1) == _lib.BQ_OK and lib.bq_set_option(b"push_tma", 1) == _lib.BQ_OK
     assert lib.bq_set_option(b"decode_split_k", 0) == _lib.BQ_OK
     for code in range(0, 9):
         assert _lib.status_string(code)
