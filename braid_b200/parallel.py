@@ -263,8 +263,8 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
     stores it into every rank's `h` buffer; down shard: one GEMM whose epilogue stores its slice
     into every rank's `y` buffer.  The last CTA of a launch signals every rank once.  The wait
     for `h` sits inside the quantizer that consumes it; the wait for `y` is a one-thread kernel.
-    Both are bounded (a wait that runs out raises a status word).  Four launches per rank and
-    no collective.  Buffers are reused from call to call: a rank cannot start writing exchange
+    Both are bounded (a wait that runs out raises a status word).  Four launches per rank at
+    decode sizes (eight at prefill sizes, see the phases below) and no collective.  Buffers are reused from call to call: a rank cannot start writing exchange
     n+1 into a peer before that peer has finished reading exchange n, because its own exchange
     n completes only after every peer has launched past that read."""
 
@@ -304,11 +304,11 @@ class FusedColumnParallelMLP(ColumnParallelMLP):
         self.buffers.close(self.group)
 
     # -- the phases (a test interleaves them over emulated ranks; forward() runs them in order)
-    # Prefill sizes (from `codes_from` rows on) exchange h as e4m3 CODES: the gate/up GEMM keeps
+    # Prefill sizes (from `amax_from` rows on) exchange h as e4m3 CODES: the gate/up GEMM keeps
     # its shard of h local and returns the shard's scale; the scales go round as 4-byte words;
     # a one-thread kernel waits for them and takes their maximum (the scale of the whole h); an
     # elementwise kernel casts the shard and stores the codes into every rank's buffer, a warp
-    # writing 256 contiguous bytes per rank.  Half the bytes of the bf16 exchange and whole
+    # writing 512 contiguous bytes per rank.  Half the bytes of the bf16 exchange and whole
     # lines on the links.  `prefill_form = "epilogue"` selects the other spelling: bf16 pieces
     # pushed from the GEMM's epilogue (overlapped with the GEMM, but 128-byte pieces scattered
     # over rows move at about two thirds of the links' copy rate) and the shard's max |h| ahead
