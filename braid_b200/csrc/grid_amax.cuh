@@ -110,5 +110,32 @@ __device__ __forceinline__ void grid_depart(QuantWs* ws, unsigned int* wait_seen
   }
 }
 
+// Host side: launches a grid-stride kernel with at most as many CTAs as the device holds at
+// once (`want` CTAs if that is fewer), so that no partial second wave trails the first -- a grid
+// of 8 CTAs per SM where five fit ran 1.6 waves.  Programmatic dependent launch on request.
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_resident(Kernel kernel, long long want, int threads, int sms, bool pdl,
+                                   cudaStream_t stream, Args... args) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess ||
+      per_sm < 1) {
+    (void)cudaGetLastError();
+    per_sm = 4;
+  }
+  const long long cap = static_cast<long long>(per_sm) * sms;
+  long long grid = want < cap ? want : cap;
+  if (grid < 1) grid = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 }  // namespace qd
 }  // namespace bq

@@ -493,21 +493,11 @@ int launch_rmsnorm_scale(const NormParams& p, cudaStream_t stream) {
     return bq::kErrLaunch;
   }
   const int per_thread = (p.cols / kVec + kNormThreads - 1) / kNormThreads;
-  const int grid = p.rows < 8 * sms ? p.rows : 8 * sms;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kNormThreads, 1, 1);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
   cudaError_t e;
-  if (per_thread <= 2) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 2>, p);
-  else if (per_thread <= 4) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 4>, p);
-  else if (per_thread <= 8) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 8>, p);
-  else if (per_thread <= 16) e = cudaLaunchKernelEx(&cfg, rmsnorm_scale_kernel<T, 16>, p);
+  if (per_thread <= 2) e = launch_resident(rmsnorm_scale_kernel<T, 2>, p.rows, kNormThreads, sms, true, stream, p);
+  else if (per_thread <= 4) e = launch_resident(rmsnorm_scale_kernel<T, 4>, p.rows, kNormThreads, sms, true, stream, p);
+  else if (per_thread <= 8) e = launch_resident(rmsnorm_scale_kernel<T, 8>, p.rows, kNormThreads, sms, true, stream, p);
+  else if (per_thread <= 16) e = launch_resident(rmsnorm_scale_kernel<T, 16>, p.rows, kNormThreads, sms, true, stream, p);
   else return bq::kErrUnsupported;
   if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
   return bq::kOk;
@@ -624,27 +614,21 @@ extern "C" int bq_gated_rmsnorm_scale(const void* y, int y_dtype, int64_t ld_y, 
     return bq::kErrLaunch;
   }
   const long long want = (rows * heads + kGatedWarps - 1) / kGatedWarps;
-  const int grid = static_cast<int>(want < 8LL * sms ? want : 8LL * sms);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kGatedWarps * 32, 1, 1);
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int threads = kGatedWarps * 32;
   const bool yf32 = (y_dtype == BQ_DTYPE_F32) && (dtype != BQ_DTYPE_F32);
   cudaError_t e;
   switch (dtype) {
-    case BQ_DTYPE_F32: e = cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<float, false>, p); break;
+    case BQ_DTYPE_F32:
+      e = launch_resident(gated_rmsnorm_scale_kernel<float, false>, want, threads, sms, true, st, p);
+      break;
     case BQ_DTYPE_BF16:
-      e = yf32 ? cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__nv_bfloat16, true>, p)
-               : cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__nv_bfloat16, false>, p);
+      e = yf32 ? launch_resident(gated_rmsnorm_scale_kernel<__nv_bfloat16, true>, want, threads, sms, true, st, p)
+               : launch_resident(gated_rmsnorm_scale_kernel<__nv_bfloat16, false>, want, threads, sms, true, st, p);
       break;
     default:
-      e = yf32 ? cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__half, true>, p)
-               : cudaLaunchKernelEx(&cfg, gated_rmsnorm_scale_kernel<__half, false>, p);
+      e = yf32 ? launch_resident(gated_rmsnorm_scale_kernel<__half, true>, want, threads, sms, true, st, p)
+               : launch_resident(gated_rmsnorm_scale_kernel<__half, false>, want, threads, sms, true, st, p);
   }
   if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
   return bq::kOk;

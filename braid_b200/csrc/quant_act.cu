@@ -908,28 +908,21 @@ template <int MODE>
 int launch_dense(int dtype, const QParams& p, void* out, cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return bq::kErrLaunch;
-  unsigned long long want = ((unsigned long long)p.n_groups + 255ull) / 256ull;
-  const int grid = (int)(want < (unsigned long long)(8 * sms) ? want : (unsigned long long)(8 * sms));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = g_opt_quant_pdl ? 1 : 0;
+  const long long want = (long long)(((unsigned long long)p.n_groups + 255ull) / 256ull);
+  const bool pdl = g_opt_quant_pdl != 0;
   cudaError_t e;
   switch (dtype) {
     case BQ_DTYPE_F32:
-      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<float, MODE>, p, static_cast<float*>(out));
+      e = launch_resident(prologue_dense_kernel<float, MODE>, want, 256, sms, pdl, stream, p,
+                          static_cast<float*>(out));
       break;
     case BQ_DTYPE_BF16:
-      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<__nv_bfloat16, MODE>, p,
-                             static_cast<__nv_bfloat16*>(out));
+      e = launch_resident(prologue_dense_kernel<__nv_bfloat16, MODE>, want, 256, sms, pdl, stream, p,
+                          static_cast<__nv_bfloat16*>(out));
       break;
     case BQ_DTYPE_F16:
-      e = cudaLaunchKernelEx(&cfg, prologue_dense_kernel<__half, MODE>, p, static_cast<__half*>(out));
+      e = launch_resident(prologue_dense_kernel<__half, MODE>, want, 256, sms, pdl, stream, p,
+                          static_cast<__half*>(out));
       break;
     default: return bq::kErrBadArg;
   }
@@ -1015,21 +1008,14 @@ template <bool CAST>
 int launch_row_push(int dtype, const RowPush& p, cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return bq::kErrLaunch;
-  const int grid = p.rows < 8 * sms ? p.rows : 8 * sms;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = g_opt_quant_pdl ? 1 : 0;
+  const bool pdl = g_opt_quant_pdl != 0;
   cudaError_t e;
   switch (dtype) {
-    case BQ_DTYPE_F32: e = cudaLaunchKernelEx(&cfg, row_push_kernel<float, CAST>, p); break;
-    case BQ_DTYPE_BF16: e = cudaLaunchKernelEx(&cfg, row_push_kernel<__nv_bfloat16, CAST>, p); break;
-    case BQ_DTYPE_F16: e = cudaLaunchKernelEx(&cfg, row_push_kernel<__half, CAST>, p); break;
+    case BQ_DTYPE_F32: e = launch_resident(row_push_kernel<float, CAST>, p.rows, 256, sms, pdl, stream, p); break;
+    case BQ_DTYPE_BF16:
+      e = launch_resident(row_push_kernel<__nv_bfloat16, CAST>, p.rows, 256, sms, pdl, stream, p);
+      break;
+    case BQ_DTYPE_F16: e = launch_resident(row_push_kernel<__half, CAST>, p.rows, 256, sms, pdl, stream, p); break;
     default: return bq::kErrBadArg;
   }
   if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
