@@ -114,10 +114,10 @@ __device__ __forceinline__ void grid_depart(QuantWs* ws, unsigned int* wait_seen
 // once (`want` CTAs if that is fewer), so that no partial second wave trails the first -- a grid
 // of 8 CTAs per SM where five fit ran 1.6 waves.  Programmatic dependent launch on request.
 template <typename Kernel, typename... Args>
-inline cudaError_t launch_resident(Kernel kernel, long long want, int threads, int sms, bool pdl,
-                                   cudaStream_t stream, Args... args) {
+inline cudaError_t launch_resident_smem(Kernel kernel, long long want, int threads, int sms, bool pdl,
+                                        size_t dynamic_smem, cudaStream_t stream, Args... args) {
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess ||
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dynamic_smem) != cudaSuccess ||
       per_sm < 1) {
     (void)cudaGetLastError();
     per_sm = 4;
@@ -128,6 +128,7 @@ inline cudaError_t launch_resident(Kernel kernel, long long want, int threads, i
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = dynamic_smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -135,6 +136,11 @@ inline cudaError_t launch_resident(Kernel kernel, long long want, int threads, i
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_resident(Kernel kernel, long long want, int threads, int sms, bool pdl,
+                                   cudaStream_t stream, Args... args) {
+  return launch_resident_smem(kernel, want, threads, sms, pdl, 0, stream, args...);
 }
 
 }  // namespace qd

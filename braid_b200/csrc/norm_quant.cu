@@ -191,15 +191,11 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_scale_kernel(const NormP
   __shared__ float s_max[4];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int n_vec = p.cols / kVec;
-  float g[VPT][kVec];
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = t + i * kNormThreads;
-    if (v < n_vec) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(p.gamma) + v);
-      g[i][0] = f.x; g[i][1] = f.y; g[i][2] = f.z; g[i][3] = f.w;
-    }
-  }
+  // gamma lives in shared memory here, not in registers: a CTA normalises many rows, and 32
+  // registers less per thread are three more CTAs per SM to hide the loads behind
+  extern __shared__ float4 s_gamma[];
+  for (int v = t; v < n_vec; v += kNormThreads) s_gamma[v] = __ldg(reinterpret_cast<const float4*>(p.gamma) + v);
+  __syncthreads();
   bq::pdl_wait_prior_grids();
   float m = 0.0f;
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
@@ -237,9 +233,11 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_scale_kernel(const NormP
     for (int i = 0; i < VPT; ++i) {
       const int v = t + i * kNormThreads;
       if (v < n_vec) {
+        const float4 gv = s_gamma[v];
+        const float g[kVec] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
         for (int j = 0; j < kVec; ++j) {
-          const float y = __fmul_rn(g[i][j], __fmul_rn(rstd, widen(x[i].v[j])));
+          const float y = __fmul_rn(g[j], __fmul_rn(rstd, widen(x[i].v[j])));
           x[i].v[j] = narrow<T>(y);
           m = nan_max(m, fabsf(widen(x[i].v[j])));
         }
@@ -493,11 +491,13 @@ int launch_rmsnorm_scale(const NormParams& p, cudaStream_t stream) {
     return bq::kErrLaunch;
   }
   const int per_thread = (p.cols / kVec + kNormThreads - 1) / kNormThreads;
+  const size_t smem = static_cast<size_t>(p.cols) * sizeof(float);     // gamma
+  if (smem > 48 * 1024) return bq::kErrUnsupported;
   cudaError_t e;
-  if (per_thread <= 2) e = launch_resident(rmsnorm_scale_kernel<T, 2>, p.rows, kNormThreads, sms, true, stream, p);
-  else if (per_thread <= 4) e = launch_resident(rmsnorm_scale_kernel<T, 4>, p.rows, kNormThreads, sms, true, stream, p);
-  else if (per_thread <= 8) e = launch_resident(rmsnorm_scale_kernel<T, 8>, p.rows, kNormThreads, sms, true, stream, p);
-  else if (per_thread <= 16) e = launch_resident(rmsnorm_scale_kernel<T, 16>, p.rows, kNormThreads, sms, true, stream, p);
+  if (per_thread <= 2) e = launch_resident_smem(rmsnorm_scale_kernel<T, 2>, p.rows, kNormThreads, sms, true, smem, stream, p);
+  else if (per_thread <= 4) e = launch_resident_smem(rmsnorm_scale_kernel<T, 4>, p.rows, kNormThreads, sms, true, smem, stream, p);
+  else if (per_thread <= 8) e = launch_resident_smem(rmsnorm_scale_kernel<T, 8>, p.rows, kNormThreads, sms, true, smem, stream, p);
+  else if (per_thread <= 16) e = launch_resident_smem(rmsnorm_scale_kernel<T, 16>, p.rows, kNormThreads, sms, true, smem, stream, p);
   else return bq::kErrUnsupported;
   if (e != cudaSuccess) { (void)cudaGetLastError(); return bq::kErrLaunch; }
   return bq::kOk;
