@@ -144,6 +144,7 @@ struct GemmParams {
   int b_stages;        // stream kernel: depth of the activation ring
   int out_dtype;
   int m_tiles;         // tile kernel: ceil(M / 128)
+  int pair_n;          // pair kernel, plain form: output columns per tile, 256 or 128
   int total_tiles;     // tile kernel
   unsigned int* status;
   ArgmaxOut argmax;
@@ -981,9 +982,9 @@ __device__ __forceinline__ void pair_epilogue_rows(const GemmParams& p, const Se
                                                    float& mx) {
   constexpr int kCols = 128 / ES;              // output columns per 128-byte piece
   constexpr int kPieces = ES == 4 ? 4 : 2;     // 16-byte pieces per 16 accumulator columns
-  constexpr int kOutCols = SILU ? kPairTile / 2 : kPairTile;
-  const int c_end = (col_half + 1) * (kOutCols / 2);
-  for (int c = col_half * (kOutCols / 2); c < c_end; c += kCols) {
+  const int out_cols = SILU ? kPairTile / 2 : p.pair_n;
+  const int c_end = (col_half + 1) * (out_cols / 2);
+  for (int c = col_half * (out_cols / 2); c < c_end; c += kCols) {
     // pieces beyond this weight's rows are never stored (warp-uniform)
     if ((n0 + c) >= seg.n) break;
     // the TMA store of the previous piece must have finished reading the box
@@ -1081,7 +1082,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + kPairTile - 1) / kPairTile;
   const bool silu = p.pair.on != 0;                       // gate/up tiles, h = silu(gate) * up out
-  const int n_step = silu ? kPairTile / 2 : kPairTile;    // output columns per tile
+  // output columns per tile: 128 of h in the SiLU form; 256 in the plain form, or 128 for a weight
+  // so narrow that 256-wide tiles would leave CTA pairs without work (same sums, more tiles)
+  const int n_step = silu ? kPairTile / 2 : p.pair_n;
+  const int b_rows = silu ? kRowTile : p.pair_n / 2;       // weight rows this CTA loads per K block
   float* const s_amax = reinterpret_cast<float*>(base_ptr + kPairStages * kPairStageBytes + 512);
 
   if (threadIdx.x == 0) {
@@ -1122,12 +1126,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
         const int m0 = m_idx * kPairTile + rank * kRowTile;
         // plain: this CTA's half of the tile's 256 weight rows; SiLU form: the leader loads 128
         // gate rows, its peer the 128 up rows of the same output columns
-        const int n0 = silu ? n_idx * kRowTile : n_idx * kPairTile + rank * kRowTile;
+        const int n0 = silu ? n_idx * kRowTile : n_idx * n_step + rank * b_rows;
         const CUtensorMap* const w_map = silu ? &tm_w.w[rank] : &tm_w.w[sg];
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kPairStages, use = it / kPairStages;
           if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2u * (kATileBytes + (uint32_t)b_rows * kBK));
           tma_load_2d_pair(a_tile(s), &tm_x, full_bar(s), kb * kBK, m0, pol);
           tma_load_2d_pair(b_tile(s), w_map, full_bar(s), kb * kBK, n0, pol);
         }
@@ -1137,7 +1141,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x,
     __syncwarp();
   } else if (warp == 1) {
     if (rank == 0 && elect_one()) {
-      const uint32_t idesc = idesc_e4m3(kPairTile, kPairTile);
+      const uint32_t idesc = (silu || p.pair_n == kPairTile) ? idesc_e4m3(kPairTile, kPairTile)
+                                                             : idesc_e4m3(kPairTile, kPairTile / 2);
       int it = 0, tile_iter = 0;
       bool ok = true;
       for (int t = pair; t < p.total_tiles && ok; t += n_pairs, ++tile_iter) {
@@ -1366,6 +1371,7 @@ int device_sms() {
 
 long long g_opt_split = 0, g_opt_stages = 0, g_opt_stream_max_m = 256, g_opt_cta_target = 160;
 long long g_opt_push_tma = 1;   // prefill push epilogue: bulk tensor stores (0: 16-byte plain stores)
+long long g_opt_pair_narrow = -1;   // prefill: 128-column tiles for a lone narrow weight (-1 auto, 0 never, 1 always)
 long long g_opt_pdl = 1;   // programmatic dependent launch on by default
 long long g_opt_b_stages = 0;   // activation ring depth: 0 = heuristic, -1 = as deep as the weight ring
 long long g_opt_smem_cap = 0;   // 0 = no cap on pipeline bytes per CTA
@@ -1568,7 +1574,7 @@ int launch_pair(const CUtensorMap& tm_x, const WeightMaps& maps, const OutMaps& 
   if (pairs < 1) pairs = 1;
   if (p.push.n > 0) p.push.expected = (unsigned)(2 * pairs);   // every CTA has a tile and stores
   g_last_launch[0] = 2; g_last_launch[1] = 2 * pairs; g_last_launch[2] = 2;
-  g_last_launch[3] = kPairStages; g_last_launch[4] = smem; g_last_launch[5] = kPairTile;
+  g_last_launch[3] = kPairStages; g_last_launch[4] = smem; g_last_launch[5] = p.pair_n;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
@@ -1600,6 +1606,7 @@ int bq::gemm_set_option(const char* key, long long value) {
   if (strcmp(key, "decode_b_stages") == 0) { g_opt_b_stages = value; return kOk; }
   if (strcmp(key, "gemm_pdl") == 0) { g_opt_pdl = value ? 1 : 0; return kOk; }
   if (strcmp(key, "push_tma") == 0) { g_opt_push_tma = value ? 1 : 0; return kOk; }
+  if (strcmp(key, "pair_narrow") == 0) { g_opt_pair_narrow = value < 0 ? -1 : (value ? 1 : 0); return kOk; }
   if (strcmp(key, "decode_smem_cap") == 0) { g_opt_smem_cap = value; return kOk; }
   if (strcmp(key, "decode_cta_target") == 0) {
     if (value < 1) return kErrBadArg;
@@ -1713,9 +1720,18 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
   }
 
   const bool pair_path = !stream_path;
-  const int w_box_rows = kRowTile;
-  const int tile_n = pair_path ? ((pair && pair->prefill) ? kPairTile / 2 : kPairTile) : kRowTile;
   p.m_tiles = pair_path ? (int)((M + kPairTile - 1) / kPairTile) : (int)((M + kRowTile - 1) / kRowTile);
+  // plain prefill form of ONE narrow weight: 128-column tiles when 256-column ones would leave
+  // more than a quarter of the CTA pairs without a tile (the sums are the same, tile by tile)
+  p.pair_n = kPairTile;
+  if (pair_path && pair == nullptr && n_seg == 1) {
+    const long long wide_tiles = ((N[0] + kPairTile - 1) / kPairTile) * p.m_tiles;
+    const long long pairs = device_sms() / 2;
+    const bool narrow = g_opt_pair_narrow > 0 || (g_opt_pair_narrow < 0 && wide_tiles * 4 < pairs * 3);
+    if (narrow) p.pair_n = kPairTile / 2;
+  }
+  const int w_box_rows = (pair_path && pair == nullptr) ? p.pair_n / 2 : kRowTile;
+  const int tile_n = pair_path ? ((pair && pair->prefill) ? kPairTile / 2 : p.pair_n) : kRowTile;
   OutMaps ymaps;
   memset(&ymaps, 0, sizeof(ymaps));
   int tiles = 0;
