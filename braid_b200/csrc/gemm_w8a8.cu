@@ -1721,13 +1721,15 @@ int run_grouped(const void* xq, const float* sx, int64_t M, int64_t K, int n_seg
 
   const bool pair_path = !stream_path;
   p.m_tiles = pair_path ? (int)((M + kPairTile - 1) / kPairTile) : (int)((M + kRowTile - 1) / kRowTile);
-  // plain prefill form of ONE narrow weight: 128-column tiles when 256-column ones would leave
-  // more than a quarter of the CTA pairs without a tile (the sums are the same, tile by tile)
+  // plain prefill form of ONE narrow weight: 128-column tiles when all of them still run at once,
+  // i.e. when 256-column ones would leave half of the CTA pairs without a tile (the sums are the
+  // same, tile by tile; a 128-column tile takes 0.6-0.75 of a 256-column one, so a second round
+  // of them costs more than the idle pairs do)
   p.pair_n = kPairTile;
   if (pair_path && pair == nullptr && n_seg == 1) {
     const long long wide_tiles = ((N[0] + kPairTile - 1) / kPairTile) * p.m_tiles;
     const long long pairs = device_sms() / 2;
-    const bool narrow = g_opt_pair_narrow > 0 || (g_opt_pair_narrow < 0 && wide_tiles * 4 < pairs * 3);
+    const bool narrow = g_opt_pair_narrow > 0 || (g_opt_pair_narrow < 0 && wide_tiles * 2 <= pairs);
     if (narrow) p.pair_n = kPairTile / 2;
   }
   const int w_box_rows = (pair_path && pair == nullptr) ? p.pair_n / 2 : kRowTile;

@@ -563,7 +563,7 @@ int bq_read_device_status(void* ws, void* stream, int* status_out);
  * bq_set_option("quant_ring", 0/1)      plain quantizer at prefill sizes through the shared-memory ring (default 1)
  * bq_set_option("push_tma", 0/1)        prefill push epilogue by bulk tensor stores (default 1) or 16-byte plain stores
  * bq_set_option("pair_narrow", -1/0/1) prefill kernel: 128-column tiles for a lone narrow weight (-1 = when 256-column
- *                                       tiles would leave a quarter of the CTA pairs idle; same results either way)
+ *                                       tiles would leave half of the CTA pairs idle; same results either way)
  * Returns BQ_ERR_BAD_ARG for an unknown key.
  */
 int bq_set_option(const char* key, int64_t value);

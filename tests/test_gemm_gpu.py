@@ -142,8 +142,9 @@ def test_lm_head_at_full_vocabulary(Q, M):
 
 
 @pytest.mark.parametrize("M,N,K,dt", [(4096, 512, 12288, torch.bfloat16), (1000, 1040, 4096, torch.bfloat16),
-                                      (300, 144, 512, torch.float32), (2048, 4096, 4096, torch.bfloat16)],
-                         ids=["down-shard-of-8", "ragged", "tiny-fp32", "wide-weight"])
+                                      (300, 144, 512, torch.float32), (2048, 4096, 4096, torch.bfloat16),
+                                      (768, 4096, 512, torch.bfloat16)],
+                         ids=["down-shard-of-8", "ragged", "tiny-fp32", "wide-weight", "two-rounds-if-narrow"])
 def test_prefill_tiles_of_128_columns_give_the_bits_of_256(Q, M, N, K, dt):
     """A lone narrow weight at prefill sizes is tiled 256 x 128 instead of 256 x 256 so that more
     CTA pairs have work; every output element is the same sum in the same order either way."""
@@ -160,7 +161,7 @@ def test_prefill_tiles_of_128_columns_give_the_bits_of_256(Q, M, N, K, dt):
     assert torch.equal(wide, narrow)
     auto = Q.fp8_matmul(xq, sx, fw, out_dtype=dt)
     tiles_wide = -(-N // 256) * -(-M // 256)
-    assert Q.last_gemm_launch()["mma_n"] == (128 if tiles_wide * 4 < 74 * 3 else 256)
+    assert Q.last_gemm_launch()["mma_n"] == (128 if tiles_wide * 2 <= 74 else 256)
     assert torch.equal(auto, wide)
     assert Q.device_status() == 0
 
